@@ -1,0 +1,2 @@
+from .allocator import NumberPool, OutOfPagesError, OutOfSlotsError
+from .kv_cache import DEFAULT_PAGE_SIZE, Cache, LayerCache, PagedGroup, StateGroup

@@ -1,0 +1,88 @@
+// Fused attention inputs: per-head RMSNorm of q and k, rotary embedding, q written out, k
+// and v written to their place in the paged cache. One warp per (token, head).
+//
+// AntoineBut/TileInfer.jl: the norm over head_dim comes before the rotation and v is left
+// untouched (src/ops/interface.jl:161-177, src/ops/tile/fused.jl:20-33, 61-66); the rotation
+// pairs element i with i + D/2 and rounds each product and the sum
+// (src/ops/reference.jl:32-39); slot (page, offset) of the pool [pages][kv_heads][P][D]
+// (src/kv/paged_cache.jl:1-4).
+#include "common.cuh"
+
+#define AI_WARPS 4
+#define AI_MAX_D 512
+
+template <typename T>
+__global__ void attention_inputs_kernel(const T* __restrict__ qkv, long long qkv_stride, T* __restrict__ q_out,
+                                        T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                        const T* __restrict__ q_norm_w, const T* __restrict__ k_norm_w, float eps,
+                                        const float* __restrict__ cos_sin, const int* __restrict__ positions,
+                                        const int* __restrict__ slots, int nq, int nkv, int D, int page_size,
+                                        int write_kv) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int heads_total = nq + (write_kv ? 2 * nkv : 0);
+    const int head = blockIdx.y * AI_WARPS + warp;
+    if (head >= heads_total) return;
+    float* buf = smem + warp * D;
+
+    const T* src = qkv + (size_t)t * qkv_stride + (size_t)head * D;
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    const int kvh = is_q ? 0 : (is_k ? head - nq : head - nq - nkv);
+
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * nq + head) * D;
+    } else {
+        const int slot = slots[t];
+        const int page = slot / page_size, off = slot - page * page_size;
+        T* base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t)page * nkv + kvh) * page_size + off) * D;
+    }
+    if (!is_q && !is_k) {                    // value head: a copy
+        for (int d = lane; d < D; d += 32) dst[d] = src[d];
+        return;
+    }
+    const T* nw = is_q ? q_norm_w : k_norm_w;
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) {
+        const float v = to_f32(src[d]);
+        buf[d] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (nw != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+        for (int d = lane; d < D; d += 32) buf[d] = rnd<T>(to_f32(nw[d]) * rnd<T>(buf[d] * inv));
+    }
+    __syncwarp();
+    if (cos_sin == nullptr) {
+        for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(buf[d]);
+        return;
+    }
+    const int half = D >> 1;
+    const float* cs = cos_sin + (size_t)positions[t] * D;     // [half][2] = (cos, sin)
+    for (int d = lane; d < D; d += 32) {
+        const int i = d < half ? d : d - half;
+        const float c = cs[2 * i], s = cs[2 * i + 1];
+        const float rot = d < half ? -buf[d + half] : buf[d - half];
+        dst[d] = from_f32<T>(rnd<T>(buf[d] * c) + rnd<T>(rot * s));
+    }
+}
+
+extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, void* q_out, void* k_cache, void* v_cache,
+                                   const void* q_norm_w, const void* k_norm_w, float eps, const float* cos_sin,
+                                   const int* positions, const int* slots, int n_tokens, int nq, int nkv, int D,
+                                   int page_size, int write_kv, int dtype, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    TI_REQUIRE(D > 0 && D % 2 == 0 && D <= AI_MAX_D, "attention_inputs: head_dim %d must be even and at most %d", D, AI_MAX_D);
+    TI_REQUIRE(nq > 0 && nkv > 0 && page_size > 0, "attention_inputs: bad sizes nq=%d nkv=%d page=%d", nq, nkv, page_size);
+    const int heads_total = nq + (write_kv ? 2 * nkv : 0);
+    dim3 grid(n_tokens, (heads_total + AI_WARPS - 1) / AI_WARPS);
+    const size_t smem = (size_t)AI_WARPS * D * sizeof(float);
+    TI_DISPATCH_DTYPE(dtype, (attention_inputs_kernel<T><<<grid, AI_WARPS * 32, smem, stream>>>(
+                                 (const T*)qkv, qkv_stride, (T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)q_norm_w,
+                                 (const T*)k_norm_w, eps, cos_sin, positions, slots, nq, nkv, D, page_size, write_kv)));
+    return ti_check_launch("attention_inputs");
+}

@@ -1,0 +1,97 @@
+// Shared by every kernel file: element types, conversions, reductions, error reporting.
+//
+// All entry points are extern "C", take raw device pointers and a stream, allocate
+// nothing, and return 0 on success. On a refused size or a CUDA error they return non-zero
+// and ti_last_error() gives the text. Element types are passed as TI_F32 / TI_BF16.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#define TI_F32 0
+#define TI_BF16 1
+
+typedef __nv_bfloat16 bf16;
+
+extern "C" const char* ti_last_error();
+int ti_fail(const char* fmt, ...);
+int ti_check_launch(const char* what);
+
+#define TI_REQUIRE(cond, ...)                \
+    do {                                     \
+        if (!(cond)) return ti_fail(__VA_ARGS__); \
+    } while (0)
+
+// ---- conversions: every kernel computes in float and rounds once on store ---------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+// Round to the storage type and come back: the rounding points of the bfloat16 path.
+template <typename T> __device__ __forceinline__ float rnd(float v) { return to_f32(from_f32<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `scratch` holds
+// 33 floats of shared memory. The order of the additions is fixed by the block size.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < warps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < warps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// xIELU with the reference's rounding points (src/ops/reference.jl:49-56):
+//   bx = rnd(beta x); x > 0: rnd(rnd(rnd(ap x) x) + bx); else rnd(rnd(rnd(rnd(expm1(min(x,eps))) - x) an) + bx)
+struct XieluParams {
+    float alpha_p, alpha_n, beta, eps;
+};
+template <typename T> __device__ __forceinline__ float xielu_value(float x, const XieluParams& a) {
+    const float bx = rnd<T>(a.beta * x);
+    if (x > 0.f) return rnd<T>(rnd<T>(rnd<T>(a.alpha_p * x) * x) + bx);
+    const float e = rnd<T>(expm1f(fminf(x, a.eps)));
+    return rnd<T>(rnd<T>(rnd<T>(e - x) * a.alpha_n) + bx);
+}
+
+#define TI_DISPATCH_DTYPE(dtype, ...)                                   \
+    do {                                                                \
+        if ((dtype) == TI_F32) { typedef float T; __VA_ARGS__; }        \
+        else if ((dtype) == TI_BF16) { typedef bf16 T; __VA_ARGS__; }   \
+        else return ti_fail("unknown element type code %d", (int)(dtype)); \
+    } while (0)

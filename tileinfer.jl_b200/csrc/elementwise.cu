@@ -1,0 +1,167 @@
+// Embedding gather, row gather, xIELU, RMSNorm and the fused residual-add + RMSNorm.
+//
+// Formulas and rounding points follow AntoineBut/TileInfer.jl: embedding
+// src/ops/reference.jl:10; RMSNorm (normalise in 32-bit, round, then scale in the storage
+// type) src/ops/reference.jl:17-21; residual add rounded to the storage type before the norm
+// src/ops/tile/norm.jl:48-77; xIELU src/ops/reference.jl:49-56.
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+extern "C" const char* ti_last_error() { return g_error; }
+
+int ti_fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return 1;
+}
+
+int ti_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return ti_fail("%s: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
+                             int hidden, int vocab, int* __restrict__ status) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) {            // never read outside the table; report instead
+        if (threadIdx.x == 0) atomicExch(status, 1 + t);
+        id = 0;
+    }
+    const T* row = table + (size_t)id * hidden;
+    T* dst = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = row[i];
+}
+
+extern "C" int ti_embed(void* out, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
+                        int dtype, int* status, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    TI_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes n=%d hidden=%d vocab=%d", n_tokens, hidden, vocab);
+    const int threads = hidden >= 1024 ? 256 : 128;
+    TI_DISPATCH_DTYPE(dtype, (embed_kernel<T><<<n_tokens, threads, 0, stream>>>((T*)out, (const T*)table, ids, hidden, vocab, status)));
+    return ti_check_launch("embed");
+}
+
+// Rows idx[i] of x [*, size] to out [n, size] (the positions whose logits are wanted).
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ idx, int size) {
+    const T* row = x + (size_t)idx[blockIdx.x] * size;
+    T* dst = out + (size_t)blockIdx.x * size;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) dst[i] = row[i];
+}
+
+extern "C" int ti_gather_rows(void* out, const void* x, const int* idx, int n, int size, int dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    TI_DISPATCH_DTYPE(dtype, (gather_rows_kernel<T><<<n, 128, 0, stream>>>((T*)out, (const T*)x, idx, size)));
+    return ti_check_launch("gather_rows");
+}
+
+// ---------------------------------------------------------------------------- xIELU
+template <typename T>
+__global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ in, size_t count, XieluParams a) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < count; i += stride) out[i] = from_f32<T>(xielu_value<T>(to_f32(in[i]), a));
+}
+
+extern "C" int ti_xielu(void* out, const void* in, long long count, float alpha_p, float alpha_n, float beta, float eps,
+                        int dtype, cudaStream_t stream) {
+    if (count == 0) return 0;
+    XieluParams a{alpha_p, alpha_n, beta, eps};
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TI_DISPATCH_DTYPE(dtype, (xielu_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, (const T*)in, (size_t)count, a)));
+    return ti_check_launch("xielu");
+}
+
+// ---------------------------------------------------------------------------- RMSNorm
+// One block per row. y = rnd(w * rnd(x * inv_rms)), inv_rms = 1/sqrt(mean(x^2) + eps) in 32-bit.
+template <typename T>
+__global__ void rmsnorm_kernel(T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ w, int size, float eps) {
+    __shared__ float scratch[33];
+    const T* row = x + (size_t)blockIdx.x * size;
+    T* dst = y + (size_t)blockIdx.x * size;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float v = to_f32(row[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+    for (int i = threadIdx.x; i < size; i += blockDim.x)
+        dst[i] = from_f32<T>(to_f32(w[i]) * rnd<T>(to_f32(row[i]) * inv));
+}
+
+extern "C" int ti_rmsnorm(void* y, const void* x, const void* w, int n_rows, int size, float eps, int dtype, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    TI_REQUIRE(size > 0, "rmsnorm: size %d", size);
+    const int threads = size >= 2048 ? 512 : size >= 512 ? 256 : 128;
+    TI_DISPATCH_DTYPE(dtype, (rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((T*)y, (const T*)x, (const T*)w, size, eps)));
+    return ti_check_launch("rmsnorm");
+}
+
+// x <- rnd(x + d), h <- RMSNorm(x) * w. d is either `delta` (storage type) or the sum, in
+// a fixed order, of `n_partials` 32-bit partial products [s][n_rows][size] (a split-K
+// matrix product), rounded to the storage type first like any product's output.
+template <typename T>
+__global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
+                                   int n_partials, size_t partial_stride, const T* __restrict__ w, T* __restrict__ h,
+                                   int size, float eps) {
+    __shared__ float scratch[33];
+    T* row = x + (size_t)blockIdx.x * size;
+    T* dst = h + (size_t)blockIdx.x * size;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        float d;
+        if (partials != nullptr) {
+            const float* p = partials + (size_t)blockIdx.x * size + i;
+            d = p[0];
+            for (int s = 1; s < n_partials; ++s) d += p[(size_t)s * partial_stride];
+            d = rnd<T>(d);
+        } else {
+            d = to_f32(delta[(size_t)blockIdx.x * size + i]);
+        }
+        const float v = rnd<T>(to_f32(row[i]) + d);
+        row[i] = from_f32<T>(v);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+    // Each thread re-reads exactly the elements it wrote above.
+    for (int i = threadIdx.x; i < size; i += blockDim.x)
+        dst[i] = from_f32<T>(to_f32(w[i]) * rnd<T>(to_f32(row[i]) * inv));
+}
+
+extern "C" int ti_add_rmsnorm(void* x, const void* delta, const float* partials, int n_partials, long long partial_stride,
+                              const void* w, void* h, int n_rows, int size, float eps, int dtype, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    TI_REQUIRE(size > 0, "add_rmsnorm: size %d", size);
+    TI_REQUIRE((delta != nullptr) != (partials != nullptr), "add_rmsnorm: give delta or partials, not both");
+    TI_REQUIRE(partials == nullptr || n_partials >= 1, "add_rmsnorm: n_partials %d", n_partials);
+    const int threads = size >= 2048 ? 512 : size >= 512 ? 256 : 128;
+    TI_DISPATCH_DTYPE(dtype, (add_rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>(
+                                 (T*)x, (const T*)delta, partials, n_partials, (size_t)partial_stride, (const T*)w, (T*)h, size, eps)));
+    return ti_check_launch("add_rmsnorm");
+}
+
+// Plain residual add for blocks whose next norm is not fused: x <- rnd(x + delta).
+template <typename T>
+__global__ void add_kernel(T* __restrict__ x, const T* __restrict__ delta, size_t count) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < count; i += stride) x[i] = from_f32<T>(to_f32(x[i]) + to_f32(delta[i]));
+}
+
+extern "C" int ti_add(void* x, const void* delta, long long count, int dtype, cudaStream_t stream) {
+    if (count == 0) return 0;
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    TI_DISPATCH_DTYPE(dtype, (add_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)x, (const T*)delta, (size_t)count)));
+    return ti_check_launch("add");
+}

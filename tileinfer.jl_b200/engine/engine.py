@@ -1,0 +1,188 @@
+"""The engine: a model, its cache, and ONE step function.
+
+``Engine.step(entries, want)`` runs the next tokens of some live sequences as one batch
+from the cache and returns the logits at the wanted places. It is the only way tokens go
+through the model: generation, trace replay and the benchmarks all call it. The sequences
+of a step may have any lengths (whole prompts, or one token each); a step longer than
+``max_step_tokens`` is cut into chunks internally, which changes no result.
+
+AntoineBut/TileInfer.jl's counterpart runs one sequence per step
+(``forward!``: src/model/decoder.jl:210-227, src/engine/runner.jl:65-102): host preparation,
+one upload, the device-only step; steps of a few tokens are replayed from CUDA graphs
+(src/engine/runner.jl:1-12, 86-99). The batch, the slots and the chunking are this library's
+own.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache import Cache, DEFAULT_PAGE_SIZE
+from ..config import load_config, resolve_architecture
+from ..parts import Runtime
+from ..weights import load_tensors, random_tensors
+from .model import DecoderModel, ignorable_tensors, tensor_declarations
+from .step import StepPlanner
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def require_cuda(device="cuda") -> torch.device:
+    d = torch.device(device)
+    if d.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError("tileinfer_b200 runs on a CUDA device only (sm_100a); there is no CPU path")
+    return d
+
+
+class Engine:
+    def __init__(self, config, tensors: Dict[str, torch.Tensor], dtype="bfloat16", device="cuda",
+                 max_tokens: int = 4096, max_seqs: int = 8, max_context: Optional[int] = None,
+                 page_size: int = DEFAULT_PAGE_SIZE, max_step_tokens: int = 8192, kernels: str = "fast",
+                 graphs: bool = True, model_factory=None):
+        self.device = require_cuda(device)
+        self.config = config
+        self.dtype = _DTYPES[dtype]
+        self.rt = Runtime(self.dtype, self.device, kernels)
+        self.spec = config.model_spec()
+        max_context = int(min(max_context or self.spec.max_positions, self.spec.max_positions))
+        self.max_context = max_context
+        factory = model_factory or DecoderModel
+        self.model = factory(self.spec, tensors, self.rt, max_context)
+        self.cache = Cache(self.model.cache_requests(), self.dtype, self.device, max_tokens=max_tokens,
+                           max_seqs=max_seqs, page_size=page_size, max_seq_len=max_context,
+                           share=self.model.cache_shares())
+        self.max_step_tokens = int(max_step_tokens)
+        self.planner = StepPlanner(self.cache, self.max_step_tokens, self.device)
+        self.use_graphs = graphs
+        self._graphs: Dict[int, object] = {}
+        self._logits: Dict[int, torch.Tensor] = {}
+        self.vocab_size = self.spec.vocab_size
+
+    # ---- construction
+    @classmethod
+    def load(cls, model_dir: str, **kw) -> "Engine":
+        """From a folder with config.json and safetensors; the model class is chosen by config.json."""
+        with open(os.path.join(model_dir, "config.json")) as f:
+            raw = json.load(f)
+        arch = resolve_architecture(raw)
+        config = arch.config_class.from_dict(raw)
+        spec = config.model_spec()
+        tensors = load_tensors(model_dir, tensor_declarations(spec), ignorable_tensors(spec))
+        return cls(config, tensors, model_factory=arch.model_factory, **kw)
+
+    @classmethod
+    def random(cls, config, seed: int = 0, **kw) -> "Engine":
+        """Random weights drawn on the device (nothing is written to disk)."""
+        device = require_cuda(kw.get("device", "cuda"))
+        tensors = random_tensors(tensor_declarations(config.model_spec()), seed, dtype=torch.bfloat16, device=str(device))
+        return cls(config, tensors, **kw)
+
+    # ---- sequences
+    def new_sequence(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_sequence(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def sequence_length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Run ``entries`` = [(slot, next tokens)] as one batch; returns float32 logits
+        ``[wanted, vocab]`` in the order of the entries and of ``want`` (offsets into each entry's
+        tokens; default: each entry's last token)."""
+        entries = [(int(s), list(t)) for s, t in entries]
+        if want is None:
+            want = [[len(t) - 1] for _, t in entries]
+        want = [list(w) for w in want]
+        if len(want) != len(entries):
+            raise ValueError("want needs one list per entry")
+        seen = set()
+        for slot, toks in entries:
+            if slot in seen:
+                raise ValueError(f"sequence slot {slot} appears twice in one step")
+            seen.add(slot)
+            if not toks:
+                raise ValueError("an entry of a step has no tokens")
+            for t in toks:
+                if not 0 <= t < self.vocab_size:
+                    raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+            if self.cache.length(slot) + len(toks) > self.max_context:
+                raise ValueError(f"sequence would reach {self.cache.length(slot) + len(toks)} positions; "
+                                 f"max context is {self.max_context}")
+        # All pages first: a step that cannot be held changes nothing.
+        self.cache.reserve([(s, len(t)) for s, t in entries])
+        n_want = sum(len(w) for w in want)
+        n_total = sum(len(t) for _, t in entries)
+        decode = all(len(t) == 1 for _, t in entries) and all(w == [0] for w in want)
+        if decode and self.use_graphs and out is None:
+            return self._decode_step(entries, want)
+        logits = out if out is not None else torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device)
+        if n_total <= self.max_step_tokens:
+            ctx = self.planner.plan(entries, want)
+            self.model.forward(ctx, self.cache, logits)
+            for s, t in entries:
+                self.cache.advance(s, len(t))
+            return logits
+        row = 0
+        for chunk_entries, chunk_want in self._chunks(entries, want):
+            nw = sum(len(w) for w in chunk_want)
+            ctx = self.planner.plan(chunk_entries, chunk_want)
+            self.model.forward(ctx, self.cache, logits[row:row + nw] if nw else None)
+            for s, t in chunk_entries:
+                self.cache.advance(s, len(t))
+            row += nw
+        return logits
+
+    def _chunks(self, entries, want):
+        """Cut a long step into steps of at most max_step_tokens, in token order."""
+        cur_e, cur_w, room = [], [], self.max_step_tokens
+        for (slot, toks), w in zip(entries, want):
+            a = 0
+            while a < len(toks):
+                take = min(room, len(toks) - a)
+                cur_e.append((slot, toks[a:a + take]))
+                cur_w.append([x - a for x in w if a <= x < a + take])
+                a += take
+                room -= take
+                if room == 0:
+                    yield cur_e, cur_w
+                    cur_e, cur_w, room = [], [], self.max_step_tokens
+        if cur_e:
+            yield cur_e, cur_w
+
+    def _decode_step(self, entries, want):
+        """One token per sequence: replayed from a CUDA graph captured per batch size."""
+        B = len(entries)
+        logits = self._logits.get(B)
+        if logits is None:
+            logits = self._logits[B] = torch.empty((B, self.vocab_size), dtype=torch.float32, device=self.device)
+        ctx = self.planner.plan(entries, want)
+        graph = self._graphs.get(B)
+        if graph is None:
+            # First step of this size runs eagerly (it sizes the scratch buffers), then a capture
+            # of the same launches replaces it; the capture recomputes the same values.
+            self.model.forward(ctx, self.cache, logits)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, self.cache, logits)
+            self._graphs[B] = graph
+        else:
+            graph.replay()
+        for s, t in entries:
+            self.cache.advance(s, 1)
+        return logits
+
+    # ---- accounting for the roofline report
+    def weight_bytes(self) -> int:
+        return self.model.weight_bytes()
+
+    def kv_bytes_per_position(self) -> int:
+        return self.cache.bytes_per_position()

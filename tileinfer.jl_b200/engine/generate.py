@@ -1,0 +1,103 @@
+"""The generation loop above the step function.
+
+Requests (lists of token ids) are run in batches, one batch after another: the prompts of
+a batch, of unequal lengths, are prefilled in one step; every later step carries one
+token of each sequence that is still alive. A sequence ends on a stop token (which is not
+emitted) or when it has ``max_new_tokens`` tokens; it then leaves the batch and gives its
+slot and pages back. No request joins a batch that has started.
+
+Per sequence this is AntoineBut/TileInfer.jl's loop (src/engine/generate.jl:26-57): prefill,
+then sample -> stop check -> append -> budget check -> one-token step. Afterwards the cache
+held every token except the last sampled one, which never went through the model.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Sequence
+
+from ..sampling import DeviceSampler, SamplingParams, sequence_seed
+
+
+@dataclass
+class BatchPlan:
+    """Which requests run together; pure bookkeeping, testable without a device."""
+    batches: List[List[int]]
+
+
+def plan_batches(prompt_lengths: Sequence[int], max_new_tokens: int, max_seqs: int, max_tokens: int,
+                 page_size: int, max_context: int) -> BatchPlan:
+    """Requests in order, as many per batch as slots and pages allow when every sequence grows to
+    its budget (each rounded up to whole pages)."""
+    batches, cur, used = [], [], 0
+    for i, n in enumerate(prompt_lengths):
+        if n < 1:
+            raise ValueError(f"request {i} has no tokens")
+        total = n + max_new_tokens
+        if total > max_context:
+            raise ValueError(f"prompt + max_new_tokens = {total} exceeds the max context {max_context}")
+        need = -(-total // page_size) * page_size
+        if need > max_tokens:
+            raise ValueError(f"request {i} needs {need} cached positions; the cache holds {max_tokens}")
+        if cur and (len(cur) == max_seqs or used + need > max_tokens):
+            batches.append(cur)
+            cur, used = [], 0
+        cur.append(i)
+        used += need
+    if cur:
+        batches.append(cur)
+    return BatchPlan(batches)
+
+
+def finished(token: int, generated: int, max_new_tokens: int, stop_ids) -> str:
+    """What a sampled token means for its sequence: "stop" (a stop token: not emitted, sequence ends),
+    "last" (emitted, budget reached) or "go"."""
+    if token in stop_ids:
+        return "stop"
+    if generated + 1 >= max_new_tokens:
+        return "last"
+    return "go"
+
+
+def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 256,
+             sampling: SamplingParams = SamplingParams(), stop_ids: Optional[Sequence[int]] = None, seed: int = 0,
+             on_token: Optional[Callable[[int, int], None]] = None) -> List[List[int]]:
+    """New token ids of every request, without stop tokens. ``on_token(request, id)`` is called
+    for each new token. ``stop_ids`` defaults to the configuration's EOS ids; ``[]`` disables them."""
+    stop = set(engine.spec.eos_token_ids if stop_ids is None else stop_ids)
+    prompts = [list(p) for p in prompts]
+    results: List[List[int]] = [[] for _ in prompts]
+    if max_new_tokens <= 0:
+        return results
+    cache = engine.cache
+    plan = plan_batches([len(p) for p in prompts], max_new_tokens, cache.max_seqs, cache.max_tokens,
+                        cache.page_size, engine.max_context)
+    sampler = DeviceSampler(cache.max_seqs, engine.device)
+    for batch in plan.batches:
+        live = list(batch)                               # request indices, in batch order
+        slots = {r: engine.new_sequence() for r in live}
+        try:
+            sampler.reset([sequence_seed(seed, r) for r in live])
+            logits = engine.step([(slots[r], prompts[r]) for r in live])
+            while live:
+                tokens = sampler.sample(logits, sampling).tolist()
+                keep_rows, next_live, next_tokens = [], [], []
+                for row, (r, t) in enumerate(zip(live, tokens)):
+                    verdict = finished(t, len(results[r]), max_new_tokens, stop)
+                    if verdict != "stop":
+                        results[r].append(t)
+                        if on_token is not None:
+                            on_token(r, t)
+                    if verdict == "go":
+                        keep_rows.append(row); next_live.append(r); next_tokens.append(t)
+                    else:
+                        engine.free_sequence(slots.pop(r))
+                if not next_live:
+                    break
+                if len(next_live) != len(live):
+                    sampler.keep_rows(keep_rows)
+                live = next_live
+                logits = engine.step([(slots[r], [t]) for r, t in zip(live, next_tokens)])
+        finally:
+            for r in list(slots):
+                engine.free_sequence(slots.pop(r))
+    return results

@@ -1,0 +1,68 @@
+"""Loads the compiled kernel library and declares its C entry points.
+
+There is no fallback: if the library cannot be built or loaded, importing the kernels
+raises with the reason.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint, c_void_p
+
+from . import build as _build
+
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_P, _I, _L, _F, _U = c_void_p, c_int, c_longlong, c_float, c_uint
+_SIGNATURES = {
+    "ti_embed": [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    "ti_gather_rows": [_P, _P, _P, _I, _I, _I, _P],
+    "ti_xielu": [_P, _P, _L, _F, _F, _F, _F, _I, _P],
+    "ti_rmsnorm": [_P, _P, _P, _I, _I, _F, _I, _P],
+    "ti_add_rmsnorm": [_P, _P, _P, _I, _L, _P, _P, _I, _I, _F, _I, _P],
+    "ti_add": [_P, _P, _L, _I, _P],
+    "ti_attention_inputs": [_P, _L, _P, _P, _P, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ti_attention_plain": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ti_gemm_plain": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P],
+    "ti_argmax": [_P, _L, _I, _I, _P, _P],
+    "ti_sample": [_P, _L, _I, _I, _F, _I, _F, _P, _P, _P, _P],
+}
+
+
+def lib():
+    """The loaded library (built at the first call if the sources changed)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    try:
+        path = _build.build()
+        handle = ctypes.CDLL(path)
+    except Exception as e:                      # BuildError, OSError
+        raise KernelError(f"tileinfer_b200 cannot run without its CUDA kernel library: {e}") from e
+    handle.ti_last_error.restype = c_char_p
+    handle.ti_last_error.argtypes = []
+    handle.ti_sampling_uniform.restype = c_float
+    handle.ti_sampling_uniform.argtypes = [_U, _U]
+    for name, args in _SIGNATURES.items():
+        fn = getattr(handle, name)
+        fn.restype = c_int
+        fn.argtypes = args
+    _lib = handle
+    return handle
+
+
+def declare(name: str, argtypes, restype=c_int):
+    """Declare one more entry point (used by kernel files added later)."""
+    fn = getattr(lib(), name)
+    fn.restype = restype
+    fn.argtypes = argtypes
+    return fn
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what}: {lib().ti_last_error().decode()}")

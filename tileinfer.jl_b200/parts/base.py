@@ -1,0 +1,117 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A layer is a *block* (the arrangement) around a *mixer* (attention here), a *feed-forward*
+and two *norms*; a mixer may apply a *position encoding*. Each part is built from its own
+record of sizes and constants (``config.spec``), the tensors it declared, and the runtime;
+it never sees the model's configuration. Parts are looked up by the ``kind`` string of
+their record, so a new kind is added by registering a class here, from anywhere.
+
+Interfaces (duck-typed; the base classes document them):
+
+* ``Norm(spec, tensors, rt)``: ``forward(x, out)``; ``add_forward(x, delta, out, partials=None)``
+  does ``x += delta`` then ``out = norm(x)`` in one kernel.
+* ``PositionEncoding(spec, rt, max_positions)``: owns whatever table its kernels read.
+* ``Mixer(spec, tensors, rt, position)``: ``cache_request()`` says what per-sequence storage a
+  layer of this kind needs; ``forward(h, step, cache) -> delta`` mixes tokens of the same
+  sequence, reading and writing ``cache`` (the layer's view of its cache group).
+* ``FeedForward(spec, tensors, rt)``: ``forward(h, step) -> delta``, token by token.
+* ``Block(layer_spec, mixer, feed_forward, mixer_norm, feed_forward_norm)``:
+  ``forward(x, h, step, cache, next_norm, h_out)``.
+
+Every class also has ``tensors(spec) -> [TensorDecl]``: the checkpoint tensors it reads,
+with shapes, used by the loader's checks and by the random-weights mode.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..config.spec import TensorDecl
+
+
+@dataclass(frozen=True)
+class CacheRequest:
+    """Per-sequence storage a mixer needs for one layer.
+
+    ``kind == "paged_kv"``: keys and values of every position (or of the last ``window``),
+    ``kv_heads × head_dim`` each, in pages. ``kind == "state"``: a tensor of fixed ``shape``
+    and ``dtype`` per sequence, zeroed when a sequence starts.
+    """
+    kind: str
+    kv_heads: int = 0
+    head_dim: int = 0
+    window: Optional[int] = None
+    shape: Tuple[int, ...] = ()
+    dtype: Optional[torch.dtype] = None          # None: the model's element type
+
+    def group_key(self):
+        return (self.kind, self.kv_heads, self.head_dim, self.window, tuple(self.shape), self.dtype)
+
+
+class Part:
+    @classmethod
+    def tensors(cls, spec) -> List[TensorDecl]:
+        return []
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_forward(self, x, delta, out, partials=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    pass
+
+
+class Mixer(Part):
+    def cache_request(self) -> Optional[CacheRequest]:
+        return None
+
+    def forward(self, h: torch.Tensor, step, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, step) -> torch.Tensor:
+        raise NotImplementedError
+
+
+_REGISTRIES: Dict[str, Dict[str, Any]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}
+
+
+def _register(family: str, kind: str, cls):
+    _REGISTRIES[family][kind] = cls
+    return cls
+
+
+def register_mixer(kind: str, cls=None):
+    return _register("mixer", kind, cls) if cls is not None else (lambda c: _register("mixer", kind, c))
+
+
+def register_feed_forward(kind: str, cls=None):
+    return _register("feed_forward", kind, cls) if cls is not None else (lambda c: _register("feed_forward", kind, c))
+
+
+def register_norm(kind: str, cls=None):
+    return _register("norm", kind, cls) if cls is not None else (lambda c: _register("norm", kind, c))
+
+
+def register_position(kind: str, cls=None):
+    return _register("position", kind, cls) if cls is not None else (lambda c: _register("position", kind, c))
+
+
+def register_block(kind: str, cls=None):
+    return _register("block", kind, cls) if cls is not None else (lambda c: _register("block", kind, c))
+
+
+def lookup(family: str, kind: str):
+    try:
+        return _REGISTRIES[family][kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRIES[family])) or "none"
+        raise KeyError(f"no {family} part of kind \"{kind}\" is registered (registered: {known})") from None

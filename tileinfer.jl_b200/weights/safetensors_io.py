@@ -37,7 +37,8 @@ class SafetensorsFile:
         if size < 8:
             raise SafetensorsError(f"{path}: file of {size} bytes is too short for a safetensors header")
         self._file = open(path, "rb")
-        self._map = mmap.mmap(self._file.fileno(), 0, access=mmap.ACCESS_READ)
+        # Copy-on-write: tensors may view the map without ever changing the file.
+        self._map = mmap.mmap(self._file.fileno(), 0, access=mmap.ACCESS_COPY)
         (n,) = struct.unpack("<Q", self._map[:8])
         if 8 + n > size:
             raise SafetensorsError(f"{path}: header length {n} exceeds the file size {size} (truncated file?)")
