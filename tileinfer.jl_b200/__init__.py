@@ -7,3 +7,7 @@ step function and a generation loop (``engine``), sampling (``sampling``) and ha
 CUDA kernels (``csrc``, loaded by ``kernels``).
 """
 __version__ = "0.1.0"
+
+from .api import generate, generation_defaults, load_model            # noqa: E402
+from .engine import Engine                                            # noqa: E402
+from .sampling import SamplingParams                                  # noqa: E402
