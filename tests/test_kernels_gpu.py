@@ -1,0 +1,320 @@
+"""Each CUDA kernel alone against a plain PyTorch 32-bit reference of the same operation, at sizes
+other than the engine's (no powers of two, odd token counts), in float32 and bfloat16."""
+import math
+
+import pytest
+import torch
+
+import plain_apertus as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tileinfer_b200.kernels import ops
+    return ops
+
+
+def rnd(x, dtype):
+    return x if dtype == torch.float32 else x.to(dtype).float()
+
+
+def close(got, want, dtype, ulps=2.0, floor=None):
+    """Within `ulps` units in the last place of the storage type, floored at the output's RMS."""
+    got, want = got.float().cpu(), want.float().cpu()
+    eps = 2.0 ** -23 if dtype == torch.float32 else 2.0 ** -8
+    scale = torch.maximum(want.abs(), torch.full_like(want, floor if floor is not None else float(want.pow(2).mean().sqrt())))
+    err = ((got - want).abs() / (scale * eps)).max()
+    assert float(err) <= ulps, f"max error {float(err):.2f} ulps (allowed {ulps})"
+
+
+def dev(t, dtype=None):
+    return (t if dtype is None else t.to(dtype)).cuda().contiguous()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_and_gather(ops, dtype):
+    torch.manual_seed(0)
+    table = dev(torch.randn(301, 100), dtype)
+    ids = dev(torch.tensor([0, 300, 7, 7, 150], dtype=torch.int32))
+    out = torch.empty(5, 100, dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.embed(out, table, ids, status)
+    assert torch.equal(out, table[ids.long()]) and int(status) == 0
+    bad = dev(torch.tensor([3, 301], dtype=torch.int32))
+    ops.embed(out[:2], table, bad, status)
+    assert int(status) == 2                         # the out-of-range id is reported, not read
+    g = torch.empty(3, 100, dtype=dtype, device="cuda")
+    ops.gather_rows(g, out, dev(torch.tensor([4, 0, 2], dtype=torch.int32)))
+    assert torch.equal(g, out[[4, 0, 2]])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("size", [100, 2560, 4099])
+def test_rmsnorm_and_add_rmsnorm(ops, dtype, size):
+    torch.manual_seed(1)
+    x = rnd(torch.randn(7, size) * 3, dtype)
+    w = rnd(1 + 0.2 * torch.randn(size), dtype)
+    d = rnd(torch.randn(7, size), dtype)
+    want = plain.rmsnorm(x, w, 1e-5, dtype)
+    y = torch.empty(7, size, dtype=dtype, device="cuda")
+    ops.rmsnorm(y, dev(x, dtype), dev(w, dtype), 1e-5)
+    close(y, want, dtype, ulps=1.0 if dtype == torch.bfloat16 else 8.0)
+    xs = dev(x, dtype)
+    ops.add_rmsnorm(xs, dev(d, dtype), dev(w, dtype), y, 1e-5)
+    x2 = rnd(x + d, dtype)
+    assert torch.equal(xs.float().cpu(), x2)
+    close(y, plain.rmsnorm(x2, w, 1e-5, dtype), dtype, ulps=1.0 if dtype == torch.bfloat16 else 8.0)
+    parts = torch.randn(3, 7, size)
+    xs = dev(x, dtype)
+    ops.add_rmsnorm(xs, None, dev(w, dtype), y, 1e-5, partials=dev(parts))
+    x3 = rnd(x + rnd((parts[0] + parts[1]) + parts[2], dtype), dtype)
+    assert torch.equal(xs.float().cpu(), x3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_xielu_matches_the_stepwise_formula(ops, dtype):
+    torch.manual_seed(2)
+    x = rnd(torch.cat([torch.randn(5000) * 4, torch.tensor([0.0, -0.0, -1e-7, 1e-7, -30.0, 30.0])]), dtype)
+    for raw in ((18.125, 10.5), (0.3, -0.4)):       # the first layer's large alphas amplify input error
+        a = plain.xielu_scalars(torch.tensor(raw[0]), torch.tensor(raw[1]), torch.tensor(0.5), torch.tensor(-1e-6), dtype)
+        want = plain.xielu(x, a, dtype)
+        y = torch.empty_like(dev(x, dtype))
+        ops.xielu(y, dev(x, dtype), float(a.alpha_p), float(a.alpha_n), float(a.beta), float(a.eps))
+        if dtype == torch.bfloat16:
+            assert torch.equal(y.float().cpu(), want)          # every operation rounds: bit-identical
+        else:
+            # (expm1(x) - x)·an cancels for small |x|: one unit in the last place of expm1's result, which
+            # is what two correct 32-bit expm1 may differ by, is scaled by an. Bound the error by the
+            # sizes of the terms that are added, not by the (smaller) result.
+            terms = want.abs() + a.alpha_n * (torch.expm1(torch.minimum(x, a.eps)).abs() + x.abs()) + (a.beta * x).abs()
+            assert bool(((y.cpu() - want).abs() <= 4 * 2.0 ** -23 * terms).all())
+
+
+def paged(k, v, page_size, n_pages_total, perm_seed, dtype):
+    """Scatter contiguous k, v [len, nkv, D] of several sequences into pools with a shuffled page order.
+    Returns pools [pages, nkv, P, D] and the block table rows."""
+    g = torch.Generator().manual_seed(perm_seed)
+    order = torch.randperm(n_pages_total, generator=g).tolist()
+    nkv, D = k[0].shape[1], k[0].shape[2]
+    kp = torch.full((n_pages_total, nkv, page_size, D), float("nan"))
+    vp = torch.full((n_pages_total, nkv, page_size, D), float("nan"))
+    tables = []
+    for ks, vs in zip(k, v):
+        L = ks.shape[0]
+        pages = [order.pop() for _ in range(-(-L // page_size))]
+        tables.append(pages)
+        for p in range(L):
+            kp[pages[p // page_size], :, p % page_size] = ks[p]
+            vp[pages[p // page_size], :, p % page_size] = vs[p]
+    kp = torch.nan_to_num(kp, nan=7.0)              # unwritten places hold finite junk, as in a used pool
+    vp = torch.nan_to_num(vp, nan=-5.0)
+    width = max(len(t) for t in tables) + 2
+    table = torch.zeros(len(tables) + 1, width, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i + 1, :len(t)] = torch.tensor(t)      # slot 0 is left unused on purpose
+    return dev(kp, dtype), dev(vp, dtype), dev(table)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,D,page", [(6, 3, 32, 64), (5, 1, 48, 16), (8, 2, 128, 64)])
+def test_attention_inputs_and_plain_attention(ops, dtype, nq, nkv, D, page):
+    """q/k norm + rotation + cache write, then attention over the cache, for two sequences of which one
+    continues from cached positions; against the plain whole-sequence functions."""
+    torch.manual_seed(3)
+    cfg = plain.read_config({"vocab_size": 8, "hidden_size": 8, "intermediate_size": 8, "num_hidden_layers": 1,
+                             "num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": D, "rms_norm_eps": 1e-5,
+                             "rope_theta": 10000.0, "max_position_embeddings": 4096,
+                             "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 64,
+                                              "low_freq_factor": 1.0, "high_freq_factor": 4.0}})
+    lens = [150, 77]
+    qn, kn = rnd(1 + 0.2 * torch.randn(D), dtype), rnd(1 + 0.2 * torch.randn(D), dtype)
+    from tileinfer_b200.config.spec import Llama3RopeScaling, PositionSpec
+    from tileinfer_b200.parts import Runtime
+    from tileinfer_b200.parts.rope import RotaryEmbedding
+    rope = RotaryEmbedding(PositionSpec("rope", D, 10000.0, Llama3RopeScaling(8.0, 1.0, 4.0, 64), 4096), Runtime(dtype), 256)
+    qkvs = [rnd(torch.randn(L, (nq + 2 * nkv) * D), dtype) for L in lens]
+    n_pages = sum(-(-L // page) for L in lens) + 3
+    kp = torch.full((n_pages, nkv, page, D), 3.0, dtype=dtype, device="cuda")
+    vp = torch.full((n_pages, nkv, page, D), -2.0, dtype=dtype, device="cuda")
+    g = torch.Generator().manual_seed(5)
+    order = torch.randperm(n_pages, generator=g).tolist()
+    tables = [[order.pop() for _ in range(-(-L // page))] for L in lens]
+    table = torch.zeros(3, max(len(t) for t in tables) + 1, dtype=torch.int32)
+    for i, t in enumerate(tables):
+        table[i + 1, :len(t)] = torch.tensor(t)
+    table = table.cuda()
+    want_out = []
+    for qkv, L in zip(qkvs, lens):
+        q = qkv[:, :nq * D].view(L, nq, D); k = qkv[:, nq * D:(nq + nkv) * D].view(L, nkv, D); v = qkv[:, (nq + nkv) * D:].view(L, nkv, D)
+        cos, sin = plain.rope_tables(cfg, torch.arange(L), dtype)
+        q = plain.rope(plain.rmsnorm(q, qn, 1e-5, dtype), cos, sin, dtype)
+        k = plain.rope(plain.rmsnorm(k, kn, 1e-5, dtype), cos, sin, dtype)
+        want_out.append(plain.attention(q, k, v, 1 / math.sqrt(D), dtype))
+    # Step 1: the first 100 tokens of sequence 0 alone. Step 2: its other 50 together with all of sequence 1.
+    def run(entries):
+        toks = torch.cat([qkvs[s][a:b] for s, a, b in entries])
+        pos = torch.cat([torch.arange(a, b) for s, a, b in entries]).int()
+        slot = torch.cat([torch.full((b - a,), s + 1) for s, a, b in entries]).int()
+        smap = torch.tensor([tables[s][p // page] * page + p % page for s, a, b in entries for p in range(a, b)]).int()
+        n = toks.shape[0]
+        q_out = torch.empty(n, nq, D, dtype=dtype, device="cuda")
+        ops.attention_inputs(dev(toks, dtype), q_out, kp, vp, dev(qn, dtype), dev(kn, dtype), 1e-5, rope.cos_sin,
+                             pos.cuda(), smap.cuda(), nq, nkv, D, page)
+        out = torch.empty(n, nq * D, dtype=dtype, device="cuda")
+        ops.attention_plain(out, q_out, kp, vp, table, slot.cuda(), pos.cuda(), 1 / math.sqrt(D), nq, nkv, D, page)
+        return out.view(n, nq, D)
+    o1 = run([(0, 0, 100)])
+    o2 = run([(0, 100, 150), (1, 0, 77)])
+    tol = dict(ulps=3.0) if dtype == torch.bfloat16 else dict(ulps=64.0)
+    close(o1, want_out[0][:100], dtype, **tol)
+    close(o2[:50], want_out[0][100:], dtype, **tol)
+    close(o2[50:], want_out[1], dtype, **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,out,k", [(1, 100, 72), (37, 301, 120), (130, 96, 200), (5, 4099, 33)])
+def test_gemm_plain_and_epilogues(ops, dtype, n, out, k):
+    torch.manual_seed(4)
+    x, w = rnd(torch.randn(n, k), dtype), rnd(torch.randn(out, k) * k ** -0.5, dtype)
+    want = rnd((x.double() @ w.double().t()).float(), dtype)
+    y = torch.empty(n, out, dtype=dtype, device="cuda")
+    ops.gemm_plain(y, dev(x, dtype), dev(w, dtype))
+    if dtype == torch.bfloat16:
+        close(y, want, dtype, ulps=1.0)
+    else:
+        # The standard bound of a sequential 32-bit sum of k products: k · 2^-24 · sum |x_i w_i|.
+        bound = k * 2.0 ** -24 * (x.abs().double() @ w.abs().double().t()).float()
+        assert bool(((y.cpu() - want).abs() <= bound).all())
+    a = plain.xielu_scalars(torch.tensor(0.3), torch.tensor(-0.4), torch.tensor(0.5), torch.tensor(-1e-6), dtype)
+    ops.gemm_plain(y, dev(x, dtype), dev(w, dtype), ops.EPI_XIELU, (float(a.alpha_p), float(a.alpha_n), float(a.beta), float(a.eps)))
+    close(y, plain.xielu(want, a, dtype), dtype, ulps=2.0 if dtype == torch.bfloat16 else 32.0)
+    y32 = torch.empty(n, out, dtype=torch.float32, device="cuda")
+    ops.gemm_plain(y32, dev(x, dtype), dev(w, dtype), ops.EPI_F32_OUT)
+    close(y32, want, dtype, ulps=1.0 if dtype == torch.bfloat16 else 16.0)
+    # A row's result does not depend on how many rows share the launch.
+    y1 = torch.empty(1, out, dtype=dtype, device="cuda")
+    ops.gemm_plain(y1, dev(x[n - 1:], dtype), dev(w, dtype))
+    ops.gemm_plain(y, dev(x, dtype), dev(w, dtype))
+    assert torch.equal(y1[0], y[n - 1])
+
+
+@pytest.mark.parametrize("n", [1, 3, 8, 11, 16])
+@pytest.mark.parametrize("out,k", [(100, 72), (301, 120), (4096, 4096), (50, 2000)])
+def test_gemv_bf16(ops, n, out, k):
+    from tileinfer_b200.kernels.library import check, lib
+    torch.manual_seed(5)
+    x, w = rnd(torch.randn(n, k), torch.bfloat16), rnd(torch.randn(out, k) * k ** -0.5, torch.bfloat16)
+    want = (x.double() @ w.double().t()).float()
+    st = torch.cuda.current_stream().cuda_stream
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    y = torch.empty(n, out, dtype=torch.bfloat16, device="cuda")
+    check(lib().ti_gemv_bf16(y.data_ptr(), out, xd.data_ptr(), k, wd.data_ptr(), n, out, k, 1, 0, 0, 0, 0, 0, st), "gemv")
+    close(y, rnd(want, torch.bfloat16), torch.bfloat16, ulps=1.0)
+    for splits in (2, 3):
+        part = torch.full((splits, n, out), float("nan"), device="cuda")
+        check(lib().ti_gemv_bf16(part.data_ptr(), out, xd.data_ptr(), k, wd.data_ptr(), n, out, k, splits, 3, 0, 0, 0, 0, st), "gemv")
+        close(part.sum(0), want, torch.float32, ulps=64.0)
+    y32 = torch.empty(n, out, dtype=torch.float32, device="cuda")
+    check(lib().ti_gemv_bf16(y32.data_ptr(), out, xd.data_ptr(), k, wd.data_ptr(), n, out, k, 1, 2, 0, 0, 0, 0, st), "gemv")
+    close(y32, rnd(want, torch.bfloat16), torch.bfloat16, ulps=1.0)
+    a = plain.xielu_scalars(torch.tensor(18.125), torch.tensor(10.5), torch.tensor(0.5), torch.tensor(-1e-6), torch.bfloat16)
+    check(lib().ti_gemv_bf16(y.data_ptr(), out, xd.data_ptr(), k, wd.data_ptr(), n, out, k, 1, 1, float(a.alpha_p),
+                             float(a.alpha_n), float(a.beta), float(a.eps), st), "gemv")
+    got, ref = y.float().cpu(), plain.xielu(rnd(want, torch.bfloat16), a, torch.bfloat16)
+    # Where the product itself rounds to a neighbouring bfloat16 the activation amplifies it: compare on
+    # the kernel's own rounded product instead.
+    mine = plain.xielu(y32.cpu(), a, torch.bfloat16)
+    assert torch.equal(got, mine)
+    close(got, ref, torch.bfloat16, ulps=4.0)
+
+
+@pytest.mark.parametrize("nq,nkv,D", [(32, 8, 128), (6, 3, 32), (5, 1, 48), (4, 2, 16), (16, 1, 64), (12, 3, 96)])
+def test_attention_decode(ops, nq, nkv, D):
+    """Batch of sequences of very different lengths (one key, a page border, hundreds of keys), shuffled
+    pages, against exact 32-bit attention. One sequence has a far key made to stand out."""
+    from tileinfer_b200.kernels.library import check, lib
+    torch.manual_seed(6)
+    dtype = torch.bfloat16
+    lens = [1, 64, 65, 130, 777, 300]
+    B = len(lens)
+    ks = [rnd(torch.randn(L, nkv, D), dtype) for L in lens]
+    vs = [rnd(torch.randn(L, nkv, D), dtype) for L in lens]
+    q = rnd(torch.randn(B, nq, D), dtype)
+    # Sequence 4: key 3 (far from the end, in the first page) matches the query of head 0 strongly.
+    ks[4][3, 0] = rnd(q[4, 0] * 4.0, dtype)
+    n_pages = sum(-(-L // 64) for L in lens) + 4
+    kp, vp, table = paged(ks, vs, 64, n_pages, 9, dtype)
+    scale = 1 / math.sqrt(D)
+    want = torch.stack([plain.attention(q[b:b + 1], ks[b], vs[b], scale, torch.float32, start=lens[b] - 1)[0] for b in range(B)])
+    slots = dev(torch.arange(1, B + 1, dtype=torch.int32))
+    kv_lens = dev(torch.tensor(lens, dtype=torch.int32))
+    st = torch.cuda.current_stream().cuda_stream
+    for splits in (1, 2, 5, 32):
+        out = torch.full((B, nq, D), float("nan"), dtype=dtype, device="cuda")
+        ws_o = torch.full((B, nq, splits, D), float("nan"), device="cuda")
+        ws_ml = torch.full((B, nq, splits, 2), float("nan"), device="cuda")
+        check(lib().ti_attention_decode(out.data_ptr(), dev(q, dtype).data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(),
+                                        table.stride(0), slots.data_ptr(), kv_lens.data_ptr(), ws_o.data_ptr(), ws_ml.data_ptr(),
+                                        scale, B, nq, nkv, D, 64, splits, 0, st), "attention_decode")
+        close(out, want, dtype, ulps=5.0)
+    assert float(want[4, 0].sub(vs[4][3, 0]).abs().max()) < 0.2       # the far key really dominates its head
+
+
+def test_argmax_ties_go_to_the_smaller_id(ops):
+    torch.manual_seed(7)
+    logits = torch.randn(5, 1000)
+    logits[1, 700] = logits[1, 30] = 9.0
+    logits[2] = 0.0                                  # flat
+    logits[3, 999] = 50.0                            # all in the last element
+    logits[4] = -torch.arange(1000.0)
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(logits), out)
+    assert out.tolist() == [int(logits[0].argmax()), 30, 0, 999, 0]
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 5, 1.0), (0.7, 50, 0.9), (1.3, 0, 0.5), (1.0, 1, 1.0), (0.5, 200, 0.95)])
+def test_device_sampler_follows_the_host_rule(ops, temperature, top_k, top_p):
+    """Same token as the plain rule for the same (logits, settings, u), except where u × total or top_p
+    falls within 1e-5 of a boundary of the cumulative distribution (the reference's own filter,
+    test/ops/tile.jl:264-298)."""
+    torch.manual_seed(8)
+    V, rows = 1531, 24
+    logits = torch.randn(rows, V) * 2.5
+    logits[0] = 0.0                                   # flat
+    logits[1, 100] = logits[1, 900] = logits[1].max() + 1     # ties at the top
+    logits[2, :] = -30.0; logits[2, V - 1] = 5.0             # everything in the last token
+    logits[3, ::7] = logits[3, 0]                            # many ties across the k-th
+    seeds = [(1234567 * (r + 1)) & 0xFFFFFFFF for r in range(rows)]
+    from tileinfer_b200.sampling.device import _as_i32
+    sd = _as_i32(seeds).cuda()
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    checked = 0
+    for counter in (0, 1, 17):
+        ct = torch.full((rows,), counter, dtype=torch.int32, device="cuda")
+        ops.sample(dev(logits), out, temperature, top_k, top_p, sd, ct)
+        assert ct.tolist() == [counter + 1] * rows           # the kernel advances the counters
+        got = out.tolist()
+        for r in range(rows):
+            u = plain.sampling_uniform(seeds[r], counter)
+            ids, probs = plain.filtered_dist(logits[r], temperature, top_k, top_p)
+            cum, near = 0.0, False
+            for p in probs:
+                cum += p
+                if abs(cum - u) < 1e-5:
+                    near = True
+            if top_p < 1:
+                full_ids, full = plain.filtered_dist(logits[r], temperature, top_k, 1.0)
+                c = 0.0
+                for p in full:
+                    c += p
+                    if abs(c - top_p) < 1e-5:
+                        near = True
+            if near:
+                continue
+            assert got[r] == ids[plain.pick(probs, u)], f"row {r} counter {counter}"
+            checked += 1
+    assert checked > rows * 2

@@ -1,0 +1,308 @@
+// Decode attention over the paged cache in bfloat16: one new token per sequence, a batch
+// of sequences of any lengths, split over the keys (flash-decoding) so that the grid does
+// not depend on the lengths and a captured step stays valid.
+//
+// Grid (split, kv head, sequence). A block walks its share of the sequence's pages; a page
+// of one KV head is a dense [64, D] tile that is copied to shared memory with 16-byte
+// cp.async in a 3-stage pipeline (XOR-swizzled against bank conflicts). The query heads
+// that share the KV head are the 16 rows of the mma.sync tiles (GQA packing), so K and V
+// are read once for the whole group. Each of the 4 warps takes 16 keys of a 64-key tile
+// and keeps its own online-softmax state; the warps are merged in shared memory, the
+// splits by a small combine kernel. Scores, softmax and accumulators are 32-bit, P is
+// rounded to bfloat16 only as the operand of P·V, O is rounded once.
+//
+// AntoineBut/TileInfer.jl's counterpart: attention_decode_kernel + attention_combine_kernel
+// (src/ops/tile/attention.jl:185-245), GQA-packed split-KV with a fixed split count, exp2
+// with scale·log2e folded in (attention.jl:34-59), partial (acc, m, l) in a 32-bit workspace.
+#include "common.cuh"
+
+#define AD_PAGE 64
+#define AD_WARPS 4
+#define AD_THREADS (AD_WARPS * 32)
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// 16-byte chunk `c` of row `row` of a [rows, D] tile lands at chunk swz(row, c): the eight rows of
+// an ldmatrix then fall into different bank groups for every D that is a multiple of 16.
+template <int D> __device__ __forceinline__ int swz(int row, int c) {
+    constexpr int CPR = D / 8;
+    if (CPR % 8 == 0) return c ^ (row & 7);
+    if (CPR % 4 == 0) return c ^ ((row >> 1) & 3);
+    return c ^ ((row >> 2) & 1);
+}
+
+template <int D> struct DecodeSmem {
+    static constexpr int STAGES = D <= 128 ? 3 : 2;
+    static constexpr int TILE = AD_PAGE * D;                 // elements of one K or V tile
+    static constexpr size_t BYTES = (size_t)STAGES * 2 * TILE * sizeof(bf16);
+};
+
+template <int D>
+__device__ __forceinline__ void load_tile(bf16* dst, const bf16* __restrict__ src) {
+    constexpr int CPR = D / 8;
+    for (int c = threadIdx.x; c < AD_PAGE * CPR; c += AD_THREADS) {
+        const int row = c / CPR, cc = c % CPR;
+        cp_async16(smem_u32(dst + (row * CPR + swz<D>(row, cc)) * 8), src + (size_t)c * 8);
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
+    bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+    const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slots,
+    const int* __restrict__ kv_lens, float* __restrict__ ws_o, float* __restrict__ ws_ml, float scale_log2e, int nq,
+    int nkv, int splits, int window) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    typedef DecodeSmem<D> SM;
+    constexpr int CPR = D / 8, KS = D / 16, NT = D / 8;
+    bf16* tiles = reinterpret_cast<bf16*>(smem_raw);
+
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int group = nq / nkv;
+    const int kv_len = kv_lens[b];
+    const int first_key = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    const int t_begin = first_key / AD_PAGE, t_end = (kv_len + AD_PAGE - 1) / AD_PAGE;
+    const int n_tiles = t_end - t_begin;
+    const int my_lo = t_begin + (int)((long long)n_tiles * split / splits);
+    const int my_hi = t_begin + (int)((long long)n_tiles * (split + 1) / splits);
+    const int* table = block_table + (size_t)seq_slots[b] * table_stride;
+
+    // Query rows = the heads of this KV head's group, padded to 16.
+    unsigned qf[KS][4];
+    {
+        const bf16* q0 = q + ((size_t)b * nq + (size_t)kvh * group) * D;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int d = ks * 16 + 2 * t;
+            qf[ks][0] = g < group ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + d) : 0u;
+            qf[ks][1] = g + 8 < group ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + d) : 0u;
+            qf[ks][2] = g < group ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + d + 8) : 0u;
+            qf[ks][3] = g + 8 < group ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + d + 8) : 0u;
+        }
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;       // rows g and g + 8
+
+    auto issue = [&](int tile, int stage) {
+        if (tile < my_hi) {
+            const size_t base = ((size_t)table[tile] * nkv + kvh) * AD_PAGE * D;
+            load_tile<D>(tiles + (size_t)stage * 2 * SM::TILE, k_cache + base);
+            load_tile<D>(tiles + (size_t)stage * 2 * SM::TILE + SM::TILE, v_cache + base);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < SM::STAGES - 1; ++s) issue(my_lo + s, s);
+
+    for (int tile = my_lo; tile < my_hi; ++tile) {
+        const int stage = (tile - my_lo) % SM::STAGES;
+        cp_async_wait<SM::STAGES - 2>();
+        __syncthreads();
+        // The stage freed by the previous iteration is refilled while this one is used.
+        issue(tile + SM::STAGES - 1, (tile - my_lo + SM::STAGES - 1) % SM::STAGES);
+        const bf16* kt = tiles + (size_t)stage * 2 * SM::TILE;
+        const bf16* vt = kt + SM::TILE;
+
+        float s[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+        {
+            const int mat = lane >> 3, r = lane & 7;
+            const int row = warp * 16 + (mat >> 1) * 8 + r;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                unsigned kb[4];
+                ldmatrix_x4(kb, smem_u32(kt + (row * CPR + swz<D>(row, 2 * ks + (mat & 1))) * 8));
+                mma16816(s[0], qf[ks], kb[0], kb[1]);
+                mma16816(s[1], qf[ks], kb[2], kb[3]);
+            }
+        }
+        const int key0 = tile * AD_PAGE + warp * 16 + 2 * t;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int key = key0 + 8 * nt + j;
+                const bool ok = key < kv_len && key >= first_key;
+                s[nt][j] = ok ? s[nt][j] * scale_log2e : -INFINITY;
+                s[nt][2 + j] = ok ? s[nt][2 + j] * scale_log2e : -INFINITY;
+                mx0 = fmaxf(mx0, s[nt][j]);
+                mx1 = fmaxf(mx1, s[nt][2 + j]);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float b0 = n0 == -INFINITY ? 0.f : n0, b1 = n1 == -INFINITY ? 0.f : n1;
+        const float c0 = exp2f(m0 - b0), c1 = exp2f(m1 - b1);
+        m0 = n0; m1 = n1;
+        unsigned pf[4];
+        {
+            float p[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                p[nt][0] = exp2f(s[nt][0] - b0); p[nt][1] = exp2f(s[nt][1] - b0);
+                p[nt][2] = exp2f(s[nt][2] - b1); p[nt][3] = exp2f(s[nt][3] - b1);
+            }
+            l0 = l0 * c0 + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+            l1 = l1 * c1 + (p[0][2] + p[0][3] + p[1][2] + p[1][3]);
+            pf[0] = pack_bf16(p[0][0], p[0][1]); pf[1] = pack_bf16(p[0][2], p[0][3]);
+            pf[2] = pack_bf16(p[1][0], p[1][1]); pf[3] = pack_bf16(p[1][2], p[1][3]);
+        }
+#pragma unroll
+        for (int i = 0; i < NT; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+        {
+            const int mat = lane >> 3, r = lane & 7;
+            const int row = warp * 16 + (mat & 1) * 8 + r;
+#pragma unroll
+            for (int c = 0; c < NT; c += 2) {
+                unsigned vb[4];
+                ldmatrix_x4_trans(vb, smem_u32(vt + (row * CPR + swz<D>(row, c + (mat >> 1))) * 8));
+                mma16816(o[c], pf, vb[0], vb[1]);
+                mma16816(o[c + 1], pf, vb[2], vb[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // Merge the warps: [warp][row 0..15][D + 2] floats in the (now idle) tile memory.
+    float* mg = reinterpret_cast<float*>(smem_raw);
+    constexpr int RS = D + 2;
+    {
+        float* mine = mg + (size_t)warp * 16 * RS;
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+            mine[g * RS + i * 8 + 2 * t] = o[i][0]; mine[g * RS + i * 8 + 2 * t + 1] = o[i][1];
+            mine[(g + 8) * RS + i * 8 + 2 * t] = o[i][2]; mine[(g + 8) * RS + i * 8 + 2 * t + 1] = o[i][3];
+        }
+        if (t == 0) {
+            mine[g * RS + D] = m0; mine[g * RS + D + 1] = l0;
+            mine[(g + 8) * RS + D] = m1; mine[(g + 8) * RS + D + 1] = l1;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < group * D; e += AD_THREADS) {
+        const int row = e / D, d = e % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, mg[((size_t)w * 16 + row) * RS + D]);
+        const float base = M == -INFINITY ? 0.f : M;
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) {
+            const float* src = mg + ((size_t)w * 16 + row) * RS;
+            const float f = exp2f(src[D] - base);
+            L += src[D + 1] * f;
+            O += src[d] * f;
+        }
+        const int head = kvh * group + row;
+        if (splits == 1) {
+            out[((size_t)b * nq + head) * D + d] = __float2bfloat16_rn(O / L);
+        } else {
+            const size_t idx = ((size_t)b * nq + head) * splits + split;
+            ws_o[idx * D + d] = O;
+            if (d == 0) { ws_ml[idx * 2] = M; ws_ml[idx * 2 + 1] = L; }
+        }
+    }
+}
+
+__global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __restrict__ ws_o,
+                                         const float* __restrict__ ws_ml, int D, int splits) {
+    const size_t row = blockIdx.x;                          // (sequence, head)
+    const float* ml = ws_ml + row * splits * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) L += ml[2 * s + 1] * exp2f(ml[2 * s] - M);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float O = 0.f;
+        for (int s = 0; s < splits; ++s) O += ws_o[(row * splits + s) * D + d] * exp2f(ml[2 * s] - M);
+        out[row * D + d] = __float2bfloat16_rn(O / L);
+    }
+}
+
+template <int D>
+static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v, const int* table, int table_stride,
+                         const int* seq_slots, const int* kv_lens, float* ws_o, float* ws_ml, float scale, int B, int nq,
+                         int nkv, int splits, int window, cudaStream_t stream) {
+    static bool configured = false;
+    const size_t smem = DecodeSmem<D>::BYTES > (size_t)AD_WARPS * 16 * (D + 2) * 4 ? DecodeSmem<D>::BYTES
+                                                                                    : (size_t)AD_WARPS * 16 * (D + 2) * 4;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return ti_fail("attention_decode: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(splits, nkv, B);
+    attention_decode_kernel<D><<<grid, AD_THREADS, smem, stream>>>(out, q, k, v, table, table_stride, seq_slots, kv_lens,
+                                                                  ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv,
+                                                                  splits, window);
+    if (int rc = ti_check_launch("attention_decode")) return rc;
+    if (splits > 1) {
+        attention_combine_kernel<<<B * nq, D <= 64 ? 64 : 128, 0, stream>>>(out, ws_o, ws_ml, D, splits);
+        return ti_check_launch("attention_combine");
+    }
+    return 0;
+}
+
+// Returns 2 (and sets the error text) when the sizes are outside what this kernel takes, so
+// that the caller can fall back to the plain kernel; 1 on a CUDA error.
+extern "C" int ti_attention_decode(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                   const int* block_table, int table_stride, const int* seq_slots, const int* kv_lens,
+                                   float* ws_o, float* ws_ml, float scale, int B, int nq, int nkv, int D, int page_size,
+                                   int splits, int window, cudaStream_t stream) {
+    if (B == 0) return 0;
+    if (page_size != AD_PAGE || nq % nkv != 0 || nq / nkv > 16 || D % 16 != 0 || B > 65535 || nkv > 65535) {
+        ti_fail("attention_decode takes page size %d, at most 16 query heads per KV head and head sizes in steps of 16; "
+                "got page %d, %d/%d heads, head size %d", AD_PAGE, page_size, nq, nkv, D);
+        return 2;
+    }
+    TI_REQUIRE(splits >= 1 && (splits == 1 || (ws_o != nullptr && ws_ml != nullptr)), "attention_decode: splits need a workspace");
+#define AD_CASE(d)                                                                                                     \
+    case d:                                                                                                            \
+        return launch_decode<d>((bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,     \
+                                table_stride, seq_slots, kv_lens, ws_o, ws_ml, scale, B, nq, nkv, splits, window, stream);
+    switch (D) {
+        AD_CASE(16) AD_CASE(32) AD_CASE(48) AD_CASE(64) AD_CASE(80) AD_CASE(96) AD_CASE(112) AD_CASE(128) AD_CASE(256)
+        default:
+            ti_fail("attention_decode has no instance for head size %d", D);
+            return 2;
+    }
+#undef AD_CASE
+}

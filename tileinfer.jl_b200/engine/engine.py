@@ -57,6 +57,7 @@ class Engine:
                            share=self.model.cache_shares())
         self.max_step_tokens = int(max_step_tokens)
         self.planner = StepPlanner(self.cache, self.max_step_tokens, self.device)
+        self.planner.runtime = self.rt
         self.use_graphs = graphs
         self._graphs: Dict[int, object] = {}
         self._logits: Dict[int, torch.Tensor] = {}

@@ -45,6 +45,7 @@ class StepContext:
     is_decode: bool = False
     max_q_len: int = 0
     max_kv_len: int = 0
+    runtime: object = None              # scratch buffers for kernels that need a workspace
 
     def group(self, index: int) -> GroupMeta:
         return self.groups[index]
@@ -65,6 +66,7 @@ class StepPlanner:
         self.events = [None, None]
         self.turn = 0
         self.meta = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self.runtime = None
 
     def plan(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Sequence[Sequence[int]]) -> StepContext:
         """``entries``: (slot, new tokens) per sequence; ``want[i]``: offsets into entry i's tokens.
@@ -131,4 +133,5 @@ class StepPlanner:
             host_slots=slots, host_q_lens=q_lens, host_starts=starts,
             is_decode=all(q == 1 for q in q_lens), max_q_len=max(q_lens, default=0),
             max_kv_len=max((s + q for s, q in zip(starts, q_lens)), default=0),
+            runtime=self.runtime,
         )

@@ -1,12 +1,73 @@
-"""Choice of the bfloat16 kernels. Each function returns True when it ran a fast kernel
-and False when the sizes are outside what the fast kernels take, in which case the caller
-runs the plain CUDA-core kernel instead (same result up to rounding)."""
+"""Choice of the bfloat16 kernels. Each function returns None/False when the sizes are
+outside what the fast kernels take, in which case the caller runs the plain CUDA-core
+kernel instead (same result up to rounding); it never returns a wrong result."""
 from __future__ import annotations
 
+import torch
 
-def linear(lin, x, out, epilogue, act) -> bool:
-    return False
+from . import ops
+from .library import KernelError, check, lib
+
+GEMV_MAX_TOKENS = 16
+SM_COUNT = 148
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def gemv_splits(out_features: int, in_features: int) -> int:
+    """How many slices of k a decode product is cut into when its consumer can add partial sums:
+    products with few output rows and a long k otherwise leave most SMs idle."""
+    if out_features // 16 >= 1024:
+        return 1
+    return max(1, min(8, in_features // 2048))
+
+
+def linear(lin, x, out, epilogue, act, allow_partials=False):
+    """Returns the tensor that holds the result (``out``, or 32-bit partial sums [s, n, out] when
+    ``allow_partials``), or None when no fast kernel takes these sizes."""
+    n, k = x.shape
+    w = lin.weight
+    if x.dtype != torch.bfloat16 or n == 0:
+        return None
+    if n <= GEMV_MAX_TOKENS and k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        splits = gemv_splits(lin.out_features, k) if (allow_partials and epilogue == ops.EPI_NONE) else 1
+        if splits > 1:
+            partials = lin.rt.buffer("linear.partials", (splits, n, lin.out_features), torch.float32)
+            check(lib().ti_gemv_bf16(partials.data_ptr(), lin.out_features, x.data_ptr(), x.stride(0), w.data_ptr(), n,
+                                     lin.out_features, k, splits, 3, 0.0, 0.0, 0.0, 0.0, _stream()), "gemv_bf16")
+            return partials
+        check(lib().ti_gemv_bf16(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), n,
+                                 lin.out_features, k, 1, epilogue, act[0], act[1], act[2], act[3], _stream()), "gemv_bf16")
+        return out
+    return None
+
+
+def decode_splits(batch: int, kv_heads: int, max_context: int) -> int:
+    """Split count of decode attention: fixed by the batch size alone, so that a captured step
+    stays valid whatever the lengths are (the reference fixes it per model:
+    src/ops/tile/attention.jl:250-263)."""
+    want = -(-2 * SM_COUNT // max(1, batch * kv_heads))
+    return max(1, min(want, 32, -(-max_context // 64)))
 
 
 def attention(out, q, cache, meta, step, spec) -> bool:
+    if q.dtype != torch.bfloat16:
+        return False
+    if step.is_decode:
+        B = step.n_seqs
+        splits = decode_splits(B, spec.num_kv_heads, cache.k.shape[0] * 64)
+        rt_buffer = step.runtime.buffer
+        ws_o = rt_buffer("attention.ws_o", (B, spec.num_heads, splits, spec.head_dim), torch.float32)
+        ws_ml = rt_buffer("attention.ws_ml", (B, spec.num_heads, splits, 2), torch.float32)
+        rc = lib().ti_attention_decode(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                                       meta.block_table.data_ptr(), meta.block_table.stride(0),
+                                       step.seq_slots.data_ptr(), step.kv_lens.data_ptr(), ws_o.data_ptr(),
+                                       ws_ml.data_ptr(), spec.scale, B, spec.num_heads, spec.num_kv_heads,
+                                       spec.head_dim, cache.page_size, splits, spec.window or 0, _stream())
+        if rc == 2:
+            return False
+        check(rc, "attention_decode")
+        return True
     return False

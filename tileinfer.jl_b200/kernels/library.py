@@ -66,3 +66,9 @@ def declare(name: str, argtypes, restype=c_int):
 def check(rc: int, what: str) -> None:
     if rc != 0:
         raise KernelError(f"{what}: {lib().ti_last_error().decode()}")
+
+_SIGNATURES_FAST = {
+    "ti_gemv_bf16": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P],
+    "ti_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
+}
+_SIGNATURES.update(_SIGNATURES_FAST)

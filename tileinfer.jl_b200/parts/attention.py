@@ -74,5 +74,4 @@ class Attention(Mixer):
             ops.attention_plain(attn, q, cache.k, cache.v, meta.block_table, step.tok_slot, step.positions,
                                 s.scale, nq, nkv, D, cache.page_size, window=s.window or 0)
         proj = rt.buffer("mixer.delta", (n, s.hidden_size))
-        self.o.forward(attn, proj)
-        return proj
+        return self.o.forward(attn, proj, allow_partials=True)

@@ -8,8 +8,8 @@ their record, so a new kind is added by registering a class here, from anywhere.
 
 Interfaces (duck-typed; the base classes document them):
 
-* ``Norm(spec, tensors, rt)``: ``forward(x, out)``; ``add_forward(x, delta, out, partials=None)``
-  does ``x += delta`` then ``out = norm(x)`` in one kernel.
+* ``Norm(spec, tensors, rt)``: ``forward(x, out)``; ``add_forward(x, delta, out)`` does
+  ``x += delta`` then ``out = norm(x)`` in one kernel (``delta`` may be 32-bit partial sums [s, n, size]).
 * ``PositionEncoding(spec, rt, max_positions)``: owns whatever table its kernels read.
 * ``Mixer(spec, tensors, rt, position)``: ``cache_request()`` says what per-sequence storage a
   layer of this kind needs; ``forward(h, step, cache) -> delta`` mixes tokens of the same
@@ -60,7 +60,7 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
-    def add_forward(self, x, delta, out, partials=None):
+    def add_forward(self, x, delta, out):
         raise NotImplementedError
 
 

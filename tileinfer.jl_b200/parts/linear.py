@@ -16,10 +16,15 @@ class Linear:
         self.out_features, self.in_features = weight.shape
         self.name = name
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor, epilogue: int = ops.EPI_NONE, act=(0.0, 0.0, 0.0, 0.0)):
+    def forward(self, x: torch.Tensor, out: torch.Tensor, epilogue: int = ops.EPI_NONE, act=(0.0, 0.0, 0.0, 0.0),
+                allow_partials: bool = False):
+        """Writes y to ``out`` and returns it. With ``allow_partials`` the result may instead come back
+        as 32-bit partial sums ``[s, n, out]`` (a product split over k), for a consumer that adds them:
+        the norm's ``add_forward``."""
         if self.rt.fast:
             from ..kernels import fast
-            if fast.linear(self, x, out, epilogue, act):
-                return out
+            done = fast.linear(self, x, out, epilogue, act, allow_partials)
+            if done is not None:
+                return done
         ops.gemm_plain(out, x, self.weight, epilogue, act)
         return out

@@ -56,5 +56,4 @@ class XieluMLP(FeedForward):
         act = self.rt.buffer("feed_forward.act", (n, self.spec.intermediate_size))
         self.up.forward(h, act, ops.EPI_XIELU, self.act)
         out = self.rt.buffer("feed_forward.delta", (n, self.spec.hidden_size))
-        self.down.forward(act, out)
-        return out
+        return self.down.forward(act, out, allow_partials=True)

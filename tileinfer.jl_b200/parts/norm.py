@@ -23,6 +23,11 @@ class RMSNorm(Norm):
         ops.rmsnorm(out, x, self.weight, self.eps)
         return out
 
-    def add_forward(self, x, delta, out, partials=None):
-        ops.add_rmsnorm(x, delta, self.weight, out, self.eps, partials=partials)
+    def add_forward(self, x, delta, out):
+        """x += delta; out = norm(x). ``delta`` is [n, size] in the model's element type, or 32-bit
+        partial sums [s, n, size] of a product that was split over k."""
+        if delta.dim() == 3:
+            ops.add_rmsnorm(x, None, self.weight, out, self.eps, partials=delta)
+        else:
+            ops.add_rmsnorm(x, delta, self.weight, out, self.eps)
         return out
