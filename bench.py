@@ -1,0 +1,270 @@
+#!/usr/bin/env python3
+"""Benchmark of the serving step on ONE GPU: decode tokens per second of an Apertus-8B-shaped
+model with random weights (bfloat16), plus prefill throughput and roofline fractions.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+
+Prints one JSON line. A "step" is one decode step of the whole batch (default batch 8, every
+sequence after 1,023 cached positions, context 4,096). ``value`` is decoded tokens per second
+timed on the device with CUDA events around K graph-replayed steps; ``e2e`` is the same
+through the Python entry point (``tileinfer_b200.generate``), host token ids in and out.
+``prefill`` is one 2,048-token prompt; ``points`` holds decode at batch 1 and 64; ``roofline``
+relates the decode step's bytes (every weight once + the live cache) to the HBM peak.
+
+Timing: W >= 3 warm-up steps; every step reads all weights (16 GB), far more than the 126 MB
+L2, so no flush is needed between steps; SM clocks and throttle reasons are sampled with
+nvidia-smi during the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Apertus-8B sizes.
+APERTUS_8B = {
+    "architectures": ["ApertusForCausalLM"], "model_type": "apertus",
+    "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
+    "head_dim": 128, "intermediate_size": 21504, "vocab_size": 131072, "rope_theta": 12000000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 8192,
+                     "low_freq_factor": 1.0, "high_freq_factor": 4.0},
+    "rms_norm_eps": 1e-5, "qk_norm": True, "tie_word_embeddings": False, "hidden_act": "xielu",
+    "max_position_embeddings": 4096, "attention_bias": False, "mlp_bias": False,
+}
+CONTEXT = 4096
+CACHED = 1023           # positions every sequence holds before the timed decode steps
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                p = json.load(f)
+            return {k: float(p.get(k, FALLBACK_PEAKS[k])) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+        sm = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples if len(s) >= 6 for n, v in zip(names, s[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def fill_cache(engine, batch, cached, seed=0):
+    """``batch`` live sequences with ``cached`` positions each. The cache's contents do not change the
+    work of a decode step, so they are drawn at random instead of being prefilled."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    for grp in engine.cache.paged_groups:
+        for pool in (grp.k, grp.v):
+            for l in range(pool.shape[0]):
+                pool[l].copy_(torch.randn(pool[l].shape, generator=g, device="cuda", dtype=torch.float32).to(pool.dtype))
+    slots = [engine.new_sequence() for _ in range(batch)]
+    engine.cache.reserve([(s, cached) for s in slots])
+    for s in slots:
+        engine.cache.advance(s, cached)
+    return slots
+
+
+def release(engine, slots):
+    for s in slots:
+        engine.free_sequence(s)
+
+
+def time_decode(engine, batch, steps, warmup, vocab, count_launches=False):
+    """Device time of ``steps`` decode steps of ``batch`` sequences (greedy sampling on the device)."""
+    import torch
+    from tileinfer_b200.sampling import DeviceSampler, SamplingParams
+    slots = fill_cache(engine, batch, CACHED)
+    sampler = DeviceSampler(batch, engine.device)
+    gen = torch.Generator().manual_seed(1)
+    tokens = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+    launches = 0
+
+    def one(tokens):
+        logits = engine.step([(s, [t]) for s, t in zip(slots, tokens)])
+        return sampler.sample(logits, SamplingParams()).tolist()
+    for _ in range(max(warmup, 3)):
+        tokens = one(tokens)
+    if count_launches:
+        launches = engine.decode_launches(batch) + 1      # the captured step + the sampling kernel
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        tokens = one(tokens)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    kv_positions = batch * (CACHED + max(warmup, 3) + steps / 2)
+    release(engine, slots)
+    return ms / steps, kv_positions, launches
+
+
+def time_prefill(engine, tokens, vocab, reps=3):
+    import torch
+    gen = torch.Generator().manual_seed(2)
+    best = None
+    for r in range(reps + 1):
+        ids = torch.randint(0, vocab, (tokens,), generator=gen).tolist()
+        s = engine.new_sequence()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        engine.step([(s, ids)])
+        b.record()
+        torch.cuda.synchronize()
+        engine.free_sequence(s)
+        if r > 0:                                       # the first run sizes the scratch buffers
+            best = a.elapsed_time(b) if best is None else min(best, a.elapsed_time(b))
+    return best
+
+
+def time_e2e(engine, batch, steps, vocab):
+    """Decode rate through the public entry point: ``generate`` with host token ids in and out; the
+    clock runs from the first generated token of the batch to the last."""
+    import torch
+    import tileinfer_b200 as ti
+    gen = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, vocab, (CACHED,), generator=gen).tolist() for _ in range(batch)]
+    stamps = []
+
+    def on_token(request, token):
+        if request == 0:
+            torch.cuda.synchronize()
+            stamps.append(time.perf_counter())
+    ti.generate(engine, prompts, max_new_tokens=steps + 2, stop_ids=[], on_token=on_token)
+    span = stamps[-1] - stamps[1]                      # from the second token on, as the reference's stats line
+    n_steps = len(stamps) - 2
+    return batch * n_steps / span, n_steps
+
+
+def flops_prefill(cfg, n_layers, tokens):
+    H, I, D = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    per_layer = 2 * tokens * (H * (nq + 2 * nkv) * D + nq * D * H + 2 * H * I) + 4 * D * nq * tokens * (tokens + 1) // 2
+    return n_layers * per_layer + 2 * H * cfg["vocab_size"]
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0: all)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick checks)")
+    args = ap.parse_args(argv)
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "AntoineBut/TileInfer.jl is a Julia package (CUDA.jl + cuTile, sm_89): pip finds neither "
+                          "setup.py nor pyproject.toml, and neither Julia nor its packages are on this machine or the network"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures the single-GPU library; --gpus {args.gpus} is not supported (one GPU only)")
+        return 2
+
+    import torch
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.engine import Engine
+
+    cfg_dict = dict(APERTUS_8B)
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    cfg = ApertusConfig.from_dict(cfg_dict)
+    pk, pk_source = peaks()
+    batches = sorted({1, args.batch, 64} if not args.skip_points else {args.batch})
+    max_batch = max(batches)
+    engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=CONTEXT, max_seqs=max_batch,
+                           max_tokens=max(max_batch * 1280, PREFILL_TOKENS + 64), max_step_tokens=PREFILL_TOKENS)
+    vocab = cfg.vocab_size
+    weight_bytes = engine.weight_bytes() - engine.model.embed.numel() * engine.model.embed.element_size() \
+        if engine.spec.lm_head_name is not None else engine.weight_bytes()
+    kv_per_pos = engine.kv_bytes_per_position()
+
+    prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab)
+    points = {}
+    for b in batches:
+        if b == args.batch:
+            continue
+        ms, _, _ = time_decode(engine, b, max(8, args.steps // 2), args.warmup, vocab)
+        points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms_step, kv_positions, launches = time_decode(engine, args.batch, args.steps, args.warmup, vocab, count_launches=True)
+    clock_info = clocks.stop()
+    e2e_value, e2e_steps = time_e2e(engine, args.batch, min(args.steps, 64), vocab)
+
+    step_bytes = weight_bytes + kv_positions * kv_per_pos
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    pf_flops = flops_prefill(cfg_dict, cfg.num_hidden_layers, PREFILL_TOKENS)
+    value = args.batch * 1000.0 / ms_step
+    line = {
+        "metric": "decode tok/s (Apertus-8B bf16, batch 8, 1023 cached positions)", "value": round(value, 1),
+        "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights, uniform random token ids",
+        "config": {"model": "Apertus-8B shapes", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "none",
+                   "layers": cfg.num_hidden_layers, "layers_full": full_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "cached_positions": CACHED,
+                   "prefill_tokens": PREFILL_TOKENS, "rope_theta": cfg.rope_theta, "page_size": engine.cache.page_size,
+                   "l2": "step inputs (16 GB of weights) exceed L2", "peaks": pk_source},
+        "clocks": clock_info,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "steps": e2e_steps,
+                "h2d_bytes_per_step": engine.planner.last_upload_bytes, "d2h_bytes_per_step": 4 * args.batch},
+        "gpu_launches": launches * args.steps,
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(pf_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

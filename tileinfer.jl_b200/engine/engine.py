@@ -61,6 +61,7 @@ class Engine:
         self.use_graphs = graphs
         self._graphs: Dict[int, object] = {}
         self._logits: Dict[int, torch.Tensor] = {}
+        self._graph_launches: Dict[int, int] = {}
         self.vocab_size = self.spec.vocab_size
 
     # ---- construction
@@ -171,15 +172,22 @@ class Engine:
             # of the same launches replaces it; the capture recomputes the same values.
             self.model.forward(ctx, self.cache, logits)
             torch.cuda.current_stream().synchronize()
+            from ..kernels import library
+            before = library.launch_count
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 self.model.forward(ctx, self.cache, logits)
             self._graphs[B] = graph
+            self._graph_launches[B] = library.launch_count - before
         else:
             graph.replay()
         for s, t in entries:
             self.cache.advance(s, 1)
         return logits
+
+    def decode_launches(self, batch: int) -> int:
+        """Kernels in one captured decode step of ``batch`` sequences (0 before its first capture)."""
+        return self._graph_launches.get(batch, 0)
 
     # ---- accounting for the roofline report
     def weight_bytes(self) -> int:

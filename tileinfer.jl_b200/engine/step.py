@@ -67,6 +67,7 @@ class StepPlanner:
         self.turn = 0
         self.meta = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self.runtime = None
+        self.last_upload_bytes = 0
 
     def plan(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Sequence[Sequence[int]]) -> StepContext:
         """``entries``: (slot, new tokens) per sequence; ``want[i]``: offsets into entry i's tokens.
@@ -119,6 +120,7 @@ class StepPlanner:
             put(o_maps[gi], maps[gi])
         put(o_seq, slots); put(o_cu, cu); put(o_kv, [s + q for s, q in zip(starts, q_lens)]); put(o_want, want_l)
         self.meta[:off].copy_(st[:off], non_blocking=True)
+        self.last_upload_bytes = off * 4
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()

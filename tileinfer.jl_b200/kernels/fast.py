@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from . import ops
-from .library import KernelError, check, lib
+from .library import KernelError, add_launches, check, lib
 
 GEMV_MAX_TOKENS = 16
 SM_COUNT = 148
@@ -69,5 +69,7 @@ def attention(out, q, cache, meta, step, spec) -> bool:
         if rc == 2:
             return False
         check(rc, "attention_decode")
+        if splits > 1:
+            add_launches(1)                     # the combine kernel
         return True
     return False

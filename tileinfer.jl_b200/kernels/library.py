@@ -11,6 +11,27 @@ from ctypes import c_char_p, c_float, c_int, c_longlong, c_uint, c_void_p
 from . import build as _build
 
 _lib = None
+# Number of kernels launched through this module so far (a launch inside a CUDA-graph capture counts
+# once; its replays are counted by whoever replays the graph).
+launch_count = 0
+
+
+class _Counted:
+    """A C entry point that launches ``kernels`` kernels per call."""
+    __slots__ = ("fn", "kernels")
+
+    def __init__(self, fn, kernels=1):
+        self.fn, self.kernels = fn, kernels
+
+    def __call__(self, *args):
+        global launch_count
+        launch_count += self.kernels
+        return self.fn(*args)
+
+
+def add_launches(n: int) -> None:
+    global launch_count
+    launch_count += n
 
 
 class KernelError(RuntimeError):
@@ -47,17 +68,24 @@ def lib():
     handle.ti_last_error.argtypes = []
     handle.ti_sampling_uniform.restype = c_float
     handle.ti_sampling_uniform.argtypes = [_U, _U]
+    class _Lib:
+        pass
+    wrapped = _Lib()
+    wrapped.ti_last_error = handle.ti_last_error
+    wrapped.ti_sampling_uniform = handle.ti_sampling_uniform
+    wrapped.handle = handle
     for name, args in _SIGNATURES.items():
         fn = getattr(handle, name)
         fn.restype = c_int
         fn.argtypes = args
-    _lib = handle
-    return handle
+        setattr(wrapped, name, _Counted(fn))
+    _lib = wrapped
+    return wrapped
 
 
 def declare(name: str, argtypes, restype=c_int):
     """Declare one more entry point (used by kernel files added later)."""
-    fn = getattr(lib(), name)
+    fn = getattr(lib().handle, name)
     fn.restype = restype
     fn.argtypes = argtypes
     return fn
