@@ -24,6 +24,18 @@ int ti_check_launch(const char* what) {
     return 0;
 }
 
+// One row of `size` elements, 16 bytes per access where both ends allow it.
+template <typename T> __device__ __forceinline__ void copy_row(T* __restrict__ dst, const T* __restrict__ src, int size) {
+    constexpr int N = 16 / sizeof(T);
+    if (size % N == 0 && (((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < size / N; i += blockDim.x) d4[i] = s4[i];
+    } else {
+        for (int i = threadIdx.x; i < size; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
 // ---------------------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
@@ -36,7 +48,7 @@ __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, c
     }
     const T* row = table + (size_t)id * hidden;
     T* dst = out + (size_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = row[i];
+    copy_row(dst, row, hidden);
 }
 
 extern "C" int ti_embed(void* out, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
@@ -53,7 +65,7 @@ template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ idx, int size) {
     const T* row = x + (size_t)idx[blockIdx.x] * size;
     T* dst = out + (size_t)blockIdx.x * size;
-    for (int i = threadIdx.x; i < size; i += blockDim.x) dst[i] = row[i];
+    copy_row(dst, row, size);
 }
 
 extern "C" int ti_gather_rows(void* out, const void* x, const int* idx, int n, int size, int dtype, cudaStream_t stream) {
@@ -98,11 +110,125 @@ __global__ void rmsnorm_kernel(T* __restrict__ y, const T* __restrict__ x, const
         dst[i] = from_f32<T>(to_f32(w[i]) * rnd<T>(to_f32(row[i]) * inv));
 }
 
+// The same with 16-byte accesses: every thread owns up to MAXV vectors of its row, so all loads
+// of a row are in flight at once and the row is read from memory exactly once. Decode steps
+// are a handful of rows, where the latency of a serial loop would be the whole cost.
+#define RN_MAXV 4
+template <typename T>
+__global__ void rmsnorm_vec_kernel(T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ w, int size, float eps) {
+    __shared__ float scratch[33];
+    constexpr int N = Vec16<T>::N;
+    const T* row = x + (size_t)blockIdx.x * size;
+    T* dst = y + (size_t)blockIdx.x * size;
+    Vec16<T> v[RN_MAXV];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < RN_MAXV; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * N;
+        if (i < size) {
+            v[j].load(row + i);
+#pragma unroll
+            for (int e = 0; e < N; ++e) ss = fmaf(v[j].v[e], v[j].v[e], ss);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+#pragma unroll
+    for (int j = 0; j < RN_MAXV; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * N;
+        if (i < size) {
+            Vec16<T> wv;
+            wv.load(w + i);
+#pragma unroll
+            for (int e = 0; e < N; ++e) v[j].v[e] = wv.v[e] * rnd<T>(v[j].v[e] * inv);
+            v[j].store(dst + i);
+        }
+    }
+}
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
+                                       int n_partials, size_t partial_stride, const T* __restrict__ w, T* __restrict__ h,
+                                       int size, float eps) {
+    __shared__ float scratch[33];
+    constexpr int N = Vec16<T>::N;
+    T* row = x + (size_t)blockIdx.x * size;
+    T* dst = h + (size_t)blockIdx.x * size;
+    Vec16<T> v[RN_MAXV];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < RN_MAXV; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * N;
+        if (i < size) {
+            v[j].load(row + i);
+            float d[N];
+            if (partials != nullptr) {
+                const float* p = partials + (size_t)blockIdx.x * size + i;
+#pragma unroll
+                for (int e = 0; e < N; e += 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(p + e);
+                    d[e] = t.x; d[e + 1] = t.y; d[e + 2] = t.z; d[e + 3] = t.w;
+                }
+                for (int s = 1; s < n_partials; ++s) {
+#pragma unroll
+                    for (int e = 0; e < N; e += 4) {
+                        const float4 t = *reinterpret_cast<const float4*>(p + (size_t)s * partial_stride + e);
+                        d[e] += t.x; d[e + 1] += t.y; d[e + 2] += t.z; d[e + 3] += t.w;
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < N; ++e) d[e] = rnd<T>(d[e]);
+            } else {
+                Vec16<T> dv;
+                dv.load(delta + (size_t)blockIdx.x * size + i);
+#pragma unroll
+                for (int e = 0; e < N; ++e) d[e] = dv.v[e];
+            }
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                v[j].v[e] = rnd<T>(v[j].v[e] + d[e]);
+                ss = fmaf(v[j].v[e], v[j].v[e], ss);
+            }
+            v[j].store(row + i);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+#pragma unroll
+    for (int j = 0; j < RN_MAXV; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * N;
+        if (i < size) {
+            Vec16<T> wv;
+            wv.load(w + i);
+#pragma unroll
+            for (int e = 0; e < N; ++e) v[j].v[e] = wv.v[e] * rnd<T>(v[j].v[e] * inv);
+            v[j].store(dst + i);
+        }
+    }
+}
+
+// Threads for the vector kernels: enough that RN_MAXV vectors per thread cover the row; 0 if they cannot.
+template <typename T> static int vec_threads(int size) {
+    constexpr int N = Vec16<T>::N;
+    if (size % N) return 0;
+    const int vecs = size / N;
+    int threads = 64;
+    while (threads < 1024 && threads * RN_MAXV < vecs) threads *= 2;
+    if (threads * RN_MAXV < vecs) return 0;
+    while (threads > 64 && (threads / 2) >= vecs) threads /= 2;     // do not launch idle warps for small rows
+    return threads;
+}
+
 extern "C" int ti_rmsnorm(void* y, const void* x, const void* w, int n_rows, int size, float eps, int dtype, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     TI_REQUIRE(size > 0, "rmsnorm: size %d", size);
     const int threads = size >= 2048 ? 512 : size >= 512 ? 256 : 128;
-    TI_DISPATCH_DTYPE(dtype, (rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((T*)y, (const T*)x, (const T*)w, size, eps)));
+    const bool al = aligned16(y) && aligned16(x) && aligned16(w);
+    TI_DISPATCH_DTYPE(dtype, {
+        const int vt = al ? vec_threads<T>(size) : 0;
+        if (vt) rmsnorm_vec_kernel<T><<<n_rows, vt, 0, stream>>>((T*)y, (const T*)x, (const T*)w, size, eps);
+        else rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((T*)y, (const T*)x, (const T*)w, size, eps);
+    });
     return ti_check_launch("rmsnorm");
 }
 
@@ -145,8 +271,15 @@ extern "C" int ti_add_rmsnorm(void* x, const void* delta, const float* partials,
     TI_REQUIRE((delta != nullptr) != (partials != nullptr), "add_rmsnorm: give delta or partials, not both");
     TI_REQUIRE(partials == nullptr || n_partials >= 1, "add_rmsnorm: n_partials %d", n_partials);
     const int threads = size >= 2048 ? 512 : size >= 512 ? 256 : 128;
-    TI_DISPATCH_DTYPE(dtype, (add_rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>(
-                                 (T*)x, (const T*)delta, partials, n_partials, (size_t)partial_stride, (const T*)w, (T*)h, size, eps)));
+    const bool al = aligned16(x) && aligned16(w) && aligned16(h) && (delta == nullptr || aligned16(delta)) &&
+                    (partials == nullptr || (aligned16(partials) && partial_stride % 4 == 0));
+    TI_DISPATCH_DTYPE(dtype, {
+        const int vt = al ? vec_threads<T>(size) : 0;
+        if (vt) add_rmsnorm_vec_kernel<T><<<n_rows, vt, 0, stream>>>((T*)x, (const T*)delta, partials, n_partials,
+                                                                    (size_t)partial_stride, (const T*)w, (T*)h, size, eps);
+        else add_rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((T*)x, (const T*)delta, partials, n_partials,
+                                                                  (size_t)partial_stride, (const T*)w, (T*)h, size, eps);
+    });
     return ti_check_launch("add_rmsnorm");
 }
 

@@ -1,0 +1,415 @@
+// Tensor-core matrix product for sm_100a: y[n, out] = x[n, in] · W[out, in]ᵀ in bfloat16 with
+// 32-bit accumulation, written directly against the Blackwell instructions: TMA
+// (cp.async.bulk.tensor) stages both operands in 128-byte-swizzled shared memory,
+// tcgen05.mma (issued by one thread) accumulates in tensor memory, tcgen05.ld brings the
+// accumulator back for the epilogue.
+//
+// The WEIGHTS are the 128-row operand and the tokens the N operand (16 to 256 wide), so the
+// same kernel serves prefill (N = 256 tokens per tile) and decode batches (N = the batch),
+// where it is a weight-streaming kernel whose TMA pipeline keeps ~190 KB in flight per SM.
+// Both operands are K-major exactly as they lie in memory ([out, in] weights, [n, in]
+// activations): no transposes anywhere.
+//
+// One persistent block per SM walks output tiles (token tile fastest, so the blocks that
+// run together share weight tiles in L2). Warp 0 produces (TMA), warp 1 issues the MMAs,
+// warps 2-5 run the epilogue on one of two accumulator buffers in tensor memory while the
+// MMAs of the next tile fill the other. A product with few output tiles can be split over
+// k; the 32-bit partial sums [split, n, out] are added by the residual-add + RMSNorm kernel.
+// Epilogues: round to bfloat16; xIELU on the rounded sums; 32-bit logits; raw partials.
+//
+// Every wait on an mbarrier is bounded: after the limit the kernel records a code in
+// `status`, stops issuing work, frees its tensor memory and returns.
+//
+// AntoineBut/TileInfer.jl's counterpart is gemm_kernel (src/ops/tile/linear.jl:80-100): 32-bit
+// accumulation, one rounding to the storage type, grouped tile order for L2 reuse.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;            // weight rows per tile (tensor-memory lanes)
+constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int THREADS = 192;
+constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr unsigned WAIT_LIMIT = 1u << 22;
+
+enum { EPI_NONE = 0, EPI_XIELU = 1, EPI_F32 = 2, EPI_PARTIAL = 3 };
+
+struct Params {
+    int M, N, K;                   // out features, tokens, in features
+    int m_tiles, n_tiles, splits, k_blocks;
+    long long ldy;
+    int epilogue;
+    XieluParams act;
+    int* status;
+};
+
+template <int BN> struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES_FIT = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
+};
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait; false (and a code in *status) when the limit is reached.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
+    for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
+        unsigned done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    atomicCAS(status, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(unsigned dst_smem, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
+                                          unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The barrier gets one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
+__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
+    d |= (unsigned long long)1 << 16;                         // leading byte offset (unused with swizzle)
+    d |= (unsigned long long)(1024 >> 4) << 32;               // stride byte offset
+    d |= (unsigned long long)1 << 46;                         // version
+    d |= (unsigned long long)2 << 61;                         // SWIZZLE_128B
+    return d;
+}
+
+// kind::f16 instruction descriptor: D 32-bit, A and B bfloat16, both K-major, M = 128, N = BN.
+template <int BN> __device__ __forceinline__ constexpr unsigned instr_desc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+}
+
+struct TileIter {
+    int id, step, total;
+    int m, n, kb_lo, kb_hi, split;
+    __device__ bool next(const Params& p) {
+        if (id >= total) return false;
+        int t = id;
+        n = t % p.n_tiles; t /= p.n_tiles;
+        split = t % p.splits; m = t / p.splits;
+        kb_lo = (int)((long long)p.k_blocks * split / p.splits);
+        kb_hi = (int)((long long)p.k_blocks * (split + 1) / p.splits);
+        id += step;
+        return true;
+    }
+};
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                 const __grid_constant__ CUtensorMap map_x,
+                                                                 void* __restrict__ y, Params p) {
+    typedef Cfg<BN> C;
+    extern __shared__ unsigned char smem_dyn[];
+    // Swizzled tiles need 1024-byte alignment.
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    unsigned char* tiles = smem;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (size_t)C::STAGES * C::STAGE_BYTES);
+    // bars: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the tensor-memory base address.
+    const unsigned full0 = smem_addr(bars), empty0 = full0 + 8 * C::STAGES;
+    const unsigned accf0 = empty0 + 8 * C::STAGES, acce0 = accf0 + 16;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * C::STAGES + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_addr(tmem_slot), C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    TileIter it;
+    it.id = blockIdx.x; it.step = gridDim.x; it.total = p.m_tiles * p.n_tiles * p.splits;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer (TMA)
+        // The whole warp walks the loop (so that it reaches the final barrier converged); lane 0 issues.
+        int stage = 0;
+        unsigned phase = 0;
+        bool ok = true;
+        while (ok && it.next(p)) {
+            for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
+                ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1));
+                if (!ok) break;
+                if (lane == 0) {
+                    const unsigned bar = full0 + 8 * stage;
+                    mbar_expect_tx(bar, C::STAGE_BYTES);
+                    const unsigned a_dst = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_w, kb * BK, it.m * BM, bar);
+                    tma_load_2d(a_dst + C::A_BYTES, &map_x, kb * BK, it.n * BN, bar);
+                }
+                __syncwarp();
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (lane 0 issues)
+        int stage = 0;
+        unsigned phase = 0;
+        int local = 0;
+        bool ok = true;
+        while (ok && it.next(p)) {
+            const int acc = local & 1;
+            const unsigned acc_phase = (local >> 1) & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(acce0 + 8 * acc, acc_phase ^ 1, p.status, 2));
+            if (!ok) break;
+            tc_fence_after();
+            const unsigned d_tmem = tmem_base + (unsigned)(acc * BN);
+            for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
+                ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, p.status, 3));
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const unsigned a_addr = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
+                    const unsigned long long da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)      // 16 k = 32 bytes further along the swizzled row
+                        umma_bf16(d_tmem, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k),
+                                  instr_desc<BN>(), (kb > it.kb_lo || k > 0) ? 1u : 0u);
+                    umma_commit(empty0 + 8 * stage);       // the stage is free once these MMAs have read it
+                }
+                __syncwarp();
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) break;
+            if (lane == 0) umma_commit(accf0 + 8 * acc);   // the accumulator is complete
+            __syncwarp();
+            ++local;
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (4 warps)
+        const int quarter = warp & 3;                      // the tensor-memory lanes this warp may read
+        int local = 0;
+        bool ok = true;
+        while (ok && it.next(p)) {
+            const int acc = local & 1;
+            const unsigned acc_phase = (local >> 1) & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(accf0 + 8 * acc, acc_phase, p.status, 4));
+            if (!ok) break;
+            tc_fence_after();
+            const int m = it.m * BM + quarter * 32 + lane;
+            const int n0 = it.n * BN;
+            const int n_valid = min(BN, p.N - n0);
+            const unsigned t_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN);
+            constexpr int CH = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += CH) {
+                if (c >= n_valid) break;                   // uniform across the warp
+                unsigned r[32];
+                if (CH == 32) tmem_ld32(t_row + c, r); else tmem_ld16(t_row + c, r);
+                tmem_ld_wait();
+                if (m < p.M) {
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        const int n = n0 + c + j;
+                        if (c + j >= n_valid) break;
+                        const float s = __uint_as_float(r[j]);
+                        if (p.epilogue == EPI_PARTIAL) {
+                            ((float*)y)[((size_t)it.split * p.N + n) * p.ldy + m] = s;
+                        } else {
+                            float v = rnd<bf16>(s);
+                            if (p.epilogue == EPI_XIELU) v = xielu_value<bf16>(v, p.act);
+                            if (p.epilogue == EPI_F32) ((float*)y)[(size_t)n * p.ldy + m] = v;
+                            else ((bf16*)y)[(size_t)n * p.ldy + m] = __float2bfloat16_rn(v);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce0 + 8 * acc);
+            ++local;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols, ld; int box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols; h = h * 1000003u ^ (size_t)k.ld;
+        return h * 1000003u ^ (size_t)k.box_rows;
+    }
+};
+
+// A [rows, cols] bfloat16 matrix with row stride ld (elements), read in boxes of box_rows x 64
+// with the 128-byte swizzle; out-of-range elements read as zero.
+int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto hit = cache.find(key);
+    if (hit != cache.end()) { *out = hit->second; return 0; }
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return ti_fail("gemm: cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ti_fail("gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int BN>
+int launch(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM);
+        if (e != cudaSuccess) return ti_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    const int tiles = p.m_tiles * p.n_tiles * p.splits;
+    const int grid = tiles < sm_count ? tiles : sm_count;
+    gemm_tcgen05_kernel<BN><<<grid, THREADS, Cfg<BN>::SMEM, stream>>>(mw, mx, y, p);
+    return ti_check_launch("gemm_tcgen05");
+}
+
+}  // namespace
+
+// y: [n, ldy] bfloat16 (float32 for EPI_F32), or partial sums [splits, n, ldy] float32 for EPI_PARTIAL.
+// `status` is a device word that must be zero; a non-zero value afterwards means a wait ran out.
+// Returns 2 when the sizes are outside what the kernel takes (the caller then uses the plain product).
+extern "C" int ti_gemm_tcgen05(void* y, long long ldy, const void* x, long long ldx, const void* W, int n, int out, int in,
+                               int splits, int epilogue, float alpha_p, float alpha_n, float beta, float eps,
+                               int* status, cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (in % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)W & 15) || ((uintptr_t)x & 15) || in < 8) {
+        ti_fail("gemm_tcgen05 needs 16-byte aligned rows: in=%d, ldx=%lld", in, ldx);
+        return 2;
+    }
+    TI_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_tcgen05: unknown epilogue %d", epilogue);
+    TI_REQUIRE(status != nullptr, "gemm_tcgen05: status word missing");
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (sm_count <= 0) sm_count = 148;
+    }
+    const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
+    Params p;
+    p.M = out; p.N = n; p.K = in;
+    p.m_tiles = (out + BM - 1) / BM;
+    p.n_tiles = (n + bn - 1) / bn;
+    p.k_blocks = (in + BK - 1) / BK;
+    p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
+    TI_REQUIRE(p.splits == 1 || epilogue == EPI_PARTIAL, "gemm_tcgen05: a split product leaves partial sums");
+    p.ldy = ldy; p.epilogue = epilogue; p.act = XieluParams{alpha_p, alpha_n, beta, eps}; p.status = status;
+    CUtensorMap mw, mx;
+    if (int rc = tensor_map(&mw, W, out, in, in, BM)) return rc;
+    if (int rc = tensor_map(&mx, x, n, in, ldx, bn)) return rc;
+    switch (bn) {
+        case 256: return launch<256>(y, mw, mx, p, sm_count, stream);
+        case 128: return launch<128>(y, mw, mx, p, sm_count, stream);
+        case 64: return launch<64>(y, mw, mx, p, sm_count, stream);
+        default: return launch<32>(y, mw, mx, p, sm_count, stream);
+    }
+}
