@@ -82,13 +82,36 @@ __global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ in, size
     for (; i < count; i += stride) out[i] = from_f32<T>(xielu_value<T>(to_f32(in[i]), a));
 }
 
+template <typename T>
+__global__ void xielu_vec_kernel(T* __restrict__ out, const T* __restrict__ in, size_t vecs, XieluParams a) {
+    constexpr int N = Vec16<T>::N;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < vecs; i += stride) {
+        Vec16<T> v;
+        v.load(in + i * N);
+#pragma unroll
+        for (int e = 0; e < N; ++e) v.v[e] = xielu_value<T>(v.v[e], a);
+        v.store(out + i * N);
+    }
+}
+
 extern "C" int ti_xielu(void* out, const void* in, long long count, float alpha_p, float alpha_n, float beta, float eps,
                         int dtype, cudaStream_t stream) {
     if (count == 0) return 0;
     XieluParams a{alpha_p, alpha_n, beta, eps};
-    long long blocks = (count + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    TI_DISPATCH_DTYPE(dtype, (xielu_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, (const T*)in, (size_t)count, a)));
+    TI_DISPATCH_DTYPE(dtype, {
+        constexpr int N = Vec16<T>::N;
+        if (count % N == 0 && aligned16(out) && aligned16(in)) {
+            long long blocks = (count / N + 255) / 256;
+            if (blocks > 148 * 32) blocks = 148 * 32;
+            xielu_vec_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, (const T*)in, (size_t)(count / N), a);
+        } else {
+            long long blocks = (count + 255) / 256;
+            if (blocks > 148 * 16) blocks = 148 * 16;
+            xielu_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, (const T*)in, (size_t)count, a);
+        }
+    });
     return ti_check_launch("xielu");
 }
 

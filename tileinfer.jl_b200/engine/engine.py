@@ -62,6 +62,7 @@ class Engine:
         self._graphs: Dict[int, object] = {}
         self._logits: Dict[int, torch.Tensor] = {}
         self._graph_launches: Dict[int, int] = {}
+        self._graph_generation = -1
         self.vocab_size = self.spec.vocab_size
 
     # ---- construction
@@ -166,6 +167,10 @@ class Engine:
         if logits is None:
             logits = self._logits[B] = torch.empty((B, self.vocab_size), dtype=torch.float32, device=self.device)
         ctx = self.planner.plan(entries, want)
+        if self._graph_generation != self.rt.generation:
+            # A scratch buffer was reallocated since the graphs were captured (a larger step came
+            # through): they point at freed memory and are captured again.
+            self._graphs.clear()
         graph = self._graphs.get(B)
         if graph is None:
             # First step of this size runs eagerly (it sizes the scratch buffers), then a capture
@@ -178,6 +183,7 @@ class Engine:
             with torch.cuda.graph(graph):
                 self.model.forward(ctx, self.cache, logits)
             self._graphs[B] = graph
+            self._graph_generation = self.rt.generation
             self._graph_launches[B] = library.launch_count - before
         else:
             graph.replay()
@@ -188,6 +194,15 @@ class Engine:
     def decode_launches(self, batch: int) -> int:
         """Kernels in one captured decode step of ``batch`` sequences (0 before its first capture)."""
         return self._graph_launches.get(batch, 0)
+
+    def check_health(self) -> None:
+        """Raise if a kernel with bounded waits gave up since the last check (one small device read)."""
+        from ..kernels import fast
+        fast.check_status()
+        code = int(self.model.status.item())
+        if code:
+            self.model.status.zero_()
+            raise RuntimeError(f"token {code - 1} of a step had an id outside the vocabulary")
 
     # ---- accounting for the roofline report
     def weight_bytes(self) -> int:

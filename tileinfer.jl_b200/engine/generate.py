@@ -97,6 +97,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 256
                     sampler.keep_rows(keep_rows)
                 live = next_live
                 logits = engine.step([(slots[r], [t]) for r, t in zip(live, next_tokens)])
+            engine.check_health()
         finally:
             for r in list(slots):
                 engine.free_sequence(slots.pop(r))

@@ -41,7 +41,63 @@ def linear(lin, x, out, epilogue, act, allow_partials=False):
         check(lib().ti_gemv_bf16(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), n,
                                  lin.out_features, k, 1, epilogue, act[0], act[1], act[2], act[3], _stream()), "gemv_bf16")
         return out
+    if k % 8 == 0 and k >= 8 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+        return _tcgen05(lin, x, out, epilogue, act, allow_partials)
     return None
+
+
+_status = None
+TC_FUSED_XIELU_MAX_TOKENS = 64
+
+
+def status_word() -> torch.Tensor:
+    """Device word that kernels with bounded waits write a code to when a wait runs out."""
+    global _status
+    if _status is None:
+        _status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return _status
+
+
+def check_status() -> None:
+    """Raise if a kernel gave up on a wait since the last check (costs one device read)."""
+    if _status is not None:
+        code = int(_status.item())
+        if code:
+            _status.zero_()
+            raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}); its results are invalid")
+
+
+def tc_splits(out_features: int, in_features: int, n: int) -> int:
+    tiles = -(-out_features // 128) * -(-n // (256 if n > 128 else 128 if n > 64 else 64 if n > 32 else 32))
+    if n > 256 or tiles >= SM_COUNT:
+        return 1
+    return max(1, min(8, SM_COUNT // tiles, (in_features // 64) // 8))
+
+
+def _tcgen05(lin, x, out, epilogue, act, allow_partials):
+    n, k = x.shape
+    w = lin.weight
+    st = status_word()
+    splits = tc_splits(lin.out_features, k, n) if (allow_partials and epilogue == ops.EPI_NONE) else 1
+    if splits > 1:
+        partials = lin.rt.buffer("linear.partials", (splits, n, lin.out_features), torch.float32)
+        rc = lib().ti_gemm_tcgen05(partials.data_ptr(), lin.out_features, x.data_ptr(), x.stride(0), w.data_ptr(), n,
+                                   lin.out_features, k, splits, 3, 0.0, 0.0, 0.0, 0.0, st.data_ptr(), _stream())
+        if rc == 2:
+            return None
+        check(rc, "gemm_tcgen05")
+        return partials
+    # The activation rides in the epilogue only for small token counts: on a wide tile the four
+    # epilogue warps cannot hide expm1 behind the MMAs, and a separate pass over the output is cheaper.
+    fused = epilogue if (epilogue != ops.EPI_XIELU or n <= TC_FUSED_XIELU_MAX_TOKENS) else ops.EPI_NONE
+    rc = lib().ti_gemm_tcgen05(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), n,
+                               lin.out_features, k, 1, fused, act[0], act[1], act[2], act[3], st.data_ptr(), _stream())
+    if rc == 2:
+        return None
+    check(rc, "gemm_tcgen05")
+    if fused != epilogue:
+        ops.xielu(out, out, *act)
+    return out
 
 
 def decode_splits(batch: int, kv_heads: int, max_context: int) -> int:
@@ -72,4 +128,17 @@ def attention(out, q, cache, meta, step, spec) -> bool:
         if splits > 1:
             add_launches(1)                     # the combine kernel
         return True
-    return False
+    group = spec.num_heads // max(1, spec.num_kv_heads)
+    if group < 1 or group > 128 or spec.num_heads % spec.num_kv_heads:
+        return False
+    tokens_per_tile = 128 // group
+    total_tiles = sum(-(-n // tokens_per_tile) for n in step.host_q_lens)
+    rc = lib().ti_attention_prefill(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                                    meta.block_table.data_ptr(), meta.block_table.stride(0), step.seq_slots.data_ptr(),
+                                    step.cu_seqlens.data_ptr(), step.kv_lens.data_ptr(), step.n_seqs, total_tiles,
+                                    spec.scale, spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
+                                    spec.window or 0, _stream())
+    if rc == 2:
+        return False
+    check(rc, "attention_prefill")
+    return True

@@ -22,7 +22,9 @@ class Runtime:
         # "plain": only the simple CUDA-core kernels, also in bfloat16. The 32-bit path always uses them.
         self.kernels = "plain" if dtype == torch.float32 else kernels
         self._buffers: Dict[str, torch.Tensor] = {}
-        self.launches = 0
+        # Counts (re)allocations of scratch buffers: a captured CUDA graph holds the addresses of the
+        # buffers it was captured with and must be dropped when this number changes.
+        self.generation = 0
 
     @property
     def fast(self) -> bool:
@@ -39,6 +41,7 @@ class Runtime:
                 raise RuntimeError(f"scratch buffer {name} would be allocated during graph capture")
             buf = torch.empty(max(count, 1), dtype=dtype, device=self.device)
             self._buffers[name] = buf
+            self.generation += 1
         return buf[:count].view(*shape)
 
     def param(self, t: torch.Tensor, keep_dtype: bool = False) -> torch.Tensor:
