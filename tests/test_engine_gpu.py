@@ -1,0 +1,197 @@
+"""The engine in-process: long decoding, first tokens, generation through the entry point, graph
+replay against eager launches, stop tokens and slot reuse, errors that leave the cache untouched,
+and the reference's own goldens."""
+import os
+import tempfile
+
+import pytest
+import torch
+
+import helpers
+import plain_apertus as plain
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models():
+    """Model folders for the tiny configurations, and the plain implementation's view of them."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.weights import write_model_folder
+    with tempfile.TemporaryDirectory() as d:
+        out = {}
+        for name, cfg_dict, seed in (("A", helpers.TINY_A, 0), ("B", helpers.TINY_B, 1), ("C", helpers.TINY_C, 2)):
+            folder = write_model_folder(ApertusConfig.from_dict(cfg_dict), seed, os.path.join(d, name))
+            out[name] = (folder,) + plain.load_folder(folder)
+        out["fixture"] = (helpers.reference_fixture_folder(os.path.join(d, "fixture")),)
+        yield out
+
+
+def tolerance(dtype, ref):
+    scale = max(float(ref.abs().max()), 1.0)
+    return 2e-5 * scale if dtype == "float32" else 4 * float(ref.abs().max()) * 2.0 ** -8
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_long_decoding_and_first_tokens(models, name, dtype):
+    """A prompt of ONE token, then 200 tokens one by one (crossing page borders at 64, 128, 192, and for B
+    the rope-scaling threshold at 64), two sequences in the batch that start together."""
+    import tileinfer_b200 as ti
+    folder, pc, pw = models[name]
+    eng = ti.load_model(folder, dtype=dtype, max_context=256, max_seqs=2)
+    pdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    seqs = helpers.random_prompts(pc.vocab, [201, 150], 5)
+    refs = [plain.forward(pc, pw, s, pdt) for s in seqs]
+    slots = [eng.new_sequence(), eng.new_sequence()]
+    worst = 0.0
+    for pos in range(201):
+        live = [i for i in range(2) if pos < len(seqs[i])]
+        logits = eng.step([(slots[i], [seqs[i][pos]]) for i in live]).cpu()
+        for row, i in enumerate(live):
+            err = float((logits[row] - refs[i][pos]).abs().max())
+            assert err <= tolerance(dtype, refs[i]), f"{name} {dtype} sequence {i} position {pos}: {err}"
+            worst = max(worst, err)
+    eng.check_health()
+    assert eng.sequence_length(slots[0]) == 201 and eng.sequence_length(slots[1]) == 150
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_equals_eager_launches(models, dtype):
+    """Decode steps replayed from CUDA graphs (kernels launched as programmatic dependents, overlapping
+    their predecessors) give bit-identical logits to strictly serial eager launches, over 70 steps that
+    cross a page border, with a batch that shrinks."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.kernels import library
+    folder, pc, pw = models["B"]
+    prompts = helpers.random_prompts(pc.vocab, [3, 60, 17], 7)
+    feeds = helpers.random_prompts(pc.vocab, [70, 70, 70], 8)
+    runs = []
+    for graphs, pdl in ((True, True), (False, False)):
+        library.set_pdl(pdl)
+        try:
+            eng = ti.Engine.load(folder, dtype=dtype, max_context=256, max_seqs=4, max_tokens=1024, graphs=graphs)
+            slots = [eng.new_sequence() for _ in prompts]
+            out = [eng.step(list(zip(slots, prompts))).clone()]
+            for t in range(70):
+                live = [i for i in range(3) if not (i == 1 and t >= 40)]       # sequence 1 leaves after 40 steps
+                out.append(eng.step([(slots[i], [feeds[i][t]]) for i in live]).clone())
+            runs.append(out)
+            eng.check_health()
+        finally:
+            library.set_pdl(True)
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_reference_goldens_through_the_engine(models, dtype):
+    """The reference's own bars on its tiny checkpoint (test/model/forward.jl:138-146)."""
+    import tileinfer_b200 as ti
+    eng = ti.load_model(models["fixture"][0], dtype=dtype, max_context=128, max_seqs=1)
+    for case in helpers.reference_goldens().values():
+        ids, gold = case["ids"], case[dtype]
+        s = eng.new_sequence()
+        logits = eng.step([(s, ids)], [list(range(len(ids)))]).cpu()
+        eng.free_sequence(s)
+        for t in range(len(ids)):
+            top, want = torch.tensor(gold["topk_ids"][t]), torch.tensor(gold["topk_logits"][t])
+            err = float((logits[t][top] - want).abs().max())
+            if dtype == "float32":
+                assert err < 1e-4 and int(logits[t].argmax()) == gold["topk_ids"][t][0]
+            else:
+                assert err < 0.1
+                if want[0] - want[1] >= 0.25:
+                    assert int(logits[t].argmax()) == gold["topk_ids"][t][0]
+        if dtype == "float32":
+            assert ti.generate(eng, ids, max_new_tokens=24, stop_ids=[]) == gold["greedy"]
+
+
+def test_greedy_generation_through_the_entry_point(models):
+    """Batches of unequal prompts, more requests than slots (so batches follow one another and slots are
+    used again), against the plain implementation's greedy continuation; 32-bit decides exactly."""
+    import tileinfer_b200 as ti
+    for name, lengths in (("A", [5, 9, 13]), ("B", [1, 4, 17, 33, 70])):
+        folder, pc, pw = models[name]
+        prompts = helpers.random_prompts(pc.vocab, lengths, 11)
+        eng = ti.load_model(folder, dtype="float32", max_context=128, max_seqs=2)
+        got = ti.generate(eng, prompts, max_new_tokens=8, stop_ids=[])
+        assert got == [plain.generate(pc, pw, p, 8) for p in prompts]
+        assert eng.cache.slots.held == 0 and eng.cache.free_pages() == eng.cache.num_pages
+        assert ti.generate(eng, prompts[0], max_new_tokens=3, stop_ids=[]) == got[0][:3]      # one prompt in, one list out
+
+
+def test_sampled_generation_and_stop_tokens(models):
+    """Temperature / top-k / top-p sampling follows the plain rule token for token (32-bit logits, same
+    seeds); a stop token ends its sequence early, is not returned, and frees the slot."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.sampling import SamplingParams, sequence_seed
+    folder, pc, pw = models["B"]
+    prompts = helpers.random_prompts(pc.vocab, [1, 4, 17, 33, 70], 12)
+    eng = ti.load_model(folder, dtype="float32", max_context=128, max_seqs=8)
+    for params in (SamplingParams(temperature=0.8), SamplingParams(temperature=1.0, top_k=20, top_p=0.9)):
+        got = ti.generate(eng, prompts, max_new_tokens=12, sampling=params, stop_ids=[], seed=1234)
+        want = [plain.generate(pc, pw, p, 12, temperature=params.temperature, top_k=params.top_k, top_p=params.top_p,
+                               seed=sequence_seed(1234, i)) for i, p in enumerate(prompts)]
+        assert got == want
+    greedy = ti.generate(eng, prompts, max_new_tokens=12, stop_ids=[])
+    stop = greedy[2][5]                                   # a token that request 2 emits as its sixth
+    cut = ti.generate(eng, prompts, max_new_tokens=12, stop_ids=[stop])
+    for g, c in zip(greedy, cut):
+        assert c == (g[:g.index(stop)] if stop in g else g)
+    assert len(cut[2]) <= 5
+    assert eng.cache.slots.held == 0
+    seen = []
+    ti.generate(eng, prompts[:2], max_new_tokens=3, stop_ids=[], on_token=lambda r, t: seen.append((r, t)))
+    assert len(seen) == 6 and {r for r, _ in seen} == {0, 1}
+
+
+def test_errors_leave_the_cache_untouched(models):
+    import tileinfer_b200 as ti
+    from tileinfer_b200.cache import OutOfPagesError
+    folder, pc, pw = models["A"]
+    eng = ti.Engine.load(folder, dtype="float32", max_context=256, max_seqs=2, max_tokens=128)
+    a, b = eng.new_sequence(), eng.new_sequence()
+    eng.step([(a, [1] * 60)])
+    free = eng.cache.free_pages()
+    with pytest.raises(OutOfPagesError):
+        eng.step([(a, [1] * 10), (b, [2] * 70)])          # needs 1 + 2 pages, 1 free
+    assert eng.cache.free_pages() == free and eng.sequence_length(a) == 60 and eng.sequence_length(b) == 0
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.step([(a, [pc.vocab])])
+    with pytest.raises(ValueError, match="twice"):
+        eng.step([(a, [1]), (a, [2])])
+    with pytest.raises(ValueError, match="max context"):
+        eng.step([(b, [1] * 300)])
+    ref = plain.forward(pc, pw, [1] * 60 + [3], torch.float32)[-1]
+    assert float((eng.step([(a, [3])]).cpu()[0] - ref).abs().max()) < 2e-5     # still consistent afterwards
+
+
+def test_a_long_prompt_is_cut_into_chunks_without_changing_results(models):
+    import tileinfer_b200 as ti
+    folder, pc, pw = models["C"]
+    prompts = helpers.random_prompts(pc.vocab, [150, 40, 99], 13)
+    whole = ti.Engine.load(folder, dtype="float32", max_context=256, max_seqs=3, max_tokens=1024)
+    cut = ti.Engine.load(folder, dtype="float32", max_context=256, max_seqs=3, max_tokens=1024, max_step_tokens=64)
+    want = [[149], [0, 39], [50, 98]]
+    outs = []
+    for eng in (whole, cut):
+        slots = [eng.new_sequence() for _ in prompts]
+        outs.append(eng.step(list(zip(slots, prompts)), want).cpu())
+    assert torch.equal(outs[0], outs[1])
+    ref = torch.stack([plain.forward(pc, pw, p, torch.float32)[w] for p, ws in zip(prompts, want) for w in ws])
+    assert float((outs[0] - ref).abs().max()) < 2e-5
+
+
+def test_command_line(models, capsys):
+    from tileinfer_b200.cli import cli
+    folder, pc, pw = models["A"]
+    prompt = helpers.random_prompts(pc.vocab, [9], 14)[0]
+    assert cli(["run", folder, " ".join(map(str, prompt)), "--max-tokens", "6", "--dtype", "float32", "--max-context", "64",
+                "--stop-ids", ""]) == 0
+    out = capsys.readouterr()
+    assert [int(t) for t in out.out.split()] == plain.generate(pc, pw, prompt, 6)
+    assert "9 prompt tokens, 6 generated" in out.err
+    assert cli(["run", folder, "1 2", "--bogus", "1"]) == 1 and "unknown option --bogus" in capsys.readouterr().err
+    assert cli(["run", folder]) == 1 and cli(["frobnicate"]) == 1 and cli([]) == 1 and cli(["help"]) == 0

@@ -28,7 +28,7 @@ template <int D> struct DecodeSmem {
 };
 
 template <int D>
-__device__ __forceinline__ void load_tile(bf16* dst, const bf16* __restrict__ src) {
+__device__ __forceinline__ void load_tile(bf16* dst, const bf16* src) {
     constexpr int CPR = D / 8;
     for (int c = threadIdx.x; c < AD_PAGE * CPR; c += AD_THREADS) {
         const int row = c / CPR, cc = c % CPR;
@@ -38,9 +38,9 @@ __device__ __forceinline__ void load_tile(bf16* dst, const bf16* __restrict__ sr
 
 template <int D>
 __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
-    bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-    const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slots,
-    const int* __restrict__ kv_lens, float* __restrict__ ws_o, float* __restrict__ ws_ml, float scale_log2e, int nq,
+    bf16* __restrict__ out, const bf16* q, const bf16* k_cache, const bf16* v_cache,
+    const int* block_table, int table_stride, const int* seq_slots,
+    const int* kv_lens, float* __restrict__ ws_o, float* __restrict__ ws_ml, float scale_log2e, int nq,
     int nkv, int splits, int window) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     typedef DecodeSmem<D> SM;
@@ -50,6 +50,8 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int group = nq / nkv;
+    pdl_wait();
+    pdl_launch_dependents();
     const int kv_len = kv_lens[b];
     const int first_key = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int t_begin = first_key / AD_PAGE, t_end = (kv_len + AD_PAGE - 1) / AD_PAGE;
@@ -208,10 +210,12 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
     }
 }
 
-__global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __restrict__ ws_o,
-                                         const float* __restrict__ ws_ml, int D, int splits) {
+__global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws_o,
+                                         const float* ws_ml, int D, int splits) {
     const size_t row = blockIdx.x;                          // (sequence, head)
     const float* ml = ws_ml + row * splits * 2;
+    pdl_wait();
+    pdl_launch_dependents();
     float M = -INFINITY;
     for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
     float L = 0.f;
@@ -236,12 +240,12 @@ static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v,
         configured = true;
     }
     dim3 grid(splits, nkv, B);
-    attention_decode_kernel<D><<<grid, AD_THREADS, smem, stream>>>(out, q, k, v, table, table_stride, seq_slots, kv_lens,
+    ti_launch(attention_decode_kernel<D>, dim3(grid), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride, seq_slots, kv_lens,
                                                                   ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv,
                                                                   splits, window);
     if (int rc = ti_check_launch("attention_decode")) return rc;
     if (splits > 1) {
-        attention_combine_kernel<<<B * nq, D <= 64 ? 64 : 128, 0, stream>>>(out, ws_o, ws_ml, D, splits);
+        ti_launch(attention_combine_kernel, dim3(B * nq), dim3(D <= 64 ? 64 : 128), 0, stream, out, ws_o, ws_ml, D, splits);
         return ti_check_launch("attention_combine");
     }
     return 0;

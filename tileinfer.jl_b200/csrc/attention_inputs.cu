@@ -12,17 +12,19 @@
 #define AI_MAX_D 512
 
 template <typename T>
-__global__ void attention_inputs_kernel(const T* __restrict__ qkv, long long qkv_stride, T* __restrict__ q_out,
+__global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, T* __restrict__ q_out,
                                         T* __restrict__ k_cache, T* __restrict__ v_cache,
                                         const T* __restrict__ q_norm_w, const T* __restrict__ k_norm_w, float eps,
-                                        const float* __restrict__ cos_sin, const int* __restrict__ positions,
-                                        const int* __restrict__ slots, int nq, int nkv, int D, int page_size,
+                                        const float* __restrict__ cos_sin, const int* positions,
+                                        const int* slots, int nq, int nkv, int D, int page_size,
                                         int write_kv) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     const int head = blockIdx.y * AI_WARPS + warp;
+    pdl_wait();
+    pdl_launch_dependents();
     if (head >= heads_total) return;
     float* buf = smem + warp * D;
 
@@ -81,7 +83,7 @@ extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, void* 
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     dim3 grid(n_tokens, (heads_total + AI_WARPS - 1) / AI_WARPS);
     const size_t smem = (size_t)AI_WARPS * D * sizeof(float);
-    TI_DISPATCH_DTYPE(dtype, (attention_inputs_kernel<T><<<grid, AI_WARPS * 32, smem, stream>>>(
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(attention_inputs_kernel<T>, dim3(grid), dim3(AI_WARPS * 32), smem, stream, 
                                  (const T*)qkv, qkv_stride, (T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)q_norm_w,
                                  (const T*)k_norm_w, eps, cos_sin, positions, slots, nq, nkv, D, page_size, write_kv)));
     return ti_check_launch("attention_inputs");

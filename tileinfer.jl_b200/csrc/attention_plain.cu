@@ -19,10 +19,10 @@
 #define AP_MAX_D 512
 
 template <typename T>
-__global__ void attention_plain_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_cache,
-                                       const T* __restrict__ v_cache, const int* __restrict__ block_table,
-                                       int table_stride, const int* __restrict__ tok_slot,
-                                       const int* __restrict__ positions, float scale, int nq, int nkv, int D,
+__global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T* k_cache,
+                                       const T* v_cache, const int* block_table,
+                                       int table_stride, const int* tok_slot,
+                                       const int* positions, float scale, int nq, int nkv, int D,
                                        int page_size, int window) {
     extern __shared__ float smem[];
     float* qs = smem;                  // [D]
@@ -30,6 +30,8 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* __restrict_
     __shared__ float scratch[33];
     const int t = blockIdx.x, h = blockIdx.y;
     const int kvh = h / (nq / nkv);
+    pdl_wait();
+    pdl_launch_dependents();
     const int p = positions[t];
     const int* table = block_table + (size_t)tok_slot[t] * table_stride;
     const T* qrow = q + ((size_t)t * nq + h) * D;
@@ -100,7 +102,7 @@ extern "C" int ti_attention_plain(void* out, const void* q, const void* k_cache,
     TI_REQUIRE(nq <= 65535, "attention: too many heads (%d)", nq);
     dim3 grid(n_tokens, nq);
     const size_t smem = (size_t)(D + AP_CHUNK) * sizeof(float);
-    TI_DISPATCH_DTYPE(dtype, (attention_plain_kernel<T><<<grid, AP_THREADS, smem, stream>>>(
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(attention_plain_kernel<T>, dim3(grid), dim3(AP_THREADS), smem, stream, 
                                  (T*)out, (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, table_stride,
                                  tok_slot, positions, scale, nq, nkv, D, page_size, window)));
     return ti_check_launch("attention_plain");

@@ -34,7 +34,7 @@ template <int D> struct PrefillSmem {
 };
 
 template <int D>
-__device__ __forceinline__ void pf_load_tile(bf16* dst, const bf16* __restrict__ src) {
+__device__ __forceinline__ void pf_load_tile(bf16* dst, const bf16* src) {
     constexpr int CPR = D / 8;
     for (int c = threadIdx.x; c < PF_PAGE * CPR; c += PF_THREADS) {
         const int row = c / CPR, cc = c % CPR;
@@ -44,9 +44,9 @@ __device__ __forceinline__ void pf_load_tile(bf16* dst, const bf16* __restrict__
 
 template <int D>
 __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
-    bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-    const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_slots,
-    const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens, int n_seqs, float scale_log2e, int nq, int nkv,
+    bf16* __restrict__ out, const bf16* q, const bf16* k_cache, const bf16* v_cache,
+    const int* block_table, int table_stride, const int* seq_slots,
+    const int* cu_seqlens, const int* kv_lens, int n_seqs, float scale_log2e, int nq, int nkv,
     int tokens_per_tile, int window) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     typedef PrefillSmem<D> SM;
@@ -56,6 +56,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
     const int kvh = blockIdx.y;
     const int group = nq / nkv;
 
+    pdl_wait();
+    pdl_launch_dependents();
     // Which (sequence, query tile) is this block's?
     int b = 0, tile_in_seq = blockIdx.x;
     for (; b < n_seqs; ++b) {
@@ -224,7 +226,7 @@ static int launch_prefill(bf16* out, const bf16* q, const bf16* k, const bf16* v
         configured = true;
     }
     dim3 grid(total_tiles, nkv);
-    attention_prefill_kernel<D><<<grid, PF_THREADS, smem, stream>>>(out, q, k, v, table, table_stride, seq_slots, cu_seqlens,
+    ti_launch(attention_prefill_kernel<D>, dim3(grid), dim3(PF_THREADS), smem, stream, out, q, k, v, table, table_stride, seq_slots, cu_seqlens,
                                                                    kv_lens, n_seqs, scale * 1.4426950408889634f, nq, nkv,
                                                                    tokens_per_tile, window);
     return ti_check_launch("attention_prefill");

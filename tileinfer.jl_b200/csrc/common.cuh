@@ -19,6 +19,36 @@ extern "C" const char* ti_last_error();
 int ti_fail(const char* fmt, ...);
 int ti_check_launch(const char* what);
 
+// Programmatic dependent launch. Every kernel of a step lets its successor start launching at
+// once (`pdl_launch_dependents`) and waits for its predecessor's results only where it first
+// needs them (`pdl_wait`): the successor's blocks come up, and prefetch what does not depend on
+// the predecessor (weights), while the predecessor's last blocks drain. Both are no-ops for a
+// kernel that was launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Inputs that another kernel of the same step writes (activations, step metadata, the cache, work
+// spaces) are never declared `const __restrict__`: that would let the compiler read them through the
+// non-coherent path, which requires the data to be read-only for the kernel's whole lifetime, and a
+// kernel launched as a programmatic dependent starts before its predecessor has finished writing.
+extern int ti_pdl_enabled;
+
+// Launch with the programmatic-stream-serialization attribute when enabled.
+template <typename... KArgs, typename... Args>
+inline cudaError_t ti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ti_pdl_enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define TI_REQUIRE(cond, ...)                \
     do {                                     \
         if (!(cond)) return ti_fail(__VA_ARGS__); \

@@ -18,6 +18,11 @@ int ti_fail(const char* fmt, ...) {
     return 1;
 }
 
+int ti_pdl_enabled = 1;
+
+// Switch programmatic dependent launch on or off for every later launch (default on).
+extern "C" void ti_set_pdl(int enabled) { ti_pdl_enabled = enabled ? 1 : 0; }
+
 int ti_check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return ti_fail("%s: %s", what, cudaGetErrorString(e));
@@ -25,7 +30,7 @@ int ti_check_launch(const char* what) {
 }
 
 // One row of `size` elements, 16 bytes per access where both ends allow it.
-template <typename T> __device__ __forceinline__ void copy_row(T* __restrict__ dst, const T* __restrict__ src, int size) {
+template <typename T> __device__ __forceinline__ void copy_row(T* dst, const T* src, int size) {
     constexpr int N = 16 / sizeof(T);
     if (size % N == 0 && (((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
         const uint4* s4 = reinterpret_cast<const uint4*>(src);
@@ -38,9 +43,11 @@ template <typename T> __device__ __forceinline__ void copy_row(T* __restrict__ d
 
 // ---------------------------------------------------------------------------- embedding
 template <typename T>
-__global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
+__global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* ids,
                              int hidden, int vocab, int* __restrict__ status) {
     const int t = blockIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
     int id = ids[t];
     if (id < 0 || id >= vocab) {            // never read outside the table; report instead
         if (threadIdx.x == 0) atomicExch(status, 1 + t);
@@ -56,13 +63,15 @@ extern "C" int ti_embed(void* out, const void* table, const int* ids, int n_toke
     if (n_tokens == 0) return 0;
     TI_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embed: bad sizes n=%d hidden=%d vocab=%d", n_tokens, hidden, vocab);
     const int threads = hidden >= 1024 ? 256 : 128;
-    TI_DISPATCH_DTYPE(dtype, (embed_kernel<T><<<n_tokens, threads, 0, stream>>>((T*)out, (const T*)table, ids, hidden, vocab, status)));
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(embed_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, (T*)out, (const T*)table, ids, hidden, vocab, status)));
     return ti_check_launch("embed");
 }
 
 // Rows idx[i] of x [*, size] to out [n, size] (the positions whose logits are wanted).
 template <typename T>
-__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ idx, int size) {
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* x, const int* idx, int size) {
+    pdl_wait();
+    pdl_launch_dependents();
     const T* row = x + (size_t)idx[blockIdx.x] * size;
     T* dst = out + (size_t)blockIdx.x * size;
     copy_row(dst, row, size);
@@ -70,23 +79,27 @@ __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x,
 
 extern "C" int ti_gather_rows(void* out, const void* x, const int* idx, int n, int size, int dtype, cudaStream_t stream) {
     if (n == 0) return 0;
-    TI_DISPATCH_DTYPE(dtype, (gather_rows_kernel<T><<<n, 128, 0, stream>>>((T*)out, (const T*)x, idx, size)));
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(gather_rows_kernel<T>, dim3(n), dim3(128), 0, stream, (T*)out, (const T*)x, idx, size)));
     return ti_check_launch("gather_rows");
 }
 
 // ---------------------------------------------------------------------------- xIELU
 template <typename T>
-__global__ void xielu_kernel(T* __restrict__ out, const T* __restrict__ in, size_t count, XieluParams a) {
+__global__ void xielu_kernel(T* out, const T* in, size_t count, XieluParams a) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_wait();
+    pdl_launch_dependents();
     for (; i < count; i += stride) out[i] = from_f32<T>(xielu_value<T>(to_f32(in[i]), a));
 }
 
 template <typename T>
-__global__ void xielu_vec_kernel(T* __restrict__ out, const T* __restrict__ in, size_t vecs, XieluParams a) {
+__global__ void xielu_vec_kernel(T* out, const T* in, size_t vecs, XieluParams a) {
     constexpr int N = Vec16<T>::N;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_wait();
+    pdl_launch_dependents();
     for (; i < vecs; i += stride) {
         Vec16<T> v;
         v.load(in + i * N);
@@ -105,11 +118,11 @@ extern "C" int ti_xielu(void* out, const void* in, long long count, float alpha_
         if (count % N == 0 && aligned16(out) && aligned16(in)) {
             long long blocks = (count / N + 255) / 256;
             if (blocks > 148 * 32) blocks = 148 * 32;
-            xielu_vec_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, (const T*)in, (size_t)(count / N), a);
+            ti_launch(xielu_vec_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)out, (const T*)in, (size_t)(count / N), a);
         } else {
             long long blocks = (count + 255) / 256;
             if (blocks > 148 * 16) blocks = 148 * 16;
-            xielu_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)out, (const T*)in, (size_t)count, a);
+            ti_launch(xielu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)out, (const T*)in, (size_t)count, a);
         }
     });
     return ti_check_launch("xielu");
@@ -118,11 +131,13 @@ extern "C" int ti_xielu(void* out, const void* in, long long count, float alpha_
 // ---------------------------------------------------------------------------- RMSNorm
 // One block per row. y = rnd(w * rnd(x * inv_rms)), inv_rms = 1/sqrt(mean(x^2) + eps) in 32-bit.
 template <typename T>
-__global__ void rmsnorm_kernel(T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ w, int size, float eps) {
+__global__ void rmsnorm_kernel(T* y, const T* x, const T* __restrict__ w, int size, float eps) {
     __shared__ float scratch[33];
     const T* row = x + (size_t)blockIdx.x * size;
     T* dst = y + (size_t)blockIdx.x * size;
     float ss = 0.f;
+    pdl_wait();
+    pdl_launch_dependents();
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
         const float v = to_f32(row[i]);
         ss = fmaf(v, v, ss);
@@ -138,13 +153,15 @@ __global__ void rmsnorm_kernel(T* __restrict__ y, const T* __restrict__ x, const
 // are a handful of rows, where the latency of a serial loop would be the whole cost.
 #define RN_MAXV 4
 template <typename T>
-__global__ void rmsnorm_vec_kernel(T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ w, int size, float eps) {
+__global__ void rmsnorm_vec_kernel(T* y, const T* x, const T* __restrict__ w, int size, float eps) {
     __shared__ float scratch[33];
     constexpr int N = Vec16<T>::N;
     const T* row = x + (size_t)blockIdx.x * size;
     T* dst = y + (size_t)blockIdx.x * size;
     Vec16<T> v[RN_MAXV];
     float ss = 0.f;
+    pdl_wait();
+    pdl_launch_dependents();
 #pragma unroll
     for (int j = 0; j < RN_MAXV; ++j) {
         const int i = (threadIdx.x + j * blockDim.x) * N;
@@ -170,7 +187,7 @@ __global__ void rmsnorm_vec_kernel(T* __restrict__ y, const T* __restrict__ x, c
 }
 
 template <typename T>
-__global__ void add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
+__global__ void add_rmsnorm_vec_kernel(T* x, const T* delta, const float* partials,
                                        int n_partials, size_t partial_stride, const T* __restrict__ w, T* __restrict__ h,
                                        int size, float eps) {
     __shared__ float scratch[33];
@@ -179,6 +196,8 @@ __global__ void add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ 
     T* dst = h + (size_t)blockIdx.x * size;
     Vec16<T> v[RN_MAXV];
     float ss = 0.f;
+    pdl_wait();
+    pdl_launch_dependents();
 #pragma unroll
     for (int j = 0; j < RN_MAXV; ++j) {
         const int i = (threadIdx.x + j * blockDim.x) * N;
@@ -249,8 +268,8 @@ extern "C" int ti_rmsnorm(void* y, const void* x, const void* w, int n_rows, int
     const bool al = aligned16(y) && aligned16(x) && aligned16(w);
     TI_DISPATCH_DTYPE(dtype, {
         const int vt = al ? vec_threads<T>(size) : 0;
-        if (vt) rmsnorm_vec_kernel<T><<<n_rows, vt, 0, stream>>>((T*)y, (const T*)x, (const T*)w, size, eps);
-        else rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((T*)y, (const T*)x, (const T*)w, size, eps);
+        if (vt) ti_launch(rmsnorm_vec_kernel<T>, dim3(n_rows), dim3(vt), 0, stream, (T*)y, (const T*)x, (const T*)w, size, eps);
+        else ti_launch(rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), 0, stream, (T*)y, (const T*)x, (const T*)w, size, eps);
     });
     return ti_check_launch("rmsnorm");
 }
@@ -259,13 +278,15 @@ extern "C" int ti_rmsnorm(void* y, const void* x, const void* w, int n_rows, int
 // a fixed order, of `n_partials` 32-bit partial products [s][n_rows][size] (a split-K
 // matrix product), rounded to the storage type first like any product's output.
 template <typename T>
-__global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
+__global__ void add_rmsnorm_kernel(T* x, const T* delta, const float* partials,
                                    int n_partials, size_t partial_stride, const T* __restrict__ w, T* __restrict__ h,
                                    int size, float eps) {
     __shared__ float scratch[33];
     T* row = x + (size_t)blockIdx.x * size;
     T* dst = h + (size_t)blockIdx.x * size;
     float ss = 0.f;
+    pdl_wait();
+    pdl_launch_dependents();
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
         float d;
         if (partials != nullptr) {
@@ -298,9 +319,9 @@ extern "C" int ti_add_rmsnorm(void* x, const void* delta, const float* partials,
                     (partials == nullptr || (aligned16(partials) && partial_stride % 4 == 0));
     TI_DISPATCH_DTYPE(dtype, {
         const int vt = al ? vec_threads<T>(size) : 0;
-        if (vt) add_rmsnorm_vec_kernel<T><<<n_rows, vt, 0, stream>>>((T*)x, (const T*)delta, partials, n_partials,
+        if (vt) ti_launch(add_rmsnorm_vec_kernel<T>, dim3(n_rows), dim3(vt), 0, stream, (T*)x, (const T*)delta, partials, n_partials,
                                                                     (size_t)partial_stride, (const T*)w, (T*)h, size, eps);
-        else add_rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((T*)x, (const T*)delta, partials, n_partials,
+        else ti_launch(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), 0, stream, (T*)x, (const T*)delta, partials, n_partials,
                                                                   (size_t)partial_stride, (const T*)w, (T*)h, size, eps);
     });
     return ti_check_launch("add_rmsnorm");
@@ -308,9 +329,11 @@ extern "C" int ti_add_rmsnorm(void* x, const void* delta, const float* partials,
 
 // Plain residual add for blocks whose next norm is not fused: x <- rnd(x + delta).
 template <typename T>
-__global__ void add_kernel(T* __restrict__ x, const T* __restrict__ delta, size_t count) {
+__global__ void add_kernel(T* x, const T* delta, size_t count) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    pdl_wait();
+    pdl_launch_dependents();
     for (; i < count; i += stride) x[i] = from_f32<T>(to_f32(x[i]) + to_f32(delta[i]));
 }
 
@@ -318,6 +341,6 @@ extern "C" int ti_add(void* x, const void* delta, long long count, int dtype, cu
     if (count == 0) return 0;
     long long blocks = (count + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    TI_DISPATCH_DTYPE(dtype, (add_kernel<T><<<(int)blocks, 256, 0, stream>>>((T*)x, (const T*)delta, (size_t)count)));
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(add_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)x, (const T*)delta, (size_t)count)));
     return ti_check_launch("add");
 }

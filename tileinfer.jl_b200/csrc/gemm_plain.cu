@@ -19,7 +19,7 @@
 #define TI_EPI_F32_OUT 2   // round to the storage type, store 32-bit (logits)
 
 template <typename T>
-__global__ void __launch_bounds__(256) gemm_plain_kernel(void* __restrict__ y, long long ldy, const T* __restrict__ x,
+__global__ void __launch_bounds__(256) gemm_plain_kernel(void* __restrict__ y, long long ldy, const T* x,
                                                         long long ldx, const T* __restrict__ W, int n, int out,
                                                         int in, int epilogue, XieluParams act) {
     __shared__ float As[GP_BK][GP_BM + 4];
@@ -35,6 +35,8 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(void* __restrict__ y, l
 
     // Each thread stages 4 consecutive k of one row of each operand tile.
     const int lrow = tid / 4, lk = (tid % 4) * 4;
+    pdl_wait();
+    pdl_launch_dependents();
     for (int k0 = 0; k0 < in; k0 += GP_BK) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -83,7 +85,7 @@ extern "C" int ti_gemm_plain(void* y, long long ldy, const void* x, long long ld
     dim3 grid((out + GP_BN - 1) / GP_BN, (n + GP_BM - 1) / GP_BM);
     TI_REQUIRE(grid.y <= 65535, "gemm: too many rows (%d) for one launch", n);
     XieluParams act{alpha_p, alpha_n, beta, eps};
-    TI_DISPATCH_DTYPE(dtype, (gemm_plain_kernel<T><<<grid, 256, 0, stream>>>(y, ldy, (const T*)x, ldx, (const T*)W, n, out, in,
+    TI_DISPATCH_DTYPE(dtype, (ti_launch(gemm_plain_kernel<T>, dim3(grid), dim3(256), 0, stream, y, ldy, (const T*)x, ldx, (const T*)W, n, out, in,
                                                                           epilogue, act)));
     return ti_check_launch("gemm_plain");
 }

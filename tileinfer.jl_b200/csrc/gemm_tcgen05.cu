@@ -191,6 +191,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Barriers and tensor memory are set up while the previous kernel drains; its results (the
+    // activations, and the output buffer it may still read) are touched only after this wait.
+    pdl_wait();
+    pdl_launch_dependents();
     const unsigned tmem_base = *tmem_slot;
 
     TileIter it;
@@ -368,7 +372,7 @@ int launch(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const Params& 
     }
     const int tiles = p.m_tiles * p.n_tiles * p.splits;
     const int grid = tiles < sm_count ? tiles : sm_count;
-    gemm_tcgen05_kernel<BN><<<grid, THREADS, Cfg<BN>::SMEM, stream>>>(mw, mx, y, p);
+    ti_launch(gemm_tcgen05_kernel<BN>, dim3(grid), dim3(THREADS), Cfg<BN>::SMEM, stream, mw, mx, y, p);
     return ti_check_launch("gemm_tcgen05");
 }
 

@@ -38,7 +38,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
 }
 
 template <int NT, int U>
-__global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x,
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(const bf16* __restrict__ W, const bf16* x,
                                                                   long long ldx, void* __restrict__ y, long long ldy,
                                                                   int n, int out, int K, int splits, int epilogue,
                                                                   XieluParams act) {
@@ -65,6 +65,9 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(const bf16* __
     const int blk_lo = (int)((long long)nblk * blockIdx.y / splits);
     const int blk_hi = (int)((long long)nblk * (blockIdx.y + 1) / splits);
     const uint4 zero = make_uint4(0, 0, 0, 0);
+    // The weights do not depend on the previous kernel: the first batch of weight loads is issued
+    // before waiting for it, so this kernel's stream starts while the previous one drains.
+    bool waited = false;
     for (int b = blk_lo + warp; b < blk_hi; b += GV_WARPS * U) {
         uint4 a0[U], a1[U], xb[NT][U];
 #pragma unroll
@@ -74,8 +77,15 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(const bf16* __
             const int idx = bb * 4 + t;
             a0[u] = ok ? ld_stream(wa + idx) : zero;
             a1[u] = ok ? ld_stream(wb + idx) : zero;
+        }
+        if (!waited) { pdl_wait(); pdl_launch_dependents(); waited = true; }
 #pragma unroll
-            for (int j = 0; j < NT; ++j) xb[j][u] = (ok && xv[j]) ? __ldg(xr[j] + idx) : zero;
+        for (int u = 0; u < U; ++u) {
+            const int bb = b + u * GV_WARPS;
+            const bool ok = bb < blk_hi && bb * 32 + 8 * t < K;
+            const int idx = bb * 4 + t;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) xb[j][u] = (ok && xv[j]) ? __ldcg(xr[j] + idx) : zero;
         }
 #pragma unroll
         for (int u = 0; u < U; ++u)
@@ -85,6 +95,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(const bf16* __
                 mma_bf16(c[j], a0[u].z, a1[u].z, a0[u].w, a1[u].w, xb[j][u].z, xb[j][u].w);
             }
     }
+    if (!waited) { pdl_wait(); pdl_launch_dependents(); }   // a warp without work still orders its writes after the predecessor
 #pragma unroll
     for (int j = 0; j < NT; ++j)
 #pragma unroll
@@ -122,10 +133,10 @@ extern "C" int ti_gemv_bf16(void* y, long long ldy, const void* x, long long ldx
     dim3 grid((out + 15) / 16, splits);
     XieluParams act{alpha_p, alpha_n, beta, eps};
     if (n <= 8)
-        gemv_bf16_kernel<1, 8><<<grid, GV_WARPS * 32, 0, stream>>>((const bf16*)W, (const bf16*)x, ldx, y, ldy, n, out, in,
+        ti_launch(gemv_bf16_kernel<1, 8>, dim3(grid), dim3(GV_WARPS * 32), 0, stream, (const bf16*)W, (const bf16*)x, ldx, y, ldy, n, out, in,
                                                                    splits, epilogue, act);
     else
-        gemv_bf16_kernel<2, 4><<<grid, GV_WARPS * 32, 0, stream>>>((const bf16*)W, (const bf16*)x, ldx, y, ldy, n, out, in,
+        ti_launch(gemv_bf16_kernel<2, 4>, dim3(grid), dim3(GV_WARPS * 32), 0, stream, (const bf16*)W, (const bf16*)x, ldx, y, ldy, n, out, in,
                                                                    splits, epilogue, act);
     return ti_check_launch("gemv_bf16");
 }

@@ -36,10 +36,12 @@ __device__ __forceinline__ u32 desc_key(float l) {
 }
 
 // ------------------------------------------------------------------------------ greedy
-__global__ void argmax_kernel(const float* __restrict__ logits, long long ld, int vocab, int* __restrict__ out) {
+__global__ void argmax_kernel(const float* logits, long long ld, int vocab, int* __restrict__ out) {
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const float* row = logits + (size_t)blockIdx.x * ld;
+    pdl_wait();
+    pdl_launch_dependents();
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
@@ -70,7 +72,7 @@ __global__ void argmax_kernel(const float* __restrict__ logits, long long ld, in
 extern "C" int ti_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     TI_REQUIRE(vocab > 0, "argmax: vocab %d", vocab);
-    argmax_kernel<<<n_rows, 512, 0, stream>>>(logits, ld, vocab, out);
+    ti_launch(argmax_kernel, dim3(n_rows), dim3(512), 0, stream, logits, ld, vocab, out);
     return ti_check_launch("argmax");
 }
 
@@ -92,7 +94,7 @@ __device__ __forceinline__ u64 token_weight(int mode, float l, float maxl, float
 
 // First key (ascending) among keys <= bound whose cumulative weight reaches target (at
 // least 1); if the set's total is smaller, the last key with weight. All threads get it.
-__device__ Selected select_key(const float* __restrict__ row, int vocab, int mode, u64 bound, u64 target,
+__device__ Selected select_key(const float* row, int vocab, int mode, u64 bound, u64 target,
                                float maxl, float inv_t, u64* hist /*[SM_WARPS][256]*/, u64* totals /*[256]*/,
                                u64* shared /*[4]*/) {
     const int warp = threadIdx.x >> 5;
@@ -147,9 +149,9 @@ __device__ Selected select_key(const float* __restrict__ row, int vocab, int mod
     return r;
 }
 
-__global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restrict__ logits, long long ld, int vocab,
+__global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* logits, long long ld, int vocab,
                                                             float inv_t, int top_k, float top_p,
-                                                            const u32* __restrict__ seeds, u32* __restrict__ counters,
+                                                            const u32* seeds, u32* counters,
                                                             int* __restrict__ out) {
     extern __shared__ u64 dyn[];
     u64* hist = dyn;
@@ -157,6 +159,8 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* __restr
     u64* shared = totals + 256;
     __shared__ float scratch[33];
     const float* row = logits + (size_t)blockIdx.x * ld;
+    pdl_wait();
+    pdl_launch_dependents();
 
     float maxl = -INFINITY;
     for (int i = threadIdx.x; i < vocab; i += SM_THREADS) maxl = fmaxf(maxl, row[i]);
@@ -217,7 +221,7 @@ extern "C" int ti_sample(const float* logits, long long ld, int n_rows, int voca
         if (e != cudaSuccess) return ti_fail("sample: %s", cudaGetErrorString(e));
         configured = true;
     }
-    sample_kernel<<<n_rows, SM_THREADS, smem, stream>>>(logits, ld, vocab, 1.0f / temperature, top_k, top_p, seeds,
+    ti_launch(sample_kernel, dim3(n_rows), dim3(SM_THREADS), smem, stream, logits, ld, vocab, 1.0f / temperature, top_k, top_p, seeds,
                                                         counters, out);
     return ti_check_launch("sample");
 }

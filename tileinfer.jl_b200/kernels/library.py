@@ -83,6 +83,15 @@ def lib():
     return wrapped
 
 
+def set_pdl(enabled: bool) -> None:
+    """Launch kernels as programmatic dependents of their predecessors (default) or strictly one
+    after the other."""
+    h = lib().handle
+    h.ti_set_pdl.restype = None
+    h.ti_set_pdl.argtypes = [c_int]
+    h.ti_set_pdl(1 if enabled else 0)
+
+
 def declare(name: str, argtypes, restype=c_int):
     """Declare one more entry point (used by kernel files added later)."""
     fn = getattr(lib().handle, name)
