@@ -37,7 +37,7 @@ class StepContext:
     cu_seqlens: torch.Tensor            # [n_seqs + 1] token ranges of the sequences
     kv_lens: torch.Tensor               # [n_seqs] cached length of each sequence after this step
     want_idx: torch.Tensor              # [n_want] flat token indices whose logits are wanted
-    groups: List[GroupMeta]
+    groups: dict                        # cache group index -> GroupMeta, for the paged groups
     # Host copies, for parts that choose kernels or walk sequences themselves.
     host_slots: List[int] = field(default_factory=list)
     host_q_lens: List[int] = field(default_factory=list)
@@ -131,7 +131,7 @@ class StepPlanner:
             token_ids=m[o_ids:o_ids + n], positions=m[o_pos:o_pos + n], tok_slot=m[o_slot:o_slot + n],
             seq_slots=m[o_seq:o_seq + B], cu_seqlens=m[o_cu:o_cu + B + 1], kv_lens=m[o_kv:o_kv + B],
             want_idx=m[o_want:o_want + nw],
-            groups=[GroupMeta(m[o_maps[gi]:o_maps[gi] + n], g.device_table) for gi, g in enumerate(cache.paged_groups)],
+            groups={g.index: GroupMeta(m[o_maps[gi]:o_maps[gi] + n], g.device_table) for gi, g in enumerate(cache.paged_groups)},
             host_slots=slots, host_q_lens=q_lens, host_starts=starts,
             is_decode=all(q == 1 for q in q_lens), max_q_len=max(q_lens, default=0),
             max_kv_len=max((s + q for s, q in zip(starts, q_lens)), default=0),
