@@ -276,3 +276,42 @@ extern "C" int ti_attention_decode(void* out, const void* q, const void* k_cache
     }
 #undef AD_CASE
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same kernels with their work space inside the library: see attention_decode_noalloc.h.
+#include "attention_decode_noalloc.h"
+
+// File-scope device array. In host code this name is only a stand-in for the symbol, not a device
+// address: the address each device gave it is looked up below and that pointer goes to the kernels.
+static __device__ __align__(256) unsigned char ti_decode_noalloc_scratch[TI_DECODE_NOALLOC_SCRATCH_BYTES];
+
+#define TI_NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_scratch[TI_NOALLOC_MAX_DEVICES] = {nullptr};
+
+extern "C" int ti_attention_decode_noalloc(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                           const int* block_table, int table_stride, const int* seq_slots,
+                                           const int* kv_lens, float scale, int B, int nq, int nkv, int D, int page_size,
+                                           int splits, int window, cudaStream_t stream) {
+    if (B == 0) return 0;
+    TI_REQUIRE(B > 0 && nq > 0 && D > 0 && splits >= 1, "attention_decode_noalloc: bad sizes B=%d nq=%d D=%d splits=%d", B, nq, D, splits);
+    const unsigned long long floats = splits > 1 ? (unsigned long long)B * nq * splits * (D + 2) : 0ull;
+    TI_REQUIRE(floats * sizeof(float) <= TI_DECODE_NOALLOC_SCRATCH_BYTES,
+               "attention_decode_noalloc: B=%d, %d heads, %d splits and head size %d need %llu bytes of work space; the "
+               "built-in array holds %u", B, nq, splits, D, floats * (unsigned long long)sizeof(float), TI_DECODE_NOALLOC_SCRATCH_BYTES);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return ti_fail("attention_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    TI_REQUIRE(dev >= 0 && dev < TI_NOALLOC_MAX_DEVICES, "attention_decode_noalloc: device %d is beyond the %d this build tracks", dev, TI_NOALLOC_MAX_DEVICES);
+    if (g_noalloc_scratch[dev] == nullptr) {
+        // Once per device, with that device current: the array's address on THIS device.
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, ti_decode_noalloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return ti_fail("attention_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_noalloc_scratch[dev] = static_cast<float*>(ptr);
+    }
+    float* ws_o = g_noalloc_scratch[dev];                       // [B, nq, splits, D]
+    float* ws_ml = ws_o + (size_t)B * nq * splits * D;          // [B, nq, splits, 2]
+    return ti_attention_decode(out, q, k_cache, v_cache, block_table, table_stride, seq_slots, kv_lens, ws_o, ws_ml, scale,
+                               B, nq, nkv, D, page_size, splits, window, stream);
+}
