@@ -20,6 +20,7 @@
 #define AD_PAGE 64
 #define AD_WARPS 4
 #define AD_THREADS (AD_WARPS * 32)
+#define AD_MAX_SPLITS 64
 
 template <int D> struct DecodeSmem {
     static constexpr int STAGES = D <= 128 ? 3 : 2;
@@ -50,15 +51,38 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int group = nq / nkv;
-    pdl_wait();
-    pdl_launch_dependents();
-    const int kv_len = kv_lens[b];
+    // The step's lengths and block tables were uploaded before its first kernel, and every page but
+    // the sequence's last one holds only older positions: their copies start BEFORE waiting for the
+    // kernel that writes this step's key, value and query.
+    const int kv_len = __ldcg(kv_lens + b);
     const int first_key = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int t_begin = first_key / AD_PAGE, t_end = (kv_len + AD_PAGE - 1) / AD_PAGE;
     const int n_tiles = t_end - t_begin;
     const int my_lo = t_begin + (int)((long long)n_tiles * split / splits);
     const int my_hi = t_begin + (int)((long long)n_tiles * (split + 1) / splits);
-    const int* table = block_table + (size_t)seq_slots[b] * table_stride;
+    const int* table = block_table + (size_t)__ldcg(seq_slots + b) * table_stride;
+    bool waited = false;
+
+    auto issue = [&](int tile, int stage) {
+        if (tile < my_hi) {
+            if (tile == t_end - 1 && !waited) {              // the page that this step writes to
+                pdl_wait();
+                pdl_launch_dependents();
+                waited = true;
+            }
+            const size_t base = ((size_t)__ldcg(table + tile) * nkv + kvh) * AD_PAGE * D;
+            load_tile<D>(tiles + (size_t)stage * 2 * SM::TILE, k_cache + base);
+            load_tile<D>(tiles + (size_t)stage * 2 * SM::TILE + SM::TILE, v_cache + base);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < SM::STAGES - 1; ++s) issue(my_lo + s, s);
+    if (!waited) {
+        pdl_wait();
+        pdl_launch_dependents();
+        waited = true;
+    }
 
     // Query rows = the heads of this KV head's group, padded to 16.
     unsigned qf[KS][4];
@@ -67,10 +91,10 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int d = ks * 16 + 2 * t;
-            qf[ks][0] = g < group ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + d) : 0u;
-            qf[ks][1] = g + 8 < group ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + d) : 0u;
-            qf[ks][2] = g < group ? *reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + d + 8) : 0u;
-            qf[ks][3] = g + 8 < group ? *reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + d + 8) : 0u;
+            qf[ks][0] = g < group ? __ldcg(reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + d)) : 0u;
+            qf[ks][1] = g + 8 < group ? __ldcg(reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + d)) : 0u;
+            qf[ks][2] = g < group ? __ldcg(reinterpret_cast<const unsigned*>(q0 + (size_t)g * D + d + 8)) : 0u;
+            qf[ks][3] = g + 8 < group ? __ldcg(reinterpret_cast<const unsigned*>(q0 + (size_t)(g + 8) * D + d + 8)) : 0u;
         }
     }
     float o[NT][4];
@@ -79,17 +103,6 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;       // rows g and g + 8
-
-    auto issue = [&](int tile, int stage) {
-        if (tile < my_hi) {
-            const size_t base = ((size_t)table[tile] * nkv + kvh) * AD_PAGE * D;
-            load_tile<D>(tiles + (size_t)stage * 2 * SM::TILE, k_cache + base);
-            load_tile<D>(tiles + (size_t)stage * 2 * SM::TILE + SM::TILE, v_cache + base);
-        }
-        cp_async_commit();
-    };
-#pragma unroll
-    for (int s = 0; s < SM::STAGES - 1; ++s) issue(my_lo + s, s);
 
     for (int tile = my_lo; tile < my_hi; ++tile) {
         const int stage = (tile - my_lo) % SM::STAGES;
@@ -214,16 +227,46 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws
                                          const float* ws_ml, int D, int splits) {
     const size_t row = blockIdx.x;                          // (sequence, head)
     const float* ml = ws_ml + row * splits * 2;
-    pdl_wait();
-    pdl_launch_dependents();
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[2 * s]);
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) L += ml[2 * s + 1] * exp2f(ml[2 * s] - M);
+    __shared__ float sm[AD_MAX_SPLITS], sl[AD_MAX_SPLITS], sw[AD_MAX_SPLITS];
+    __shared__ float s_inv;
+    pdl_enter();
+    // One round of loads: every thread's partial outputs (for up to 16 splits) are requested together
+    // with the splits' (m, l), before anything is computed.
+    const int d0 = threadIdx.x;
+    float first[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) first[u] = (d0 < D && u < splits) ? __ldcg(ws_o + (row * splits + u) * D + d0) : 0.f;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        sm[s] = __ldcg(ml + 2 * s);
+        sl[s] = __ldcg(ml + 2 * s + 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float M = -INFINITY;
+        for (int s = 0; s < splits; ++s) M = fmaxf(M, sm[s]);
+        float L = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            sw[s] = exp2f(sm[s] - M);
+            L += sl[s] * sw[s];
+        }
+        s_inv = 1.0f / L;
+    }
+    __syncthreads();
+    const float inv = s_inv;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float O = 0.f;
-        for (int s = 0; s < splits; ++s) O += ws_o[(row * splits + s) * D + d] * exp2f(ml[2 * s] - M);
-        out[row * D + d] = __float2bfloat16_rn(O / L);
+        if (d == d0) {
+#pragma unroll
+            for (int u = 0; u < 16; ++u) O += (u < splits ? sw[u] : 0.f) * first[u];
+        }
+        for (int s0 = d == d0 ? 16 : 0; s0 < splits; s0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = s0 + u < splits ? __ldcg(ws_o + (row * splits + s0 + u) * D + d) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) O += (s0 + u < splits ? sw[s0 + u] : 0.f) * v[u];
+        }
+        out[row * D + d] = __float2bfloat16_rn(O * inv);
     }
 }
 
@@ -263,7 +306,8 @@ extern "C" int ti_attention_decode(void* out, const void* q, const void* k_cache
                 "got page %d, %d/%d heads, head size %d", AD_PAGE, page_size, nq, nkv, D);
         return 2;
     }
-    TI_REQUIRE(splits >= 1 && (splits == 1 || (ws_o != nullptr && ws_ml != nullptr)), "attention_decode: splits need a workspace");
+    TI_REQUIRE(splits >= 1 && splits <= AD_MAX_SPLITS, "attention_decode: %d splits (1 to %d)", splits, AD_MAX_SPLITS);
+    TI_REQUIRE(splits == 1 || (ws_o != nullptr && ws_ml != nullptr), "attention_decode: splits need a workspace");
 #define AD_CASE(d)                                                                                                     \
     case d:                                                                                                            \
         return launch_decode<d>((bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,     \

@@ -23,8 +23,11 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, T* _
     const int t = blockIdx.x;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     const int head = blockIdx.y * AI_WARPS + warp;
-    pdl_wait();
-    pdl_launch_dependents();
+    // Positions and slots were uploaded before the step's first kernel: they, and the rotation table's
+    // row they select, are read before waiting for the projection that produces qkv.
+    const int slot_t = slots != nullptr ? __ldcg(slots + t) : 0;
+    const int pos_t = __ldcg(positions + t);
+    pdl_enter();
     if (head >= heads_total) return;
     float* buf = smem + warp * D;
 
@@ -37,19 +40,19 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, T* _
     if (is_q) {
         dst = q_out + ((size_t)t * nq + head) * D;
     } else {
-        const int slot = slots[t];
+        const int slot = slot_t;
         const int page = slot / page_size, off = slot - page * page_size;
         T* base = is_k ? k_cache : v_cache;
         dst = base + (((size_t)page * nkv + kvh) * page_size + off) * D;
     }
     if (!is_q && !is_k) {                    // value head: a copy
-        for (int d = lane; d < D; d += 32) dst[d] = src[d];
+        for (int d = lane; d < D; d += 32) dst[d] = __ldcg(src + d);
         return;
     }
     const T* nw = is_q ? q_norm_w : k_norm_w;
     float ss = 0.f;
     for (int d = lane; d < D; d += 32) {
-        const float v = to_f32(src[d]);
+        const float v = to_f32(__ldcg(src + d));
         buf[d] = v;
         ss = fmaf(v, v, ss);
     }
@@ -64,7 +67,7 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, T* _
         return;
     }
     const int half = D >> 1;
-    const float* cs = cos_sin + (size_t)positions[t] * D;     // [half][2] = (cos, sin)
+    const float* cs = cos_sin + (size_t)pos_t * D;     // [half][2] = (cos, sin)
     for (int d = lane; d < D; d += 32) {
         const int i = d < half ? d : d - half;
         const float c = cs[2 * i], s = cs[2 * i + 1];

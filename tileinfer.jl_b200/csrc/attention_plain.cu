@@ -32,10 +32,10 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
     const int kvh = h / (nq / nkv);
     pdl_wait();
     pdl_launch_dependents();
-    const int p = positions[t];
-    const int* table = block_table + (size_t)tok_slot[t] * table_stride;
+    const int p = __ldcg(positions + t);
+    const int* table = block_table + (size_t)__ldcg(tok_slot + t) * table_stride;
     const T* qrow = q + ((size_t)t * nq + h) * D;
-    for (int d = threadIdx.x; d < D; d += AP_THREADS) qs[d] = to_f32(qrow[d]);
+    for (int d = threadIdx.x; d < D; d += AP_THREADS) qs[d] = to_f32(__ldcg(qrow + d));
     __syncthreads();
 
     constexpr int ACC = AP_MAX_D / AP_THREADS;
@@ -50,10 +50,10 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
         const int hi = (c0 + AP_CHUNK - 1 < p) ? c0 + AP_CHUNK - 1 : p;       // inclusive
         float cmax = -INFINITY;
         for (int j = lo + threadIdx.x; j <= hi; j += AP_THREADS) {
-            const int page = table[j / page_size], off = j % page_size;
+            const int page = __ldcg(table + j / page_size), off = j % page_size;
             const T* krow = k_cache + (((size_t)page * nkv + kvh) * page_size + off) * D;
             float s = 0.f;
-            for (int d = 0; d < D; ++d) s = fmaf(qs[d], to_f32(krow[d]), s);
+            for (int d = 0; d < D; ++d) s = fmaf(qs[d], to_f32(__ldcg(krow + d)), s);
             s *= scale;
             sc[j - c0] = s;
             cmax = fmaxf(cmax, s);
@@ -76,8 +76,8 @@ __global__ void attention_plain_kernel(T* __restrict__ out, const T* q, const T*
             if (d < D) {
                 float a = acc[i] * factor;
                 for (int j = lo; j <= hi; ++j) {
-                    const int page = table[j / page_size], off = j % page_size;
-                    a = fmaf(sc[j - c0], to_f32(v_cache[(((size_t)page * nkv + kvh) * page_size + off) * D + d]), a);
+                    const int page = __ldcg(table + j / page_size), off = j % page_size;
+                    a = fmaf(sc[j - c0], to_f32(__ldcg(v_cache + (((size_t)page * nkv + kvh) * page_size + off) * D + d)), a);
                 }
                 acc[i] = a;
             }

@@ -61,17 +61,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
     // Which (sequence, query tile) is this block's?
     int b = 0, tile_in_seq = blockIdx.x;
     for (; b < n_seqs; ++b) {
-        const int tiles_b = (cu_seqlens[b + 1] - cu_seqlens[b] + tokens_per_tile - 1) / tokens_per_tile;
+        const int tiles_b = (__ldcg(cu_seqlens + b + 1) - __ldcg(cu_seqlens + b) + tokens_per_tile - 1) / tokens_per_tile;
         if (tile_in_seq < tiles_b) break;
         tile_in_seq -= tiles_b;
     }
     if (b >= n_seqs) return;
-    const int q_begin = cu_seqlens[b], q_len = cu_seqlens[b + 1] - q_begin;
-    const int kv_len = kv_lens[b];
+    const int q_begin = __ldcg(cu_seqlens + b), q_len = __ldcg(cu_seqlens + b + 1) - q_begin;
+    const int kv_len = __ldcg(kv_lens + b);
     const int start = kv_len - q_len;                        // position of the sequence's first token in this step
     const int j0 = tile_in_seq * tokens_per_tile;
     const int n_tok = min(tokens_per_tile, q_len - j0);
-    const int* table = block_table + (size_t)seq_slots[b] * table_stride;
+    const int* table = block_table + (size_t)__ldcg(seq_slots + b) * table_stride;
 
     // This thread's two rows (r0, r0 + 8): token and head inside the tile, and the position.
     const int r0 = warp * 16 + g, r1 = r0 + 8;
@@ -88,10 +88,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int d = ks * 16 + 2 * t;
-            qf[ks][0] = live0 ? *reinterpret_cast<const unsigned*>(qa + d) : 0u;
-            qf[ks][1] = live1 ? *reinterpret_cast<const unsigned*>(qb + d) : 0u;
-            qf[ks][2] = live0 ? *reinterpret_cast<const unsigned*>(qa + d + 8) : 0u;
-            qf[ks][3] = live1 ? *reinterpret_cast<const unsigned*>(qb + d + 8) : 0u;
+            qf[ks][0] = live0 ? __ldcg(reinterpret_cast<const unsigned*>(qa + d)) : 0u;
+            qf[ks][1] = live1 ? __ldcg(reinterpret_cast<const unsigned*>(qb + d)) : 0u;
+            qf[ks][2] = live0 ? __ldcg(reinterpret_cast<const unsigned*>(qa + d + 8)) : 0u;
+            qf[ks][3] = live1 ? __ldcg(reinterpret_cast<const unsigned*>(qb + d + 8)) : 0u;
         }
     }
     float o[NT][4];
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) attention_prefill_kernel(
 
     auto issue = [&](int tile, int stage) {
         if (tile < t_hi) {
-            const size_t base = ((size_t)table[tile] * nkv + kvh) * PF_PAGE * D;
+            const size_t base = ((size_t)__ldcg(table + tile) * nkv + kvh) * PF_PAGE * D;
             pf_load_tile<D>(tiles + (size_t)stage * 2 * SM::TILE, k_cache + base);
             pf_load_tile<D>(tiles + (size_t)stage * 2 * SM::TILE + SM::TILE, v_cache + base);
         }

@@ -33,6 +33,14 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // kernel launched as a programmatic dependent starts before its predecessor has finished writing.
 extern int ti_pdl_enabled;
 
+// Wait for the predecessor, then let the successor start: at most two kernels overlap. (Releasing the
+// successor before waiting, so that more kernels are resident at once, was measured on the decode
+// step and was slower: blocks that sit waiting take residency away from the kernel that is running.)
+__device__ __forceinline__ void pdl_enter() {
+    pdl_wait();
+    pdl_launch_dependents();
+}
+
 // Launch with the programmatic-stream-serialization attribute when enabled.
 template <typename... KArgs, typename... Args>
 inline cudaError_t ti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
@@ -128,13 +136,17 @@ template <> struct Vec16<float> {
         const float4 t = *reinterpret_cast<const float4*>(p);
         v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
     }
+    // Through L2, never from a line that L1 may still hold from before another kernel wrote it.
+    __device__ __forceinline__ void load_cg(const float* p) {
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(p));
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
     __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
 };
 template <> struct Vec16<bf16> {
     static constexpr int N = 8;
     float v[8];
-    __device__ __forceinline__ void load(const bf16* p) {
-        const uint4 t = *reinterpret_cast<const uint4*>(p);
+    __device__ __forceinline__ void unpack(const uint4& t) {
         const unsigned w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -142,6 +154,8 @@ template <> struct Vec16<bf16> {
             v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
         }
     }
+    __device__ __forceinline__ void load(const bf16* p) { unpack(*reinterpret_cast<const uint4*>(p)); }
+    __device__ __forceinline__ void load_cg(const bf16* p) { unpack(__ldcg(reinterpret_cast<const uint4*>(p))); }
     __device__ __forceinline__ void store(bf16* p) const {
         unsigned w[4];
 #pragma unroll

@@ -35,9 +35,9 @@ template <typename T> __device__ __forceinline__ void copy_row(T* dst, const T* 
     if (size % N == 0 && (((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
         const uint4* s4 = reinterpret_cast<const uint4*>(src);
         uint4* d4 = reinterpret_cast<uint4*>(dst);
-        for (int i = threadIdx.x; i < size / N; i += blockDim.x) d4[i] = s4[i];
+        for (int i = threadIdx.x; i < size / N; i += blockDim.x) d4[i] = __ldcg(s4 + i);
     } else {
-        for (int i = threadIdx.x; i < size; i += blockDim.x) dst[i] = src[i];
+        for (int i = threadIdx.x; i < size; i += blockDim.x) dst[i] = __ldcg(src + i);
     }
 }
 
@@ -46,9 +46,8 @@ template <typename T>
 __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* ids,
                              int hidden, int vocab, int* __restrict__ status) {
     const int t = blockIdx.x;
-    pdl_wait();
-    pdl_launch_dependents();
-    int id = ids[t];
+    pdl_enter();
+    int id = __ldcg(ids + t);
     if (id < 0 || id >= vocab) {            // never read outside the table; report instead
         if (threadIdx.x == 0) atomicExch(status, 1 + t);
         id = 0;
@@ -70,9 +69,8 @@ extern "C" int ti_embed(void* out, const void* table, const int* ids, int n_toke
 // Rows idx[i] of x [*, size] to out [n, size] (the positions whose logits are wanted).
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* x, const int* idx, int size) {
-    pdl_wait();
-    pdl_launch_dependents();
-    const T* row = x + (size_t)idx[blockIdx.x] * size;
+    pdl_enter();
+    const T* row = x + (size_t)__ldcg(idx + blockIdx.x) * size;
     T* dst = out + (size_t)blockIdx.x * size;
     copy_row(dst, row, size);
 }
@@ -90,7 +88,7 @@ __global__ void xielu_kernel(T* out, const T* in, size_t count, XieluParams a) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     pdl_wait();
     pdl_launch_dependents();
-    for (; i < count; i += stride) out[i] = from_f32<T>(xielu_value<T>(to_f32(in[i]), a));
+    for (; i < count; i += stride) out[i] = from_f32<T>(xielu_value<T>(to_f32(__ldcg(in + i)), a));
 }
 
 template <typename T>
@@ -102,7 +100,7 @@ __global__ void xielu_vec_kernel(T* out, const T* in, size_t vecs, XieluParams a
     pdl_launch_dependents();
     for (; i < vecs; i += stride) {
         Vec16<T> v;
-        v.load(in + i * N);
+        v.load_cg(in + i * N);
 #pragma unroll
         for (int e = 0; e < N; ++e) v.v[e] = xielu_value<T>(v.v[e], a);
         v.store(out + i * N);
@@ -139,13 +137,13 @@ __global__ void rmsnorm_kernel(T* y, const T* x, const T* __restrict__ w, int si
     pdl_wait();
     pdl_launch_dependents();
     for (int i = threadIdx.x; i < size; i += blockDim.x) {
-        const float v = to_f32(row[i]);
+        const float v = to_f32(__ldcg(row + i));
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)size + eps);
     for (int i = threadIdx.x; i < size; i += blockDim.x)
-        dst[i] = from_f32<T>(to_f32(w[i]) * rnd<T>(to_f32(row[i]) * inv));
+        dst[i] = from_f32<T>(to_f32(w[i]) * rnd<T>(to_f32(__ldcg(row + i)) * inv));
 }
 
 // The same with 16-byte accesses: every thread owns up to MAXV vectors of its row, so all loads
@@ -160,13 +158,12 @@ __global__ void rmsnorm_vec_kernel(T* y, const T* x, const T* __restrict__ w, in
     T* dst = y + (size_t)blockIdx.x * size;
     Vec16<T> v[RN_MAXV];
     float ss = 0.f;
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_enter();
 #pragma unroll
     for (int j = 0; j < RN_MAXV; ++j) {
         const int i = (threadIdx.x + j * blockDim.x) * N;
         if (i < size) {
-            v[j].load(row + i);
+            v[j].load_cg(row + i);
 #pragma unroll
             for (int e = 0; e < N; ++e) ss = fmaf(v[j].v[e], v[j].v[e], ss);
         }
@@ -194,35 +191,50 @@ __global__ void add_rmsnorm_vec_kernel(T* x, const T* delta, const float* partia
     constexpr int N = Vec16<T>::N;
     T* row = x + (size_t)blockIdx.x * size;
     T* dst = h + (size_t)blockIdx.x * size;
-    Vec16<T> v[RN_MAXV];
+    Vec16<T> v[RN_MAXV], wv[RN_MAXV];
     float ss = 0.f;
-    pdl_wait();
-    pdl_launch_dependents();
+    // The norm's weight does not depend on the predecessor: it is read before waiting for it.
+#pragma unroll
+    for (int j = 0; j < RN_MAXV; ++j) {
+        const int i = (threadIdx.x + j * blockDim.x) * N;
+        if (i < size) wv[j].load(w + i);
+    }
+    pdl_enter();
 #pragma unroll
     for (int j = 0; j < RN_MAXV; ++j) {
         const int i = (threadIdx.x + j * blockDim.x) * N;
         if (i < size) {
-            v[j].load(row + i);
+            v[j].load_cg(row + i);
             float d[N];
             if (partials != nullptr) {
                 const float* p = partials + (size_t)blockIdx.x * size + i;
 #pragma unroll
                 for (int e = 0; e < N; e += 4) {
-                    const float4 t = *reinterpret_cast<const float4*>(p + e);
+                    const float4 t = __ldcg(reinterpret_cast<const float4*>(p + e));
                     d[e] = t.x; d[e + 1] = t.y; d[e + 2] = t.z; d[e + 3] = t.w;
                 }
-                for (int s = 1; s < n_partials; ++s) {
+                // Eight splits at a time: their loads are issued together, the additions stay in split order.
+                for (int s0 = 1; s0 < n_partials; s0 += 8) {
+                    float4 t[8][N / 4];
 #pragma unroll
-                    for (int e = 0; e < N; e += 4) {
-                        const float4 t = *reinterpret_cast<const float4*>(p + (size_t)s * partial_stride + e);
-                        d[e] += t.x; d[e + 1] += t.y; d[e + 2] += t.z; d[e + 3] += t.w;
-                    }
+                    for (int u = 0; u < 8; ++u)
+#pragma unroll
+                        for (int e = 0; e < N; e += 4)
+                            t[u][e / 4] = s0 + u < n_partials
+                                              ? __ldcg(reinterpret_cast<const float4*>(p + (size_t)(s0 + u) * partial_stride + e))
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+#pragma unroll
+                        for (int e = 0; e < N; e += 4) {
+                            d[e] += t[u][e / 4].x; d[e + 1] += t[u][e / 4].y; d[e + 2] += t[u][e / 4].z; d[e + 3] += t[u][e / 4].w;
+                        }
                 }
 #pragma unroll
                 for (int e = 0; e < N; ++e) d[e] = rnd<T>(d[e]);
             } else {
                 Vec16<T> dv;
-                dv.load(delta + (size_t)blockIdx.x * size + i);
+                dv.load_cg(delta + (size_t)blockIdx.x * size + i);
 #pragma unroll
                 for (int e = 0; e < N; ++e) d[e] = dv.v[e];
             }
@@ -240,10 +252,8 @@ __global__ void add_rmsnorm_vec_kernel(T* x, const T* delta, const float* partia
     for (int j = 0; j < RN_MAXV; ++j) {
         const int i = (threadIdx.x + j * blockDim.x) * N;
         if (i < size) {
-            Vec16<T> wv;
-            wv.load(w + i);
 #pragma unroll
-            for (int e = 0; e < N; ++e) v[j].v[e] = wv.v[e] * rnd<T>(v[j].v[e] * inv);
+            for (int e = 0; e < N; ++e) v[j].v[e] = wv[j].v[e] * rnd<T>(v[j].v[e] * inv);
             v[j].store(dst + i);
         }
     }
@@ -291,13 +301,13 @@ __global__ void add_rmsnorm_kernel(T* x, const T* delta, const float* partials,
         float d;
         if (partials != nullptr) {
             const float* p = partials + (size_t)blockIdx.x * size + i;
-            d = p[0];
-            for (int s = 1; s < n_partials; ++s) d += p[(size_t)s * partial_stride];
+            d = __ldcg(p);
+            for (int s = 1; s < n_partials; ++s) d += __ldcg(p + (size_t)s * partial_stride);
             d = rnd<T>(d);
         } else {
-            d = to_f32(delta[(size_t)blockIdx.x * size + i]);
+            d = to_f32(__ldcg(delta + (size_t)blockIdx.x * size + i));
         }
-        const float v = rnd<T>(to_f32(row[i]) + d);
+        const float v = rnd<T>(to_f32(__ldcg(row + i)) + d);
         row[i] = from_f32<T>(v);
         ss = fmaf(v, v, ss);
     }
@@ -305,7 +315,7 @@ __global__ void add_rmsnorm_kernel(T* x, const T* delta, const float* partials,
     const float inv = 1.0f / sqrtf(ss / (float)size + eps);
     // Each thread re-reads exactly the elements it wrote above.
     for (int i = threadIdx.x; i < size; i += blockDim.x)
-        dst[i] = from_f32<T>(to_f32(w[i]) * rnd<T>(to_f32(row[i]) * inv));
+        dst[i] = from_f32<T>(to_f32(w[i]) * rnd<T>(to_f32(__ldcg(row + i)) * inv));
 }
 
 extern "C" int ti_add_rmsnorm(void* x, const void* delta, const float* partials, int n_partials, long long partial_stride,
@@ -334,7 +344,7 @@ __global__ void add_kernel(T* x, const T* delta, size_t count) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     pdl_wait();
     pdl_launch_dependents();
-    for (; i < count; i += stride) x[i] = from_f32<T>(to_f32(x[i]) + to_f32(delta[i]));
+    for (; i < count; i += stride) x[i] = from_f32<T>(to_f32(__ldcg(x + i)) + to_f32(__ldcg(delta + i)));
 }
 
 extern "C" int ti_add(void* x, const void* delta, long long count, int dtype, cudaStream_t stream) {

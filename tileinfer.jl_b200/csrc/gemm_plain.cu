@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(void* __restrict__ y, l
         for (int i = 0; i < 4; ++i) {
             const int k = k0 + lk + i;
             const int r = m0 + lrow, c = n0 + lrow;
-            As[lk + i][lrow] = (r < n && k < in) ? to_f32(x[(size_t)r * ldx + k]) : 0.f;
+            As[lk + i][lrow] = (r < n && k < in) ? to_f32(__ldcg(x + (size_t)r * ldx + k)) : 0.f;
             Bs[lk + i][lrow] = (c < out && k < in) ? to_f32(W[(size_t)c * in + k]) : 0.f;
         }
         __syncthreads();

@@ -40,12 +40,11 @@ __global__ void argmax_kernel(const float* logits, long long ld, int vocab, int*
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const float* row = logits + (size_t)blockIdx.x * ld;
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_enter();
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
+        const float v = __ldcg(row + i);
         if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
     }
     for (int o = 16; o > 0; o >>= 1) {
@@ -163,7 +162,7 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* logits,
     pdl_launch_dependents();
 
     float maxl = -INFINITY;
-    for (int i = threadIdx.x; i < vocab; i += SM_THREADS) maxl = fmaxf(maxl, row[i]);
+    for (int i = threadIdx.x; i < vocab; i += SM_THREADS) maxl = fmaxf(maxl, __ldcg(row + i));
     maxl = block_max(maxl, scratch);
 
     u64 bound = ~0ull;
