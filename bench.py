@@ -110,32 +110,33 @@ def release(engine, slots):
 
 
 def time_decode(engine, batch, steps, warmup, vocab, count_launches=False):
-    """Device time of ``steps`` decode steps of ``batch`` sequences (greedy sampling on the device)."""
+    """Device time of ``steps`` decode steps of ``batch`` sequences through the library's own decode
+    loop (greedy sampling on the device, the host one step behind): CUDA events are recorded when the
+    tokens of step W and of step W + K reach the host, which brackets exactly K steps on the stream."""
     import torch
+    from tileinfer_b200.engine.generate import _decode_batch
     from tileinfer_b200.sampling import DeviceSampler, SamplingParams
-    slots = fill_cache(engine, batch, CACHED)
+    warmup = max(warmup, 3)
+    slots_list = fill_cache(engine, batch, CACHED - 1)
     sampler = DeviceSampler(batch, engine.device)
     gen = torch.Generator().manual_seed(1)
     tokens = torch.randint(0, vocab, (batch,), generator=gen).tolist()
-    launches = 0
+    logits = engine.decode(slots_list, tokens)                       # position CACHED - 1: now CACHED positions are held
+    slots = dict(enumerate(slots_list))
+    results = [[] for _ in range(batch)]
+    marks = {}
 
-    def one(tokens):
-        logits = engine.step([(s, [t]) for s, t in zip(slots, tokens)])
-        return sampler.sample(logits, SamplingParams()).tolist()
-    for _ in range(max(warmup, 3)):
-        tokens = one(tokens)
-    if count_launches:
-        launches = engine.decode_launches(batch) + 1      # the captured step + the sampling kernel
+    def on_token(request, token):
+        if request == 0 and len(results[0]) in (warmup, warmup + steps):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks[len(results[0])] = ev
+    _decode_batch(engine, sampler, SamplingParams(), list(range(batch)), slots, logits, results, warmup + steps + 2, set(), on_token)
     torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
-        tokens = one(tokens)
-    b.record()
-    torch.cuda.synchronize()
-    ms = a.elapsed_time(b)
-    kv_positions = batch * (CACHED + max(warmup, 3) + steps / 2)
-    release(engine, slots)
+    ms = marks[warmup].elapsed_time(marks[warmup + steps])
+    launches = engine.decode_launches(batch) + 2 if count_launches else 0     # the captured step + sampling + id hand-over
+    kv_positions = batch * (CACHED + warmup + 1 + steps / 2)
+    assert not slots                                                  # the loop freed every sequence
     return ms / steps, kv_positions, launches
 
 

@@ -36,42 +36,113 @@ __device__ __forceinline__ u32 desc_key(float l) {
 }
 
 // ------------------------------------------------------------------------------ greedy
-__global__ void argmax_kernel(const float* logits, long long ld, int vocab, int* __restrict__ out) {
-    __shared__ float best_v[32];
-    __shared__ int best_i[32];
-    const float* row = logits + (size_t)blockIdx.x * ld;
-    pdl_enter();
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = __ldcg(row + i);
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-    }
+// argmax with ties to the smaller id, over a vocabulary of any size, in ONE launch that uses many
+// blocks: each block reduces a slice of the row and leaves its candidate in a work space; the block
+// that arrives last at the row's counter (no block waits for another) reduces the candidates, writes
+// the token and resets the counter for the next launch. (value, id) under "greater value, then
+// smaller id" is a total order, so the result does not depend on the order of arrival.
+#define AM_THREADS 256
+#define AM_MAX_CHUNKS 256
+
+__device__ __forceinline__ bool am_better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__device__ __forceinline__ void am_block_reduce(float& bv, int& bi, float* sv, int* si) {
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        if (am_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
     __syncthreads();
     if (warp == 0) {
-        const int warps = blockDim.x >> 5;
-        bv = lane < warps ? best_v[lane] : -INFINITY;
-        bi = lane < warps ? best_i[lane] : 0x7fffffff;
+        bv = lane < AM_THREADS / 32 ? sv[lane] : -INFINITY;
+        bi = lane < AM_THREADS / 32 ? si[lane] : 0x7fffffff;
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            if (am_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
         }
-        if (lane == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* logits, long long ld, int vocab, int per_chunk,
+                                                            int* __restrict__ out, float* ws_val, int* ws_idx,
+                                                            unsigned* counters) {
+    __shared__ float sv[AM_THREADS / 32];
+    __shared__ int si[AM_THREADS / 32];
+    __shared__ bool last;
+    const int chunk = blockIdx.x, row_id = blockIdx.y, chunks = gridDim.x;
+    const float* row = logits + (size_t)row_id * ld;
+    const int lo = chunk * per_chunk, hi = min(vocab, lo + per_chunk);
+    pdl_enter();
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    if ((((uintptr_t)row) & 15) == 0 && (lo & 3) == 0) {
+        for (int i = lo + 4 * threadIdx.x; i < hi; i += 4 * AM_THREADS) {
+            if (i + 3 < hi) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(row + i));
+                if (am_better(v.x, i, bv, bi)) { bv = v.x; bi = i; }
+                if (am_better(v.y, i + 1, bv, bi)) { bv = v.y; bi = i + 1; }
+                if (am_better(v.z, i + 2, bv, bi)) { bv = v.z; bi = i + 2; }
+                if (am_better(v.w, i + 3, bv, bi)) { bv = v.w; bi = i + 3; }
+            } else {
+                for (int j = i; j < hi; ++j) {
+                    const float v = __ldcg(row + j);
+                    if (am_better(v, j, bv, bi)) { bv = v; bi = j; }
+                }
+            }
+        }
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += AM_THREADS) {
+            const float v = __ldcg(row + i);
+            if (am_better(v, i, bv, bi)) { bv = v; bi = i; }
+        }
+    }
+    am_block_reduce(bv, bi, sv, si);
+    if (threadIdx.x == 0) {
+        ws_val[(size_t)row_id * chunks + chunk] = bv;
+        ws_idx[(size_t)row_id * chunks + chunk] = bi;
+        __threadfence();                                   // the candidate is visible before the ticket is taken
+        last = atomicAdd(&counters[row_id], 1u) == (unsigned)chunks - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    bv = -INFINITY;
+    bi = 0x7fffffff;
+    for (int c = threadIdx.x; c < chunks; c += AM_THREADS) {
+        const float v = __ldcg(ws_val + (size_t)row_id * chunks + c);
+        const int i = __ldcg(ws_idx + (size_t)row_id * chunks + c);
+        if (am_better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+    am_block_reduce(bv, bi, sv, si);
+    if (threadIdx.x == 0) {
+        out[row_id] = bi == 0x7fffffff ? 0 : bi;
+        counters[row_id] = 0;                              // ready for the next launch
     }
 }
 
-extern "C" int ti_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out, cudaStream_t stream) {
+// Work space: ws_val and ws_idx hold n_rows x TI_ARGMAX_CHUNKS(vocab) entries, counters n_rows words
+// that are zero before the first launch (the kernel leaves them zero).
+extern "C" int ti_argmax_chunks(int vocab) {
+    int chunks = (vocab + 1023) / 1024;
+    if (chunks < 1) chunks = 1;
+    return chunks > AM_MAX_CHUNKS ? AM_MAX_CHUNKS : chunks;
+}
+
+extern "C" int ti_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out, float* ws_val, int* ws_idx,
+                         unsigned* counters, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     TI_REQUIRE(vocab > 0, "argmax: vocab %d", vocab);
-    ti_launch(argmax_kernel, dim3(n_rows), dim3(512), 0, stream, logits, ld, vocab, out);
+    TI_REQUIRE(n_rows <= 65535, "argmax: %d rows in one launch", n_rows);
+    TI_REQUIRE(ws_val != nullptr && ws_idx != nullptr && counters != nullptr, "argmax: work space missing");
+    const int chunks = ti_argmax_chunks(vocab);
+    int per_chunk = (vocab + chunks - 1) / chunks;
+    per_chunk = (per_chunk + 3) & ~3;
+    ti_launch(argmax_kernel, dim3(chunks, n_rows), dim3(AM_THREADS), 0, stream, logits, ld, vocab, per_chunk, out, ws_val, ws_idx,
+              counters);
     return ti_check_launch("argmax");
 }
 

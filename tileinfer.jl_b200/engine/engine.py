@@ -113,9 +113,9 @@ class Engine:
             seen.add(slot)
             if not toks:
                 raise ValueError("an entry of a step has no tokens")
-            for t in toks:
-                if not 0 <= t < self.vocab_size:
-                    raise ValueError(f"token id {t} is outside the vocabulary of {self.vocab_size}")
+            if min(toks) < 0 or max(toks) >= self.vocab_size:
+                bad = next(t for t in toks if not 0 <= t < self.vocab_size)
+                raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
             if self.cache.length(slot) + len(toks) > self.max_context:
                 raise ValueError(f"sequence would reach {self.cache.length(slot) + len(toks)} positions; "
                                  f"max context is {self.max_context}")
@@ -124,7 +124,7 @@ class Engine:
         n_want = sum(len(w) for w in want)
         n_total = sum(len(t) for _, t in entries)
         decode = all(len(t) == 1 for _, t in entries) and all(w == [0] for w in want)
-        if decode and self.use_graphs and out is None:
+        if decode and out is None:
             return self._decode_step(entries, want)
         logits = out if out is not None else torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device)
         if n_total <= self.max_step_tokens:
@@ -161,34 +161,52 @@ class Engine:
             yield cur_e, cur_w
 
     def _decode_step(self, entries, want):
-        """One token per sequence: replayed from a CUDA graph captured per batch size."""
-        B = len(entries)
+        return self.decode([s for s, _ in entries], [t[0] for _, t in entries], reserved=True)
+
+    def decode_token_buffer(self, batch: int) -> torch.Tensor:
+        """Where a decode step of ``batch`` sequences reads its token ids on the device: a kernel (the
+        sampler of the previous step) may write them there instead of the host uploading them."""
+        return self.planner._layout(batch, batch, batch)[1]["token_ids"]
+
+    def decode(self, slots: Sequence[int], tokens: Optional[Sequence[int]] = None, reserved: bool = False) -> torch.Tensor:
+        """One token for each sequence of ``slots`` (replayed from a CUDA graph captured per batch size);
+        returns float32 logits [len(slots), vocab]. With ``tokens`` None the ids are those already in
+        ``decode_token_buffer(len(slots))``."""
+        B = len(slots)
+        if not reserved:
+            for s in slots:
+                if self.cache.length(s) + 1 > self.max_context:
+                    raise ValueError(f"sequence would reach {self.cache.length(s) + 1} positions; max context is {self.max_context}")
+            self.cache.reserve([(s, 1) for s in slots])
         logits = self._logits.get(B)
         if logits is None:
             logits = self._logits[B] = torch.empty((B, self.vocab_size), dtype=torch.float32, device=self.device)
-        ctx = self.planner.plan(entries, want)
-        if self._graph_generation != self.rt.generation:
-            # A scratch buffer was reallocated since the graphs were captured (a larger step came
-            # through): they point at freed memory and are captured again.
-            self._graphs.clear()
-        graph = self._graphs.get(B)
-        if graph is None:
-            # First step of this size runs eagerly (it sizes the scratch buffers), then a capture
-            # of the same launches replaces it; the capture recomputes the same values.
+        ctx = self.planner.plan_decode(slots, tokens)
+        if not self.use_graphs:
             self.model.forward(ctx, self.cache, logits)
-            torch.cuda.current_stream().synchronize()
-            from ..kernels import library
-            before = library.launch_count
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self.model.forward(ctx, self.cache, logits)
-            self._graphs[B] = graph
-            self._graph_generation = self.rt.generation
-            self._graph_launches[B] = library.launch_count - before
         else:
-            graph.replay()
-        for s, t in entries:
-            self.cache.advance(s, 1)
+            if self._graph_generation != self.rt.generation:
+                # A scratch buffer was reallocated since the graphs were captured (a larger step came
+                # through): they point at freed memory and are captured again.
+                self._graphs.clear()
+            graph = self._graphs.get(B)
+            if graph is None:
+                # First step of this size runs eagerly (it sizes the scratch buffers), then a capture
+                # of the same launches replaces it; the capture recomputes the same values.
+                self.model.forward(ctx, self.cache, logits)
+                torch.cuda.current_stream().synchronize()
+                from ..kernels import library
+                before = library.launch_count
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self.model.forward(ctx, self.cache, logits)
+                self._graphs[B] = graph
+                self._graph_generation = self.rt.generation
+                self._graph_launches[B] = library.launch_count - before
+            else:
+                graph.replay()
+        for s in slots:
+            self.cache.lengths[s] += 1
         return logits
 
     def decode_launches(self, batch: int) -> int:

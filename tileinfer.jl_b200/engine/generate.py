@@ -73,32 +73,56 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 256
                         cache.page_size, engine.max_context)
     sampler = DeviceSampler(cache.max_seqs, engine.device)
     for batch in plan.batches:
-        live = list(batch)                               # request indices, in batch order
-        slots = {r: engine.new_sequence() for r in live}
+        slots = {r: engine.new_sequence() for r in batch}
         try:
-            sampler.reset([sequence_seed(seed, r) for r in live])
-            logits = engine.step([(slots[r], prompts[r]) for r in live])
-            while live:
-                tokens = sampler.sample(logits, sampling).tolist()
-                keep_rows, next_live, next_tokens = [], [], []
-                for row, (r, t) in enumerate(zip(live, tokens)):
-                    verdict = finished(t, len(results[r]), max_new_tokens, stop)
-                    if verdict != "stop":
-                        results[r].append(t)
-                        if on_token is not None:
-                            on_token(r, t)
-                    if verdict == "go":
-                        keep_rows.append(row); next_live.append(r); next_tokens.append(t)
-                    else:
-                        engine.free_sequence(slots.pop(r))
-                if not next_live:
-                    break
-                if len(next_live) != len(live):
-                    sampler.keep_rows(keep_rows)
-                live = next_live
-                logits = engine.step([(slots[r], [t]) for r, t in zip(live, next_tokens)])
+            sampler.reset([sequence_seed(seed, r) for r in batch])
+            logits = engine.step([(slots[r], prompts[r]) for r in batch])
+            _decode_batch(engine, sampler, sampling, list(batch), slots, logits, results, max_new_tokens, stop, on_token)
             engine.check_health()
         finally:
             for r in list(slots):
                 engine.free_sequence(slots.pop(r))
     return results
+
+
+def _decode_batch(engine, sampler, sampling, live, slots, logits, results, max_new_tokens, stop, on_token):
+    """Decode one batch to its end, with the host one step behind the device.
+
+    Step k+1 is put on the stream BEFORE the host has seen the tokens sampled after step k: its ids are
+    gathered on the device from the sampler's output, and its batch is every sequence that still has
+    budget, assuming that none of them just sampled a stop token. The host then reads the tokens of
+    step k while the device runs step k+1. A sequence that did sample a stop token has run through one
+    step too many; its row is ignored from then on and it leaves the batch one step later, which
+    changes nothing for the others. AntoineBut/TileInfer.jl pipelines its decode loop the same way
+    for one sequence (src/engine/runner.jl:157-191)."""
+    import torch
+    dead = set()                                       # requests known to have ended, possibly still a row of `logits`
+    while live:
+        tokens_dev = sampler.sample(logits, sampling)
+        host, ready = sampler.fetch_async(tokens_dev)
+        rows = [row for row, r in enumerate(live) if r not in dead and len(results[r]) + 1 < max_new_tokens]
+        nxt = [live[row] for row in rows]
+        next_logits = None
+        if nxt:
+            ids = engine.decode_token_buffer(len(nxt))
+            if len(rows) == len(live):
+                ids.copy_(tokens_dev)
+            else:
+                keep = torch.tensor(rows, dtype=torch.long, device=engine.device)
+                ids.copy_(tokens_dev[keep])
+                sampler.keep_rows(rows)
+            next_logits = engine.decode([slots[r] for r in nxt], None)
+        ready.synchronize()
+        tokens = host.tolist()
+        for row, r in enumerate(live):
+            if r in dead:
+                continue
+            verdict = finished(tokens[row], len(results[r]), max_new_tokens, stop)
+            if verdict != "stop":
+                results[r].append(tokens[row])
+                if on_token is not None:
+                    on_token(r, tokens[row])
+            if verdict != "go":
+                dead.add(r)
+                engine.free_sequence(slots.pop(r))
+        live, logits = nxt, next_logits

@@ -12,6 +12,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 
@@ -52,7 +53,11 @@ class StepContext:
 
 
 class StepPlanner:
-    """Builds StepContexts into a fixed device buffer through two alternating pinned staging buffers."""
+    """Builds StepContexts into a fixed device buffer through two alternating pinned staging buffers.
+
+    The layout of the buffer depends only on (tokens, sequences, wanted rows), so a decode step of a
+    given batch size always finds its values at the same addresses (what a captured graph needs), and
+    the tensor views of a layout are made once and reused."""
 
     def __init__(self, cache, max_step_tokens: int, device):
         self.cache = cache
@@ -63,77 +68,122 @@ class StepPlanner:
         self.capacity = cap
         pin = self.device.type == "cuda"
         self.staging = [torch.zeros(cap, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self.staging_np = [t.numpy() for t in self.staging]
         self.events = [None, None]
         self.turn = 0
         self.meta = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self.runtime = None
         self.last_upload_bytes = 0
+        self._layouts = {}
+        self._tables_np = [g.host_table.numpy() for g in cache.paged_groups]
 
-    def plan(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Sequence[Sequence[int]]) -> StepContext:
-        """``entries``: (slot, new tokens) per sequence; ``want[i]``: offsets into entry i's tokens.
-        Pages must already be reserved; lengths are those before the step."""
-        cache = self.cache
-        n = sum(len(t) for _, t in entries)
-        B = len(entries)
-        nw = sum(len(w) for w in want)
-        if n > self.max_step_tokens:
-            raise ValueError(f"a step of {n} tokens exceeds max_step_tokens {self.max_step_tokens}")
-        turn = self.turn
-        self.turn ^= 1
-        if self.events[turn] is not None:
-            self.events[turn].synchronize()
-        st = self.staging[turn]
-        a_n, a_b = _align(n), _align(B + 1)
+    def _layout(self, n: int, B: int, nw: int):
+        """Segment offsets and device views for a step of n tokens, B sequences, nw wanted rows."""
+        key = (n, B, nw)
+        lay = self._layouts.get(key)
+        if lay is not None:
+            return lay
         off = 0
         def seg(length):
             nonlocal off
             o = off
             off += _align(length)
             return o
-        o_ids, o_pos, o_slot = seg(n), seg(n), seg(n)
-        o_maps = [seg(n) for _ in cache.paged_groups]
-        o_seq, o_cu, o_kv, o_want = seg(B), seg(B + 1), seg(B), seg(nw)
-        ids_l, pos_l, slot_l, want_l = [], [], [], []
-        maps = [[] for _ in cache.paged_groups]
-        cu = [0]
-        starts, q_lens, slots = [], [], []
-        for i, (slot, toks) in enumerate(entries):
-            start = cache.length(slot)
-            m = len(toks)
-            ids_l.extend(toks)
-            pos_l.extend(range(start, start + m))
-            slot_l.extend([slot] * m)
-            for gi, g in enumerate(cache.paged_groups):
-                table, P = g.tables.get(slot, ()), g.page_size
-                maps[gi].extend(table[p // P] * P + p % P for p in range(start, start + m))
-            for w in want[i]:
-                if not 0 <= w < m:
-                    raise ValueError(f"wanted position {w} is outside the {m} tokens of entry {i}")
-                want_l.append(cu[-1] + w)
-            cu.append(cu[-1] + m)
-            starts.append(start); q_lens.append(m); slots.append(slot)
-        def put(o, values):
-            if values:
-                st[o:o + len(values)] = torch.tensor(values, dtype=torch.int32)
-        put(o_ids, ids_l); put(o_pos, pos_l); put(o_slot, slot_l)
-        for gi in range(len(maps)):
-            put(o_maps[gi], maps[gi])
-        put(o_seq, slots); put(o_cu, cu); put(o_kv, [s + q for s, q in zip(starts, q_lens)]); put(o_want, want_l)
-        self.meta[:off].copy_(st[:off], non_blocking=True)
-        self.last_upload_bytes = off * 4
+        o = {"ids": seg(n), "pos": seg(n), "slot": seg(n)}
+        o["maps"] = [seg(n) for _ in self.cache.paged_groups]
+        o["seq"], o["cu"], o["kv"], o["want"] = seg(B), seg(B + 1), seg(B), seg(nw)
+        o["end"] = off
+        m = self.meta
+        views = dict(
+            token_ids=m[o["ids"]:o["ids"] + n], positions=m[o["pos"]:o["pos"] + n], tok_slot=m[o["slot"]:o["slot"] + n],
+            seq_slots=m[o["seq"]:o["seq"] + B], cu_seqlens=m[o["cu"]:o["cu"] + B + 1], kv_lens=m[o["kv"]:o["kv"] + B],
+            want_idx=m[o["want"]:o["want"] + nw],
+            groups={g.index: GroupMeta(m[o["maps"][gi]:o["maps"][gi] + n], g.device_table)
+                    for gi, g in enumerate(self.cache.paged_groups)})
+        if len(self._layouts) > 256:
+            self._layouts.clear()
+        lay = self._layouts[key] = (o, views)
+        return lay
+
+    def _staging(self):
+        turn = self.turn
+        self.turn ^= 1
+        if self.events[turn] is not None:
+            self.events[turn].synchronize()          # the copy that last read this buffer has finished
+        return turn, self.staging_np[turn]
+
+    def _upload(self, turn: int, count: int, skip_ids: int = 0):
+        """One copy of the first ``count`` words (without the first ``skip_ids`` when the token ids are
+        written on the device)."""
+        self.meta[skip_ids:count].copy_(self.staging[turn][skip_ids:count], non_blocking=True)
+        self.last_upload_bytes = (count - skip_ids) * 4
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
             self.events[turn] = ev
-        m = self.meta
-        return StepContext(
-            n_tokens=n, n_seqs=B, n_want=nw,
-            token_ids=m[o_ids:o_ids + n], positions=m[o_pos:o_pos + n], tok_slot=m[o_slot:o_slot + n],
-            seq_slots=m[o_seq:o_seq + B], cu_seqlens=m[o_cu:o_cu + B + 1], kv_lens=m[o_kv:o_kv + B],
-            want_idx=m[o_want:o_want + nw],
-            groups={g.index: GroupMeta(m[o_maps[gi]:o_maps[gi] + n], g.device_table) for gi, g in enumerate(cache.paged_groups)},
-            host_slots=slots, host_q_lens=q_lens, host_starts=starts,
-            is_decode=all(q == 1 for q in q_lens), max_q_len=max(q_lens, default=0),
-            max_kv_len=max((s + q for s, q in zip(starts, q_lens)), default=0),
-            runtime=self.runtime,
-        )
+
+    def plan(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Sequence[Sequence[int]]) -> StepContext:
+        """``entries``: (slot, new tokens) per sequence; ``want[i]``: offsets into entry i's tokens.
+        Pages must already be reserved; lengths are those before the step."""
+        cache = self.cache
+        q_lens = [len(t) for _, t in entries]
+        n, B = sum(q_lens), len(entries)
+        nw = sum(len(w) for w in want)
+        if n > self.max_step_tokens:
+            raise ValueError(f"a step of {n} tokens exceeds max_step_tokens {self.max_step_tokens}")
+        o, views = self._layout(n, B, nw)
+        turn, st = self._staging()
+        slots = [s for s, _ in entries]
+        starts = [cache.length(s) for s in slots]
+        row = 0
+        wrow = o["want"]
+        for i, (slot, toks) in enumerate(entries):
+            m, start = q_lens[i], starts[i]
+            pos = np.arange(start, start + m, dtype=np.int64)
+            st[o["ids"] + row:o["ids"] + row + m] = toks
+            st[o["pos"] + row:o["pos"] + row + m] = pos
+            st[o["slot"] + row:o["slot"] + row + m] = slot
+            for gi, g in enumerate(cache.paged_groups):
+                P = g.page_size
+                st[o["maps"][gi] + row:o["maps"][gi] + row + m] = self._tables_np[gi][slot, pos // P].astype(np.int64) * P + pos % P
+            for w in want[i]:
+                if not 0 <= w < m:
+                    raise ValueError(f"wanted position {w} is outside the {m} tokens of entry {i}")
+                st[wrow] = row + w
+                wrow += 1
+            st[o["cu"] + i] = row
+            row += m
+        st[o["cu"] + B] = row
+        st[o["seq"]:o["seq"] + B] = slots
+        st[o["kv"]:o["kv"] + B] = [a + b for a, b in zip(starts, q_lens)]
+        self._upload(turn, o["end"])
+        return StepContext(n_tokens=n, n_seqs=B, n_want=nw, host_slots=slots, host_q_lens=q_lens, host_starts=starts,
+                           is_decode=all(q == 1 for q in q_lens), max_q_len=max(q_lens, default=0),
+                           max_kv_len=max((a + b for a, b in zip(starts, q_lens)), default=0), runtime=self.runtime, **views)
+
+    def plan_decode(self, slots: Sequence[int], tokens: Optional[Sequence[int]]) -> StepContext:
+        """One token for each of ``slots``, the last (only) token's logits wanted. With ``tokens`` None
+        the ids are left to a kernel that writes them into ``token_ids`` on the device (the sampler of
+        the previous step), and only the rest is uploaded."""
+        cache = self.cache
+        B = len(slots)
+        o, views = self._layout(B, B, B)
+        turn, st = self._staging()
+        slot_arr = np.asarray(slots, dtype=np.int64)
+        starts = np.fromiter((cache.lengths[s] for s in slots), dtype=np.int64, count=B)
+        if tokens is not None:
+            st[o["ids"]:o["ids"] + B] = tokens
+        st[o["pos"]:o["pos"] + B] = starts
+        st[o["slot"]:o["slot"] + B] = slot_arr
+        for gi, g in enumerate(cache.paged_groups):
+            P = g.page_size
+            st[o["maps"][gi]:o["maps"][gi] + B] = self._tables_np[gi][slot_arr, starts // P].astype(np.int64) * P + starts % P
+        ar = np.arange(B + 1)
+        st[o["cu"]:o["cu"] + B + 1] = ar
+        st[o["seq"]:o["seq"] + B] = slot_arr
+        st[o["kv"]:o["kv"] + B] = starts + 1
+        st[o["want"]:o["want"] + B] = ar[:B]
+        self._upload(turn, o["end"], skip_ids=_align(B) if tokens is None else 0)
+        starts_l = starts.tolist()
+        return StepContext(n_tokens=B, n_seqs=B, n_want=B, host_slots=list(slots), host_q_lens=[1] * B, host_starts=starts_l,
+                           is_decode=True, max_q_len=1, max_kv_len=max(starts_l, default=0) + 1, runtime=self.runtime, **views)

@@ -49,7 +49,7 @@ _SIGNATURES = {
     "ti_attention_inputs": [_P, _L, _P, _P, _P, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_attention_plain": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_gemm_plain": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P],
-    "ti_argmax": [_P, _L, _I, _I, _P, _P],
+    "ti_argmax": [_P, _L, _I, _I, _P, _P, _P, _P, _P],
     "ti_sample": [_P, _L, _I, _I, _F, _I, _F, _P, _P, _P, _P],
 }
 
@@ -68,11 +68,14 @@ def lib():
     handle.ti_last_error.argtypes = []
     handle.ti_sampling_uniform.restype = c_float
     handle.ti_sampling_uniform.argtypes = [_U, _U]
+    handle.ti_argmax_chunks.restype = c_int
+    handle.ti_argmax_chunks.argtypes = [c_int]
     class _Lib:
         pass
     wrapped = _Lib()
     wrapped.ti_last_error = handle.ti_last_error
     wrapped.ti_sampling_uniform = handle.ti_sampling_uniform
+    wrapped.ti_argmax_chunks = handle.ti_argmax_chunks
     wrapped.handle = handle
     for name, args in _SIGNATURES.items():
         fn = getattr(handle, name)

@@ -129,10 +129,28 @@ def gemm_plain(y, x, w, epilogue=EPI_NONE, act=(0.0, 0.0, 0.0, 0.0)):
                               act[0], act[1], act[2], act[3], dtype_code(x.dtype), _stream()), "gemm_plain")
 
 
-def argmax(logits, out):
+_argmax_ws = {}
+
+
+def argmax_workspace(rows: int, vocab: int, device):
+    """(values, ids, counters) for ``argmax`` over ``rows`` rows: one per device, grown on demand. The
+    counters start at zero and every launch leaves them at zero."""
+    chunks = lib().ti_argmax_chunks(vocab)
+    key = str(device)
+    ws = _argmax_ws.get(key)
+    if ws is None or ws[0].numel() < rows * chunks or ws[2].numel() < rows:
+        n = max(rows, 64)
+        ws = _argmax_ws[key] = (torch.empty(n * 256, dtype=torch.float32, device=device),
+                                torch.empty(n * 256, dtype=torch.int32, device=device),
+                                torch.zeros(n, dtype=torch.int32, device=device))
+    return ws
+
+
+def argmax(logits, out, workspace=None):
     _need(logits, "logits", torch.float32, contiguous=False); _need(out, "out", torch.int32)
+    val, idx, cnt = workspace or argmax_workspace(logits.shape[0], logits.shape[1], logits.device)
     check(lib().ti_argmax(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], out.data_ptr(),
-                          _stream()), "argmax")
+                          val.data_ptr(), idx.data_ptr(), cnt.data_ptr(), _stream()), "argmax")
 
 
 def sample(logits, out, temperature, top_k, top_p, seeds, counters):

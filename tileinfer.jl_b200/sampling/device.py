@@ -26,6 +26,9 @@ class DeviceSampler:
         self.seeds = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self.counters = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self.tokens = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        pin = torch.device(device).type == "cuda"
+        self._host = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
+        self._turn = 0
 
     def reset(self, seeds: Sequence[int], counters: Sequence[int] = None) -> None:
         """Row i samples with seeds[i] from counter counters[i] (0 by default)."""
@@ -39,6 +42,17 @@ class DeviceSampler:
         n = len(rows)
         self.seeds[:n] = self.seeds[idx]
         self.counters[:n] = self.counters[idx]
+
+    def fetch_async(self, tokens: torch.Tensor):
+        """Start copying sampled tokens to pinned host memory; returns (host tensor, event). The host reads
+        them after ``event.synchronize()``, which can be one step later."""
+        n = tokens.shape[0]
+        host = self._host[self._turn][:n]
+        self._turn ^= 1
+        host.copy_(tokens, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return host, ev
 
     def sample(self, logits: torch.Tensor, params: SamplingParams) -> torch.Tensor:
         """Tokens [rows] (int32, on the device) for float32 logits [rows, vocab]."""
