@@ -106,7 +106,8 @@ def decode_splits(batch: int, kv_heads: int, max_context: int) -> int:
     """Split count of decode attention: fixed by the batch size alone, so that a captured step
     stays valid whatever the lengths are (the reference fixes it per model:
     src/ops/tile/attention.jl:250-263)."""
-    want = -(-2 * SM_COUNT // max(1, batch * kv_heads))
+    # Two blocks fit an SM: at most 2 x 148 blocks, so that none has to wait for a second wave.
+    want = (2 * SM_COUNT) // max(1, batch * kv_heads)
     return max(1, min(want, 32, -(-max_context // 64)))
 
 
