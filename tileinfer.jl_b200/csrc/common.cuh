@@ -122,9 +122,10 @@ struct XieluParams {
 };
 template <typename T> __device__ __forceinline__ float xielu_value(float x, const XieluParams& a) {
     const float bx = rnd<T>(a.beta * x);
-    if (x > 0.f) return rnd<T>(rnd<T>(rnd<T>(a.alpha_p * x) * x) + bx);
+    const float pos = rnd<T>(rnd<T>(rnd<T>(a.alpha_p * x) * x) + bx);
     const float e = rnd<T>(expm1f(fminf(x, a.eps)));
-    return rnd<T>(rnd<T>(rnd<T>(e - x) * a.alpha_n) + bx);
+    const float neg = rnd<T>(rnd<T>(rnd<T>(e - x) * a.alpha_n) + bx);
+    return x > 0.f ? pos : neg;                // both sides are computed: no branch, elements interleave
 }
 
 // 16 bytes of elements, widened to float on load and rounded once on store.

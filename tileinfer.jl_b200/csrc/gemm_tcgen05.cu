@@ -12,7 +12,7 @@
 //
 // One persistent block per SM walks output tiles (token tile fastest, so the blocks that
 // run together share weight tiles in L2). Warp 0 produces (TMA), warp 1 issues the MMAs,
-// warps 2-5 run the epilogue on one of two accumulator buffers in tensor memory while the
+// warps 2-9 run the epilogue on one of two accumulator buffers in tensor memory while the
 // MMAs of the next tile fill the other. A product with few output tiles can be split over
 // k; the 32-bit partial sums [split, n, out] are added by the residual-add + RMSNorm kernel.
 // Epilogues: round to bfloat16; xIELU on the rounded sums; 32-bit logits; raw partials.
@@ -33,7 +33,8 @@ namespace {
 
 constexpr int BM = 128;            // weight rows per tile (tensor-memory lanes)
 constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;        // two per tensor-memory lane quarter, each takes half of the columns
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
@@ -48,13 +49,19 @@ struct Params {
     int* status;
 };
 
-template <int BN> struct Cfg {
-    static constexpr int A_BYTES = BM * BK * 2;
+// MT: 128-row weight sub-tiles per block. With MT = 2 a block owns 256 weight rows: the token
+// operand staged for a k block feeds two MMAs, so a k block moves 64 KB for 1024 tensor-core cycles
+// instead of 48 KB for 512, which is what the L2 -> shared-memory path can sustain. Both accumulators
+// then fill tensor memory (2 x 256 columns), so the epilogue of a tile is not overlapped with the next
+// tile's MMAs; it is about a tenth of a tile's time.
+template <int BN, int MT> struct Cfg {
+    static constexpr int A_BYTES = MT * BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES_FIT = (SMEM_LIMIT - 2048) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
-    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int ACC_BUFS = MT == 2 ? 1 : 2;
+    static constexpr int TMEM_COLS = ACC_BUFS * MT * BN < 32 ? 32 : ACC_BUFS * MT * BN;
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
@@ -166,11 +173,11 @@ struct TileIter {
     }
 };
 
-template <int BN>
+template <int BN, int MT>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x,
                                                                  void* __restrict__ y, Params p) {
-    typedef Cfg<BN> C;
+    typedef Cfg<BN, MT> C;
     extern __shared__ unsigned char smem_dyn[];
     // Swizzled tiles need 1024-byte alignment.
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -184,7 +191,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(smem_addr(tmem_slot), C::TMEM_COLS);
@@ -214,7 +221,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                     const unsigned bar = full0 + 8 * stage;
                     mbar_expect_tx(bar, C::STAGE_BYTES);
                     const unsigned a_dst = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_w, kb * BK, it.m * BM, bar);
+#pragma unroll
+                    for (int h = 0; h < MT; ++h)
+                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, kb * BK, (it.m * MT + h) * BM, bar);
                     tma_load_2d(a_dst + C::A_BYTES, &map_x, kb * BK, it.n * BN, bar);
                 }
                 __syncwarp();
@@ -228,23 +237,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         int local = 0;
         bool ok = true;
         while (ok && it.next(p)) {
-            const int acc = local & 1;
-            const unsigned acc_phase = (local >> 1) & 1;
+            const int acc = C::ACC_BUFS == 2 ? (local & 1) : 0;
+            const unsigned acc_phase = C::ACC_BUFS == 2 ? ((local >> 1) & 1) : (local & 1);
             ok = __all_sync(0xffffffffu, mbar_wait(acce0 + 8 * acc, acc_phase ^ 1, p.status, 2));
             if (!ok) break;
             tc_fence_after();
-            const unsigned d_tmem = tmem_base + (unsigned)(acc * BN);
+            const unsigned d_tmem = tmem_base + (unsigned)(acc * MT * BN);
             for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
                 ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, p.status, 3));
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
                     const unsigned a_addr = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
-                    const unsigned long long da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + C::A_BYTES);
+                    const unsigned long long db = smem_desc_sw128(a_addr + C::A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)      // 16 k = 32 bytes further along the swizzled row
-                        umma_bf16(d_tmem, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k),
-                                  instr_desc<BN>(), (kb > it.kb_lo || k > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int h = 0; h < MT; ++h)       // the sub-tiles share the token operand
+                            umma_bf16(d_tmem + (unsigned)(h * BN), smem_desc_sw128(a_addr + h * (BM * BK * 2)) + (unsigned long long)(2 * k),
+                                      db + (unsigned long long)(2 * k), instr_desc<BN>(), (kb > it.kb_lo || k > 0) ? 1u : 0u);
                     umma_commit(empty0 + 8 * stage);       // the stage is free once these MMAs have read it
                 }
                 __syncwarp();
@@ -256,43 +267,55 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
             ++local;
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (4 warps)
+        // ---------------------------------------------------------------- epilogue (8 warps)
         const int quarter = warp & 3;                      // the tensor-memory lanes this warp may read
+        const int col_half = (warp - 2) >> 2;              // which half of the columns (chunks alternate)
         int local = 0;
         bool ok = true;
         while (ok && it.next(p)) {
-            const int acc = local & 1;
-            const unsigned acc_phase = (local >> 1) & 1;
+            const int acc = C::ACC_BUFS == 2 ? (local & 1) : 0;
+            const unsigned acc_phase = C::ACC_BUFS == 2 ? ((local >> 1) & 1) : (local & 1);
             ok = __all_sync(0xffffffffu, mbar_wait(accf0 + 8 * acc, acc_phase, p.status, 4));
             if (!ok) break;
             tc_fence_after();
-            const int m = it.m * BM + quarter * 32 + lane;
             const int n0 = it.n * BN;
             const int n_valid = min(BN, p.N - n0);
-            const unsigned t_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN);
             constexpr int CH = BN >= 32 ? 32 : 16;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += CH) {
+            for (int h = 0; h < MT; ++h) {
+            const int m = (it.m * MT + h) * BM + quarter * 32 + lane;
+            const unsigned t_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)((acc * MT + h) * BN);
+#pragma unroll 1
+            for (int c = col_half * CH; c < BN; c += 2 * CH) {
                 if (c >= n_valid) break;                   // uniform across the warp
                 unsigned r[32];
                 if (CH == 32) tmem_ld32(t_row + c, r); else tmem_ld16(t_row + c, r);
                 tmem_ld_wait();
-                if (m < p.M) {
+                // All values of the chunk first, without branches (one warp per scheduler runs this: only
+                // independent elements in flight hide the latency of the arithmetic), then the stores.
+                float v[32];
 #pragma unroll
-                    for (int j = 0; j < CH; ++j) {
-                        const int n = n0 + c + j;
-                        if (c + j >= n_valid) break;
-                        const float s = __uint_as_float(r[j]);
-                        if (p.epilogue == EPI_PARTIAL) {
-                            ((float*)y)[((size_t)it.split * p.N + n) * p.ldy + m] = s;
-                        } else {
-                            float v = rnd<bf16>(s);
-                            if (p.epilogue == EPI_XIELU) v = xielu_value<bf16>(v, p.act);
-                            if (p.epilogue == EPI_F32) ((float*)y)[(size_t)n * p.ldy + m] = v;
-                            else ((bf16*)y)[(size_t)n * p.ldy + m] = __float2bfloat16_rn(v);
-                        }
+                for (int j = 0; j < CH; ++j) {
+                    const float s = __uint_as_float(r[j]);
+                    const float q = rnd<bf16>(s);
+                    v[j] = p.epilogue == EPI_PARTIAL ? s : (p.epilogue == EPI_XIELU ? xielu_value<bf16>(q, p.act) : q);
+                }
+                if (m < p.M) {
+                    if (p.epilogue == EPI_PARTIAL) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j)
+                            if (c + j < n_valid) ((float*)y)[((size_t)it.split * p.N + n0 + c + j) * p.ldy + m] = v[j];
+                    } else if (p.epilogue == EPI_F32) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j)
+                            if (c + j < n_valid) ((float*)y)[(size_t)(n0 + c + j) * p.ldy + m] = v[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j)
+                            if (c + j < n_valid) ((bf16*)y)[(size_t)(n0 + c + j) * p.ldy + m] = __float2bfloat16_rn(v[j]);
                     }
                 }
+            }
             }
             tc_fence_before();
             __syncwarp();
@@ -362,17 +385,17 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
     return 0;
 }
 
-template <int BN>
+template <int BN, int MT>
 int launch(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN, MT>::SMEM);
         if (e != cudaSuccess) return ti_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
         configured = true;
     }
     const int tiles = p.m_tiles * p.n_tiles * p.splits;
     const int grid = tiles < sm_count ? tiles : sm_count;
-    ti_launch(gemm_tcgen05_kernel<BN>, dim3(grid), dim3(THREADS), Cfg<BN>::SMEM, stream, mw, mx, y, p);
+    ti_launch(gemm_tcgen05_kernel<BN, MT>, dim3(grid), dim3(THREADS), Cfg<BN, MT>::SMEM, stream, mw, mx, y, p);
     return ti_check_launch("gemm_tcgen05");
 }
 
@@ -401,7 +424,17 @@ extern "C" int ti_gemm_tcgen05(void* y, long long ldy, const void* x, long long 
     const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
     Params p;
     p.M = out; p.N = n; p.K = in;
-    p.m_tiles = (out + BM - 1) / BM;
+    // Wide token tiles take 256 weight rows per block when that is the cheaper way to cover the
+    // product: a 256-row tile costs about 1.5 times a 128-row tile (its MMAs are better fed), plus an
+    // epilogue that is not overlapped, which only a long k amortises (measured: even at k = 4096).
+    int mt = 1;
+    if (bn == 256 && in >= 8192) {
+        const long long n_t = (n + bn - 1) / bn;
+        const long long waves1 = (((out + BM - 1) / BM) * n_t + sm_count - 1) / sm_count;
+        const long long waves2 = (((out + 2 * BM - 1) / (2 * BM)) * n_t + sm_count - 1) / sm_count;
+        if (3 * waves2 < 2 * waves1 && splits <= 1) mt = 2;
+    }
+    p.m_tiles = (out + mt * BM - 1) / (mt * BM);
     p.n_tiles = (n + bn - 1) / bn;
     p.k_blocks = (in + BK - 1) / BK;
     p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
@@ -411,9 +444,9 @@ extern "C" int ti_gemm_tcgen05(void* y, long long ldy, const void* x, long long 
     if (int rc = tensor_map(&mw, W, out, in, in, BM)) return rc;
     if (int rc = tensor_map(&mx, x, n, in, ldx, bn)) return rc;
     switch (bn) {
-        case 256: return launch<256>(y, mw, mx, p, sm_count, stream);
-        case 128: return launch<128>(y, mw, mx, p, sm_count, stream);
-        case 64: return launch<64>(y, mw, mx, p, sm_count, stream);
-        default: return launch<32>(y, mw, mx, p, sm_count, stream);
+        case 256: return mt == 2 ? launch<256, 2>(y, mw, mx, p, sm_count, stream) : launch<256, 1>(y, mw, mx, p, sm_count, stream);
+        case 128: return launch<128, 1>(y, mw, mx, p, sm_count, stream);
+        case 64: return launch<64, 1>(y, mw, mx, p, sm_count, stream);
+        default: return launch<32, 1>(y, mw, mx, p, sm_count, stream);
     }
 }

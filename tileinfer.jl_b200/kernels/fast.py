@@ -49,7 +49,6 @@ def linear(lin, x, out, epilogue, act, allow_partials=False):
 
 
 _status = None
-TC_FUSED_XIELU_MAX_TOKENS = 64
 
 
 def status_word() -> torch.Tensor:
@@ -89,16 +88,11 @@ def _tcgen05(lin, x, out, epilogue, act, allow_partials):
             return None
         check(rc, "gemm_tcgen05")
         return partials
-    # The activation rides in the epilogue only for small token counts: on a wide tile the four
-    # epilogue warps cannot hide expm1 behind the MMAs, and a separate pass over the output is cheaper.
-    fused = epilogue if (epilogue != ops.EPI_XIELU or n <= TC_FUSED_XIELU_MAX_TOKENS) else ops.EPI_NONE
     rc = lib().ti_gemm_tcgen05(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), w.data_ptr(), n,
-                               lin.out_features, k, 1, fused, act[0], act[1], act[2], act[3], st.data_ptr(), _stream())
+                               lin.out_features, k, 1, epilogue, act[0], act[1], act[2], act[3], st.data_ptr(), _stream())
     if rc == 2:
         return None
     check(rc, "gemm_tcgen05")
-    if fused != epilogue:
-        ops.xielu(out, out, *act)
     return out
 
 
