@@ -5,6 +5,7 @@
     python -m tileinfer_b200.kernels.microbench decode  --batch 8 --context 1024
     python -m tileinfer_b200.kernels.microbench prefill --tokens 2048
     python -m tileinfer_b200.kernels.microbench timeline --batch 1 --layers 8
+    python -m tileinfer_b200.kernels.microbench timeline --tokens 2048 --layers 4      (a prefill step)
 
 Products rotate over several weight matrices totalling more than the 126 MB L2, so weights
 come from HBM; the kernels are replayed from a CUDA graph (as in a decode step) and timed with
@@ -142,7 +143,7 @@ def bench_prefill_attention(tokens, once, heads=32, kv_heads=8, head_dim=128):
     print(f"prefill attention tokens={tokens}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s (causal)")
 
 
-def timeline(batch, layers, cached=1023):
+def timeline(batch, layers, cached=1023, prefill_tokens=0):
     from torch.profiler import ProfilerActivity, profile
 
     from ..config import ApertusConfig
@@ -153,12 +154,21 @@ def timeline(batch, layers, cached=1023):
         "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["head_dim"],
         "intermediate_size": s["intermediate"], "vocab_size": s["vocab"], "rope_theta": 12e6, "rms_norm_eps": 1e-5,
         "max_position_embeddings": 4096})
-    eng = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=4096, max_seqs=batch, max_tokens=batch * 1280)
-    slots = [eng.new_sequence() for _ in range(batch)]
-    eng.cache.reserve([(x, cached) for x in slots])
-    for x in slots:
-        eng.cache.advance(x, cached)
-    step = lambda: eng.step([(x, [1]) for x in slots])
+    eng = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=4096, max_seqs=max(batch, 1),
+                        max_tokens=max(batch * 1280, prefill_tokens + 64), max_step_tokens=max(prefill_tokens, 2048))
+    if prefill_tokens:
+        ids = torch.randint(0, s["vocab"], (prefill_tokens,)).tolist()
+
+        def step():
+            x = eng.new_sequence()
+            eng.step([(x, ids)])
+            eng.free_sequence(x)
+    else:
+        slots = [eng.new_sequence() for _ in range(batch)]
+        eng.cache.reserve([(x, cached) for x in slots])
+        for x in slots:
+            eng.cache.advance(x, cached)
+        step = lambda: eng.step([(x, [1]) for x in slots])
     for _ in range(4):
         step()
     torch.cuda.synchronize()
@@ -170,18 +180,19 @@ def timeline(batch, layers, cached=1023):
     evs.sort(key=lambda e: e.time_range.start)
     last = evs[-(len(evs) // 3):]
     t0 = last[0].time_range.start
-    print(f"batch {batch}, {layers} layers: {len(last)} kernels in one replayed decode step, "
+    what = f"prefill of {prefill_tokens} tokens" if prefill_tokens else f"replayed decode step of batch {batch}"
+    print(f"{layers} layers: {len(last)} kernels in one {what}, "
           f"{last[-1].time_range.end - t0:.1f} us from first start to last end")
     prev = None
     first_layer_end = 2 + 2 * 9
     for e in last[:first_layer_end]:
         gap = e.time_range.start - prev if prev is not None else 0.0
-        print(f"  {e.name.split('(')[0][-44:]:44s} start {e.time_range.start - t0:8.1f}  dur {e.time_range.end - e.time_range.start:6.1f}  "
+        print(f"  {(e.name.split('(')[0][-44:].replace('void', '').strip() or 'gemm_tcgen05_kernel'):44s} start {e.time_range.start - t0:8.1f}  dur {e.time_range.end - e.time_range.start:6.1f}  "
               f"gap to previous end {gap:6.1f}")
         prev = e.time_range.end
     total, count = collections.Counter(), collections.Counter()
     for e in last:
-        key = e.name.split("<")[0].split("(")[0].replace("void ", "")
+        key = e.name.split("<")[0].split("(")[0].replace("void ", "") or "gemm_tcgen05_kernel"
         total[key] += e.time_range.end - e.time_range.start
         count[key] += 1
     for key, v in total.most_common():
@@ -208,7 +219,7 @@ def main(argv=None):
     elif a.what == "prefill":
         bench_prefill_attention(a.tokens if a.tokens > 1 else 2048, a.once)
     else:
-        timeline(a.batch, a.layers)
+        timeline(a.batch, a.layers, prefill_tokens=a.tokens if a.tokens > 1 else 0)
     return 0
 
 
