@@ -8,11 +8,14 @@
 // (src/kv/paged_cache.jl:1-4).
 #include "common.cuh"
 
+#include <type_traits>
+
 #define AI_WARPS 4
 #define AI_MAX_D 512
 
 template <typename T>
-__global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, T* __restrict__ q_out,
+__global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, const float* partials, int n_partials,
+                                        long long partial_stride, T* __restrict__ q_out,
                                         T* __restrict__ k_cache, T* __restrict__ v_cache,
                                         const T* __restrict__ q_norm_w, const T* __restrict__ k_norm_w, float eps,
                                         const float* __restrict__ cos_sin, const int* positions,
@@ -31,7 +34,16 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, T* _
     if (head >= heads_total) return;
     float* buf = smem + warp * D;
 
-    const T* src = qkv + (size_t)t * qkv_stride + (size_t)head * D;
+    // The projection's output row: stored, or the sum (in split order, rounded once like any product)
+    // of the 32-bit partial sums [s][token][feature] of a product that was split over k.
+    const T* src = qkv != nullptr ? qkv + (size_t)t * qkv_stride + (size_t)head * D : nullptr;
+    const float* psrc = partials != nullptr ? partials + (size_t)t * qkv_stride + (size_t)head * D : nullptr;
+    auto value = [&](int d) -> float {
+        if (psrc == nullptr) return to_f32(__ldcg(src + d));
+        float v = __ldcg(psrc + d);
+        for (int s = 1; s < n_partials; ++s) v += __ldcg(psrc + (size_t)s * partial_stride + d);
+        return rnd<T>(v);
+    };
     const bool is_q = head < nq;
     const bool is_k = !is_q && head < nq + nkv;
     const int kvh = is_q ? 0 : (is_k ? head - nq : head - nq - nkv);
@@ -46,13 +58,13 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, T* _
         dst = base + (((size_t)page * nkv + kvh) * page_size + off) * D;
     }
     if (!is_q && !is_k) {                    // value head: a copy
-        for (int d = lane; d < D; d += 32) dst[d] = __ldcg(src + d);
+        for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(value(d));
         return;
     }
     const T* nw = is_q ? q_norm_w : k_norm_w;
     float ss = 0.f;
     for (int d = lane; d < D; d += 32) {
-        const float v = to_f32(__ldcg(src + d));
+        const float v = value(d);
         buf[d] = v;
         ss = fmaf(v, v, ss);
     }
@@ -76,18 +88,111 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, T* _
     }
 }
 
-extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, void* q_out, void* k_cache, void* v_cache,
+// The same for head sizes 64 and 128 in bfloat16 from a stored projection: a lane owns VPL = D/32
+// consecutive elements (one 4- or 8-byte access), the rotation partner i +- D/2 lives in lane +- 16 and
+// comes by shuffle, so no shared memory and no strided loops are needed.
+template <int VPL>
+__global__ void attention_inputs_vec_kernel(const bf16* qkv, long long qkv_stride, bf16* __restrict__ q_out,
+                                            bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                                            const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float eps,
+                                            const float* __restrict__ cos_sin, const int* positions, const int* slots,
+                                            int nq, int nkv, int page_size, int write_kv) {
+    constexpr int D = 32 * VPL;
+    typedef typename std::conditional<VPL == 4, uint2, unsigned>::type Pack;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int heads_total = nq + (write_kv ? 2 * nkv : 0);
+    const int head = blockIdx.y * AI_WARPS + warp;
+    const int slot_t = slots != nullptr ? __ldcg(slots + t) : 0;
+    const int pos_t = __ldcg(positions + t);
+    pdl_enter();
+    if (head >= heads_total) return;
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    const int kvh = is_q ? 0 : (is_k ? head - nq : head - nq - nkv);
+    bf16* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * nq + head) * D;
+    } else {
+        const int page = slot_t / page_size, off = slot_t - page * page_size;
+        dst = (is_k ? k_cache : v_cache) + (((size_t)page * nkv + kvh) * page_size + off) * D;
+    }
+    const Pack raw = __ldcg(reinterpret_cast<const Pack*>(qkv + (size_t)t * qkv_stride + (size_t)head * D) + lane);
+    if (!is_q && !is_k) {                    // value head: a copy
+        reinterpret_cast<Pack*>(dst)[lane] = raw;
+        return;
+    }
+    float v[VPL];
+    {
+        const unsigned* w = reinterpret_cast<const unsigned*>(&raw);
+#pragma unroll
+        for (int i = 0; i < VPL / 2; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    const bf16* nw = is_q ? q_norm_w : k_norm_w;
+    if (nw != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) ss = fmaf(v[i], v[i], ss);
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+        const Pack wraw = reinterpret_cast<const Pack*>(nw)[lane];
+        const unsigned* w = reinterpret_cast<const unsigned*>(&wraw);
+#pragma unroll
+        for (int i = 0; i < VPL / 2; ++i) {
+            v[2 * i] = rnd<bf16>(__uint_as_float(w[i] << 16) * rnd<bf16>(v[2 * i] * inv));
+            v[2 * i + 1] = rnd<bf16>(__uint_as_float(w[i] & 0xffff0000u) * rnd<bf16>(v[2 * i + 1] * inv));
+        }
+    }
+    if (cos_sin != nullptr) {
+        const float2* cs = reinterpret_cast<const float2*>(cos_sin + (size_t)pos_t * D) + (lane & 15) * VPL;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+            const float rot = lane < 16 ? -other : other;
+            const float2 c = cs[i];
+            v[i] = rnd<bf16>(v[i] * c.x) + rnd<bf16>(rot * c.y);
+        }
+    }
+    Pack outp;
+    unsigned* o = reinterpret_cast<unsigned*>(&outp);
+#pragma unroll
+    for (int i = 0; i < VPL / 2; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        o[i] = *reinterpret_cast<const unsigned*>(&h);
+    }
+    reinterpret_cast<Pack*>(dst)[lane] = outp;
+}
+
+extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, const float* partials, int n_partials,
+                                   long long partial_stride, void* q_out, void* k_cache, void* v_cache,
                                    const void* q_norm_w, const void* k_norm_w, float eps, const float* cos_sin,
                                    const int* positions, const int* slots, int n_tokens, int nq, int nkv, int D,
                                    int page_size, int write_kv, int dtype, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     TI_REQUIRE(D > 0 && D % 2 == 0 && D <= AI_MAX_D, "attention_inputs: head_dim %d must be even and at most %d", D, AI_MAX_D);
+    TI_REQUIRE((qkv != nullptr) != (partials != nullptr), "attention_inputs: give the projection's output or its partial sums");
     TI_REQUIRE(nq > 0 && nkv > 0 && page_size > 0, "attention_inputs: bad sizes nq=%d nkv=%d page=%d", nq, nkv, page_size);
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     dim3 grid(n_tokens, (heads_total + AI_WARPS - 1) / AI_WARPS);
     const size_t smem = (size_t)AI_WARPS * D * sizeof(float);
+    if (dtype == TI_BF16 && qkv != nullptr && (D == 64 || D == 128) && qkv_stride % 4 == 0 && aligned16(qkv) && aligned16(q_out) &&
+        (!write_kv || (aligned16(k_cache) && aligned16(v_cache))) && (q_norm_w == nullptr || aligned16(q_norm_w)) &&
+        (k_norm_w == nullptr || aligned16(k_norm_w)) && (cos_sin == nullptr || aligned16(cos_sin))) {
+        if (D == 128)
+            ti_launch(attention_inputs_vec_kernel<4>, grid, dim3(AI_WARPS * 32), 0, stream, (const bf16*)qkv, qkv_stride, (bf16*)q_out,
+                      (bf16*)k_cache, (bf16*)v_cache, (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, cos_sin, positions, slots, nq,
+                      nkv, page_size, write_kv);
+        else
+            ti_launch(attention_inputs_vec_kernel<2>, grid, dim3(AI_WARPS * 32), 0, stream, (const bf16*)qkv, qkv_stride, (bf16*)q_out,
+                      (bf16*)k_cache, (bf16*)v_cache, (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, cos_sin, positions, slots, nq,
+                      nkv, page_size, write_kv);
+        return ti_check_launch("attention_inputs");
+    }
     TI_DISPATCH_DTYPE(dtype, (ti_launch(attention_inputs_kernel<T>, dim3(grid), dim3(AI_WARPS * 32), smem, stream, 
-                                 (const T*)qkv, qkv_stride, (T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)q_norm_w,
+                                 (const T*)qkv, qkv_stride, partials, n_partials, partial_stride, (T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)q_norm_w,
                                  (const T*)k_norm_w, eps, cos_sin, positions, slots, nq, nkv, D, page_size, write_kv)));
     return ti_check_launch("attention_inputs");
 }

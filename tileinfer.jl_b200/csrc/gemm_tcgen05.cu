@@ -33,8 +33,9 @@ namespace {
 
 constexpr int BM = 128;            // weight rows per tile (tensor-memory lanes)
 constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int EPI_WARPS = 8;        // two per tensor-memory lane quarter, each takes half of the columns
-constexpr int THREADS = 64 + 32 * EPI_WARPS;
+// Epilogue warps: 8 (two per tensor-memory lane quarter, each takes every other column chunk) for wide
+// token tiles; 4 for token tiles of up to 64, whose blocks are small enough for TWO to share an SM, so
+// that a product with a few more tiles than SMs does not pay for a second wave.
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr unsigned WAIT_LIMIT = 1u << 22;
 
@@ -55,10 +56,13 @@ struct Params {
 // then fill tensor memory (2 x 256 columns), so the epilogue of a tile is not overlapped with the next
 // tile's MMAs; it is about a tenth of a tile's time.
 template <int BN, int MT> struct Cfg {
+    static constexpr int BLOCKS_PER_SM = BN <= 64 ? 2 : 1;
+    static constexpr int EPI_WARPS = BN <= 64 ? 4 : 8;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr int A_BYTES = MT * BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES_FIT = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+    static constexpr int STAGES_FIT = (SMEM_LIMIT / BLOCKS_PER_SM - 2048) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
     static constexpr int ACC_BUFS = MT == 2 ? 1 : 2;
     static constexpr int TMEM_COLS = ACC_BUFS * MT * BN < 32 ? 32 : ACC_BUFS * MT * BN;
@@ -174,7 +178,7 @@ struct TileIter {
 };
 
 template <int BN, int MT>
-__global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_SM) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x,
                                                                  void* __restrict__ y, Params p) {
     typedef Cfg<BN, MT> C;
@@ -191,7 +195,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, EPI_WARPS); }
+        for (int a = 0; a < 2; ++a) { mbar_init(accf0 + 8 * a, 1); mbar_init(acce0 + 8 * a, C::EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(smem_addr(tmem_slot), C::TMEM_COLS);
@@ -267,9 +271,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
             ++local;
         }
     } else {
-        // ---------------------------------------------------------------- epilogue (8 warps)
+        // ---------------------------------------------------------------- epilogue (4 or 8 warps)
         const int quarter = warp & 3;                      // the tensor-memory lanes this warp may read
-        const int col_half = (warp - 2) >> 2;              // which half of the columns (chunks alternate)
+        const int col_group = (warp - 2) >> 2;             // with 8 warps the chunks of columns alternate between two warps
         int local = 0;
         bool ok = true;
         while (ok && it.next(p)) {
@@ -286,7 +290,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
             const int m = (it.m * MT + h) * BM + quarter * 32 + lane;
             const unsigned t_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)((acc * MT + h) * BN);
 #pragma unroll 1
-            for (int c = col_half * CH; c < BN; c += 2 * CH) {
+            for (int c = col_group * CH; c < BN; c += (C::EPI_WARPS / 4) * CH) {
                 if (c >= n_valid) break;                   // uniform across the warp
                 unsigned r[32];
                 if (CH == 32) tmem_ld32(t_row + c, r); else tmem_ld16(t_row + c, r);
@@ -394,8 +398,9 @@ int launch(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const Params& 
         configured = true;
     }
     const int tiles = p.m_tiles * p.n_tiles * p.splits;
-    const int grid = tiles < sm_count ? tiles : sm_count;
-    ti_launch(gemm_tcgen05_kernel<BN, MT>, dim3(grid), dim3(THREADS), Cfg<BN, MT>::SMEM, stream, mw, mx, y, p);
+    const int slots = sm_count * Cfg<BN, MT>::BLOCKS_PER_SM;
+    const int grid = tiles < slots ? tiles : slots;
+    ti_launch(gemm_tcgen05_kernel<BN, MT>, dim3(grid), dim3(Cfg<BN, MT>::THREADS), Cfg<BN, MT>::SMEM, stream, mw, mx, y, p);
     return ti_check_launch("gemm_tcgen05");
 }
 

@@ -89,19 +89,29 @@ def add(x, delta):
 
 def attention_inputs(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, cos_sin, positions, slots,
                      nq, nkv, head_dim, page_size, write_kv=True):
-    """qkv [n, (nq + 2 nkv) D] -> q_out [n, nq, D]; k and v rows into the pools at ``slots``."""
-    _need(qkv, "qkv", contiguous=False); _need(q_out, "q_out", qkv.dtype)
+    """qkv [n, (nq + 2 nkv) D] -> q_out [n, nq, D]; k and v rows into the pools at ``slots``. ``qkv`` may
+    also be the 32-bit partial sums [s, n, features] of a projection that was split over k."""
+    _need(qkv, "qkv", contiguous=False); _need(q_out, "q_out")
     _need(positions, "positions", torch.int32)
     if qkv.stride(-1) != 1:
         raise KernelError("qkv rows must be dense")
     if write_kv:
-        _need(k_cache, "k_cache", qkv.dtype); _need(v_cache, "v_cache", qkv.dtype); _need(slots, "slots", torch.int32)
+        _need(k_cache, "k_cache", q_out.dtype); _need(v_cache, "v_cache", q_out.dtype); _need(slots, "slots", torch.int32)
     if cos_sin is not None:
         _need(cos_sin, "cos_sin", torch.float32)
-    check(lib().ti_attention_inputs(qkv.data_ptr(), qkv.stride(0), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
+    if qkv.dim() == 3:
+        _need(qkv, "partial sums", torch.float32)
+        args = (None, qkv.stride(1), qkv.data_ptr(), qkv.shape[0], qkv.stride(0))
+        n = qkv.shape[1]
+    else:
+        if qkv.dtype != q_out.dtype:
+            raise KernelError(f"qkv must be {q_out.dtype}")
+        args = (qkv.data_ptr(), qkv.stride(0), None, 0, 0)
+        n = qkv.shape[0]
+    check(lib().ti_attention_inputs(*args, q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
                                     _ptr(q_norm_w), _ptr(k_norm_w), eps, _ptr(cos_sin), positions.data_ptr(),
-                                    _ptr(slots), qkv.shape[0], nq, nkv, head_dim, page_size, int(write_kv),
-                                    dtype_code(qkv.dtype), _stream()), "attention_inputs")
+                                    _ptr(slots), n, nq, nkv, head_dim, page_size, int(write_kv),
+                                    dtype_code(q_out.dtype), _stream()), "attention_inputs")
 
 
 def attention_plain(out, q, k_cache, v_cache, block_table, tok_slot, positions, scale, nq, nkv, head_dim,
