@@ -195,3 +195,42 @@ def test_command_line(models, capsys):
     assert "9 prompt tokens, 6 generated" in out.err
     assert cli(["run", folder, "1 2", "--bogus", "1"]) == 1 and "unknown option --bogus" in capsys.readouterr().err
     assert cli(["run", folder]) == 1 and cli(["frobnicate"]) == 1 and cli([]) == 1 and cli(["help"]) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_layer_at_apertus_8b_sizes(dtype):
+    """The layer sizes of Apertus-8B (hidden 4096, 32 / 8 heads of 128, intermediate 21504, llama3 RoPE
+    with theta 12e6), one layer and a smaller vocabulary, against the plain implementation: a prompt
+    whole, its last tokens one by one, and a batch of two unequal sequences. This is where the
+    tensor-core product, the weight-streaming product and both attention kernels run at the sizes they
+    were written for."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.weights import write_model_folder
+    cfg_dict = {
+        "architectures": ["ApertusForCausalLM"], "model_type": "apertus", "num_hidden_layers": 1, "hidden_size": 4096,
+        "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 21504, "vocab_size": 16384,
+        "rope_theta": 12000000.0, "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 8192,
+                                                  "low_freq_factor": 1.0, "high_freq_factor": 4.0},
+        "rms_norm_eps": 1e-5, "qk_norm": True, "tie_word_embeddings": True, "hidden_act": "xielu", "max_position_embeddings": 4096,
+    }
+    with tempfile.TemporaryDirectory() as d:
+        folder = write_model_folder(ApertusConfig.from_dict(cfg_dict), 5, os.path.join(d, "m"))
+        pc, pw = plain.load_folder(folder)
+        pdt = torch.float32 if dtype == "float32" else torch.bfloat16
+        prompts = helpers.random_prompts(16384, [150, 37], 6)
+        refs = [plain.forward(pc, pw, p, pdt) for p in prompts]
+        eng = ti.load_model(folder, dtype=dtype, max_context=256, max_seqs=2)
+        tol = tolerance(dtype, refs[0])
+        a = eng.new_sequence()
+        got = eng.step([(a, prompts[0][:142])], [list(range(142))]).cpu()
+        assert float((got - refs[0][:142]).abs().max()) <= tol
+        for t in range(142, 150):                                      # the last tokens one by one
+            row = eng.step([(a, [prompts[0][t]])]).cpu()[0]
+            assert float((row - refs[0][t]).abs().max()) <= tol, t
+        eng.free_sequence(a)
+        a, b = eng.new_sequence(), eng.new_sequence()                  # a batch of two, in reused slots
+        got = eng.step([(a, prompts[0]), (b, prompts[1])], [[0, 149], [36]]).cpu()
+        want = torch.stack([refs[0][0], refs[0][149], refs[1][36]])
+        assert float((got - want).abs().max()) <= tol
+        eng.check_health()
