@@ -128,6 +128,30 @@ template <typename T> __device__ __forceinline__ float xielu_value(float x, cons
     return x > 0.f ? pos : neg;                // both sides are computed: no branch, elements interleave
 }
 
+// Two bfloat16 elements at once in packed bfloat16 arithmetic: a packed product or sum rounds its exact
+// result once, which is what rnd(a * b) and rnd(a + b) of bfloat16 values give (their exact result
+// fits 32-bit arithmetic whenever it is within reach of a rounding tie), at half the instructions.
+// The _rn forms keep the compiler from contracting a product and a sum into one fused operation.
+// s0, s1 are unrounded sums; the results are bfloat16 bits in the low halves of lo and hi.
+struct XieluPacked {
+    __nv_bfloat162 alpha_p, alpha_n, beta;
+    float eps;
+};
+__device__ __forceinline__ XieluPacked xielu_pack(const XieluParams& a) {
+    return XieluPacked{__float2bfloat162_rn(a.alpha_p), __float2bfloat162_rn(a.alpha_n), __float2bfloat162_rn(a.beta), a.eps};
+}
+__device__ __forceinline__ void xielu_bf16_pair(float s0, float s1, const XieluPacked& a, unsigned& lo, unsigned& hi) {
+    const __nv_bfloat162 x = __floats2bfloat162_rn(s0, s1);
+    const __nv_bfloat162 bx = __hmul2_rn(a.beta, x);
+    const __nv_bfloat162 pos = __hadd2_rn(__hmul2_rn(__hmul2_rn(a.alpha_p, x), x), bx);
+    const float x0 = __low2float(x), x1 = __high2float(x);
+    const __nv_bfloat162 e = __floats2bfloat162_rn(expm1f(fminf(x0, a.eps)), expm1f(fminf(x1, a.eps)));
+    const __nv_bfloat162 neg = __hadd2_rn(__hmul2_rn(__hsub2_rn(e, x), a.alpha_n), bx);
+    const unsigned P = *reinterpret_cast<const unsigned*>(&pos), N = *reinterpret_cast<const unsigned*>(&neg);
+    lo = (x0 > 0.f ? P : N) & 0xffffu;
+    hi = (x1 > 0.f ? P : N) >> 16;
+}
+
 // 16 bytes of elements, widened to float on load and rounded once on store.
 template <typename T> struct Vec16;
 template <> struct Vec16<float> {

@@ -16,6 +16,8 @@
 // MMAs of the next tile fill the other. A product with few output tiles can be split over
 // k; the 32-bit partial sums [split, n, out] are added by the residual-add + RMSNorm kernel.
 // Epilogues: round to bfloat16; xIELU on the rounded sums; 32-bit logits; raw partials.
+// bfloat16 results of wide token tiles are transposed through shared memory and leave by TMA stores
+// (64-byte rows instead of 2 bytes per thread; measured 274 -> 250 us on 21504 x 4096 x 2048 tokens).
 //
 // Every wait on an mbarrier is bounded: after the limit the kernel records a code in
 // `status`, stops issuing work, frees its tensor memory and returns.
@@ -48,6 +50,7 @@ struct Params {
     int epilogue;
     XieluParams act;
     int* status;
+    int tma_out;                   // bfloat16 results leave through shared memory and TMA stores
 };
 
 // MT: 128-row weight sub-tiles per block. With MT = 2 a block owns 256 weight rows: the token
@@ -62,11 +65,15 @@ template <int BN, int MT> struct Cfg {
     static constexpr int A_BYTES = MT * BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES_FIT = (SMEM_LIMIT / BLOCKS_PER_SM - 2048) / STAGE_BYTES;
+    // Wide token tiles write bfloat16 results through shared memory: each epilogue warp owns two
+    // staging tiles of 32 tokens x 32 features that leave by TMA stores.
+    static constexpr int OUT_TILE_BYTES = 32 * 32 * 2;
+    static constexpr int OUT_BYTES = BN >= 128 ? EPI_WARPS * 2 * OUT_TILE_BYTES : 0;
+    static constexpr int STAGES_FIT = (SMEM_LIMIT / BLOCKS_PER_SM - 2048 - OUT_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
     static constexpr int ACC_BUFS = MT == 2 ? 1 : 2;
     static constexpr int TMEM_COLS = ACC_BUFS * MT * BN < 32 ? 32 : ACC_BUFS * MT * BN;
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + OUT_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -100,6 +107,20 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+
+// Shared memory -> global memory; the tensor map clips what lies outside the matrix.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, unsigned src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Until at most `pending` of this thread's stores still have to read their shared memory.
+template <int pending> __device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(pending) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Orders this thread's ordinary shared-memory writes before later reads by the TMA unit.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_alloc(unsigned dst_smem, unsigned cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
@@ -180,13 +201,15 @@ struct TileIter {
 template <int BN, int MT>
 __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_SM) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x,
+                                                                 const __grid_constant__ CUtensorMap map_y,
                                                                  void* __restrict__ y, Params p) {
     typedef Cfg<BN, MT> C;
     extern __shared__ unsigned char smem_dyn[];
     // Swizzled tiles need 1024-byte alignment.
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     unsigned char* tiles = smem;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (size_t)C::STAGES * C::STAGE_BYTES);
+    unsigned char* out_tiles = smem + (size_t)C::STAGES * C::STAGE_BYTES;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(out_tiles + C::OUT_BYTES);
     // bars: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the tensor-memory base address.
     const unsigned full0 = smem_addr(bars), empty0 = full0 + 8 * C::STAGES;
     const unsigned accf0 = empty0 + 8 * C::STAGES, acce0 = accf0 + 16;
@@ -274,7 +297,8 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
         // ---------------------------------------------------------------- epilogue (4 or 8 warps)
         const int quarter = warp & 3;                      // the tensor-memory lanes this warp may read
         const int col_group = (warp - 2) >> 2;             // with 8 warps the chunks of columns alternate between two warps
-        int local = 0;
+        int local = 0, out_buf = 0;
+        const XieluPacked act = xielu_pack(p.act);
         bool ok = true;
         while (ok && it.next(p)) {
             const int acc = C::ACC_BUFS == 2 ? (local & 1) : 0;
@@ -287,7 +311,8 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
             constexpr int CH = BN >= 32 ? 32 : 16;
 #pragma unroll 1
             for (int h = 0; h < MT; ++h) {
-            const int m = (it.m * MT + h) * BM + quarter * 32 + lane;
+            const int m_first = (it.m * MT + h) * BM + quarter * 32;
+            const int m = m_first + lane;
             const unsigned t_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)((acc * MT + h) * BN);
 #pragma unroll 1
             for (int c = col_group * CH; c < BN; c += (C::EPI_WARPS / 4) * CH) {
@@ -297,27 +322,48 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
                 tmem_ld_wait();
                 // All values of the chunk first, without branches (one warp per scheduler runs this: only
                 // independent elements in flight hide the latency of the arithmetic), then the stores.
-                float v[32];
+                if (p.epilogue >= EPI_F32) {
+                    if (m < p.M) {
+                        float* yf = (float*)y + ((size_t)(p.epilogue == EPI_PARTIAL ? it.split : 0) * p.N + n0 + c) * p.ldy + m;
 #pragma unroll
-                for (int j = 0; j < CH; ++j) {
-                    const float s = __uint_as_float(r[j]);
-                    const float q = rnd<bf16>(s);
-                    v[j] = p.epilogue == EPI_PARTIAL ? s : (p.epilogue == EPI_XIELU ? xielu_value<bf16>(q, p.act) : q);
-                }
-                if (m < p.M) {
-                    if (p.epilogue == EPI_PARTIAL) {
-#pragma unroll
-                        for (int j = 0; j < CH; ++j)
-                            if (c + j < n_valid) ((float*)y)[((size_t)it.split * p.N + n0 + c + j) * p.ldy + m] = v[j];
-                    } else if (p.epilogue == EPI_F32) {
-#pragma unroll
-                        for (int j = 0; j < CH; ++j)
-                            if (c + j < n_valid) ((float*)y)[(size_t)(n0 + c + j) * p.ldy + m] = v[j];
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < CH; ++j)
-                            if (c + j < n_valid) ((bf16*)y)[(size_t)(n0 + c + j) * p.ldy + m] = __float2bfloat16_rn(v[j]);
+                        for (int j = 0; j < CH; ++j) {
+                            const float s = __uint_as_float(r[j]);
+                            if (c + j < n_valid) yf[(size_t)j * p.ldy] = p.epilogue == EPI_PARTIAL ? s : rnd<bf16>(s);
+                        }
                     }
+                    continue;
+                }
+                unsigned o[32];                            // bfloat16 bits in the low halves
+#pragma unroll
+                for (int j = 0; j < CH; j += 2) {
+                    const float s0 = __uint_as_float(r[j]), s1 = __uint_as_float(r[j + 1]);
+                    if (p.epilogue == EPI_XIELU) {
+                        xielu_bf16_pair(s0, s1, act, o[j], o[j + 1]);
+                    } else {
+                        const __nv_bfloat162 q = __floats2bfloat162_rn(s0, s1);
+                        const unsigned bits = *reinterpret_cast<const unsigned*>(&q);
+                        o[j] = bits & 0xffffu; o[j + 1] = bits >> 16;
+                    }
+                }
+                if (C::OUT_BYTES > 0 && p.tma_out) {
+                    // The warp's 32 features x 32 tokens go to one of its two staging tiles ([token][feature],
+                    // so a warp writes 64 contiguous bytes at a time) and leave as one TMA store, which
+                    // writes whole 64-byte rows instead of 2 bytes per thread.
+                    unsigned char* tile = out_tiles + (size_t)(((warp - 2) * 2 + out_buf) * C::OUT_TILE_BYTES);
+                    if (lane == 0) tma_store_wait_read<1>();          // the store that last read this tile has done so
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < CH; ++j)
+                        reinterpret_cast<unsigned short*>(tile)[j * 32 + lane] = (unsigned short)o[j];
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && m_first < p.M) tma_store_2d(&map_y, smem_addr(tile), m_first, n0 + c);
+                    out_buf ^= 1;
+                } else if (m < p.M) {
+                    unsigned short* yb = (unsigned short*)y + (size_t)(n0 + c) * p.ldy + m;
+#pragma unroll
+                    for (int j = 0; j < CH; ++j)
+                        if (c + j < n_valid) yb[(size_t)j * p.ldy] = (unsigned short)o[j];
                 }
             }
             }
@@ -326,6 +372,7 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
             if (lane == 0) mbar_arrive(acce0 + 8 * acc);
             ++local;
         }
+        if (C::OUT_BYTES > 0 && lane == 0) tma_store_wait_all();   // shared memory stays until the stores have read it
     }
     tc_fence_before();
     __syncthreads();
@@ -354,23 +401,26 @@ EncodeTiledFn encode_fn() {
 }
 
 struct MapKey {
-    const void* ptr; long long rows, cols, ld; int box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+    const void* ptr; long long rows, cols, ld; int box_rows, box_cols;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && box_cols == o.box_cols;
+    }
 };
 struct MapHash {
     size_t operator()(const MapKey& k) const {
         size_t h = (size_t)k.ptr;
         h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols; h = h * 1000003u ^ (size_t)k.ld;
-        return h * 1000003u ^ (size_t)k.box_rows;
+        return (h * 1000003u ^ (size_t)k.box_rows) * 1000003u ^ (size_t)k.box_cols;
     }
 };
 
-// A [rows, cols] bfloat16 matrix with row stride ld (elements), read in boxes of box_rows x 64
-// with the 128-byte swizzle; out-of-range elements read as zero.
-int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+// A [rows, cols] bfloat16 matrix with row stride ld (elements), moved in boxes of box_rows x box_cols:
+// operand boxes are 64 wide with the 128-byte swizzle (out-of-range elements read as zero), result
+// boxes 32 wide without swizzle (out-of-range elements are not written).
+int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols = BK) {
     static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
     static std::mutex mu;
-    MapKey key{ptr, rows, cols, ld, box_rows};
+    MapKey key{ptr, rows, cols, ld, box_rows, box_cols};
     std::lock_guard<std::mutex> lock(mu);
     auto hit = cache.find(key);
     if (hit != cache.end()) { *out = hit->second; return 0; }
@@ -378,10 +428,11 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
     if (!enc) return ti_fail("gemm: cuTensorMapEncodeTiled is not available from this driver");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == BK ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return ti_fail("gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
     if (cache.size() > 4096) cache.clear();
@@ -390,7 +441,7 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols
 }
 
 template <int BN, int MT>
-int launch(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int sm_count, cudaStream_t stream) {
+int launch(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int sm_count, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN, MT>::SMEM);
@@ -400,7 +451,7 @@ int launch(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const Params& 
     const int tiles = p.m_tiles * p.n_tiles * p.splits;
     const int slots = sm_count * Cfg<BN, MT>::BLOCKS_PER_SM;
     const int grid = tiles < slots ? tiles : slots;
-    ti_launch(gemm_tcgen05_kernel<BN, MT>, dim3(grid), dim3(Cfg<BN, MT>::THREADS), Cfg<BN, MT>::SMEM, stream, mw, mx, y, p);
+    ti_launch(gemm_tcgen05_kernel<BN, MT>, dim3(grid), dim3(Cfg<BN, MT>::THREADS), Cfg<BN, MT>::SMEM, stream, mw, mx, my, y, p);
     return ti_check_launch("gemm_tcgen05");
 }
 
@@ -431,13 +482,14 @@ extern "C" int ti_gemm_tcgen05(void* y, long long ldy, const void* x, long long 
     p.M = out; p.N = n; p.K = in;
     // Wide token tiles take 256 weight rows per block when that is the cheaper way to cover the
     // product: a 256-row tile costs about 1.5 times a 128-row tile (its MMAs are better fed), plus an
-    // epilogue that is not overlapped, which only a long k amortises (measured: even at k = 4096).
+    // epilogue that is not overlapped. With xIELU in it that epilogue is long, and only a long k
+    // amortises it (measured at k = 4096: 302 us against 296 us for the up projection of 2048 tokens).
     int mt = 1;
-    if (bn == 256 && in >= 8192) {
+    if (bn == 256 && splits <= 1 && (epilogue != EPI_XIELU || in >= 8192)) {
         const long long n_t = (n + bn - 1) / bn;
         const long long waves1 = (((out + BM - 1) / BM) * n_t + sm_count - 1) / sm_count;
         const long long waves2 = (((out + 2 * BM - 1) / (2 * BM)) * n_t + sm_count - 1) / sm_count;
-        if (3 * waves2 < 2 * waves1 && splits <= 1) mt = 2;
+        if (3 * waves2 < 2 * waves1) mt = 2;
     }
     p.m_tiles = (out + mt * BM - 1) / (mt * BM);
     p.n_tiles = (n + bn - 1) / bn;
@@ -445,13 +497,19 @@ extern "C" int ti_gemm_tcgen05(void* y, long long ldy, const void* x, long long 
     p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
     TI_REQUIRE(p.splits == 1 || epilogue == EPI_PARTIAL, "gemm_tcgen05: a split product leaves partial sums");
     p.ldy = ldy; p.epilogue = epilogue; p.act = XieluParams{alpha_p, alpha_n, beta, eps}; p.status = status;
-    CUtensorMap mw, mx;
+    CUtensorMap mw, mx, my;
     if (int rc = tensor_map(&mw, W, out, in, in, BM)) return rc;
     if (int rc = tensor_map(&mx, x, n, in, ldx, bn)) return rc;
+    p.tma_out = bn >= 128 && (epilogue == EPI_NONE || epilogue == EPI_XIELU) && ldy % 8 == 0 && !((uintptr_t)y & 15);
+    if (p.tma_out) {
+        if (int rc = tensor_map(&my, y, n, out, ldy, 32, 32)) return rc;
+    } else {
+        my = mx;                   // not read
+    }
     switch (bn) {
-        case 256: return mt == 2 ? launch<256, 2>(y, mw, mx, p, sm_count, stream) : launch<256, 1>(y, mw, mx, p, sm_count, stream);
-        case 128: return launch<128, 1>(y, mw, mx, p, sm_count, stream);
-        case 64: return launch<64, 1>(y, mw, mx, p, sm_count, stream);
-        default: return launch<32, 1>(y, mw, mx, p, sm_count, stream);
+        case 256: return mt == 2 ? launch<256, 2>(y, mw, mx, my, p, sm_count, stream) : launch<256, 1>(y, mw, mx, my, p, sm_count, stream);
+        case 128: return launch<128, 1>(y, mw, mx, my, p, sm_count, stream);
+        case 64: return launch<64, 1>(y, mw, mx, my, p, sm_count, stream);
+        default: return launch<32, 1>(y, mw, mx, my, p, sm_count, stream);
     }
 }
