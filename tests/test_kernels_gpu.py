@@ -369,6 +369,61 @@ def test_attention_prefill(ops, nq, nkv, D):
     assert float((head - vs[3][5, 1 // (nq // nkv)]).abs().max()) < 0.2
 
 
+@pytest.mark.parametrize("nq,nkv,D,window", [(32, 8, 128, 0), (8, 8, 64, 0), (16, 1, 64, 0), (4, 2, 128, 0), (6, 3, 64, 150), (8, 1, 128, 333)])
+def test_attention_prefill_tensor_core(ops, nq, nkv, D, window):
+    """The tcgen05 prefill kernel on unequal sequences in one launch (some continuing from cached
+    positions, one a single token, one of several key steps), shuffled pages, with and without a
+    window, against exact 32-bit attention. A key hundreds of positions back dominates one head (its
+    step raises the row maximum by far more than the lazy rescaling allows to pass), and a key just
+    outside a window is made huge and must not show."""
+    from tileinfer_b200.kernels import fast
+    from tileinfer_b200.kernels.library import check, lib
+    torch.manual_seed(17)
+    dtype = torch.bfloat16
+    total = [700, 1, 130, 513, 64, 257]             # cached length after the step
+    fresh = [700, 1, 30, 200, 64, 129]              # tokens of the step (the rest was cached before)
+    B, g = len(total), nq // nkv
+    ks = [rnd(torch.randn(L, nkv, D), dtype) for L in total]
+    vs = [rnd(torch.randn(L, nkv, D), dtype) for L in total]
+    qs = [rnd(torch.randn(n, nq, D), dtype) for n in fresh]
+    far = 5 if not window else 512 - window + 1     # the farthest key the last query of sequence 3 sees
+    ks[3][far, 1 // g] = rnd(qs[3][-1, 1] * 4.0, dtype)
+    ks[0][400, 0] = rnd(qs[0][650, 0] * 6.0, dtype)  # found in the fourth key step of a row that began small
+    if window:
+        ks[3][512 - window, :] = rnd(qs[3][-1, 1] * 9.0, dtype)[None].expand(nkv, D)     # one place outside
+    n_pages = sum(-(-L // 64) for L in total) + 3
+    kp, vp, table = paged(ks, vs, 64, n_pages, 13, dtype)
+    scale = 1 / math.sqrt(D)
+    wants = []
+    for b in range(B):
+        s = torch.einsum("qhd,khd->hqk", qs[b].double(), ks[b].double().repeat_interleave(g, 1)) * scale
+        kpos, qpos = torch.arange(total[b]), torch.arange(total[b] - fresh[b], total[b])
+        vis = kpos[None, :] <= qpos[:, None]
+        if window:
+            vis &= kpos[None, :] > qpos[:, None] - window
+        pr = s.masked_fill(~vis[None], float("-inf")).softmax(-1)
+        wants.append(torch.einsum("hqk,khd->qhd", pr, vs[b].double().repeat_interleave(g, 1)).float())
+    want = torch.cat(wants)
+    q = dev(torch.cat(qs), dtype)
+    cu = [0]
+    for n in fresh:
+        cu.append(cu[-1] + n)
+    per_block = 2 * (128 // g)
+    blocks = sum(-(-n // per_block) for n in fresh)
+    out = torch.full((cu[-1], nq, D), float("nan"), dtype=dtype, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    slots, cu_d, lens_d = (dev(torch.arange(1, B + 1, dtype=torch.int32)), dev(torch.tensor(cu, dtype=torch.int32)),
+                           dev(torch.tensor(total, dtype=torch.int32)))
+    status = fast.status_word()
+    check(lib().ti_attention_prefill_tc(out.data_ptr(), q.data_ptr(), kp.data_ptr(), vp.data_ptr(), kp.shape[0], table.data_ptr(),
+                                        table.stride(0), slots.data_ptr(), cu_d.data_ptr(), lens_d.data_ptr(), B, cu[-1], blocks,
+                                        scale, nq, nkv, D, 64, window, status.data_ptr(), st), "attention_prefill_tc")
+    fast.check_status()
+    close(out, want, dtype, ulps=5.0)
+    head = want[cu[4] - 1, 1]
+    assert float((head - vs[3][far, 1 // g]).abs().max()) < 0.2
+
+
 def test_attention_window_edge(ops):
     """With a window of w keys the query at position p sees exactly keys p-w+1 .. p: a key one place
     outside the window is made huge and must not show; plain, prefill and decode kernels agree."""

@@ -24,14 +24,13 @@
 //
 // AntoineBut/TileInfer.jl's counterpart is gemm_kernel (src/ops/tile/linear.jl:80-100): 32-bit
 // accumulation, one rounding to the storage type, grouped tile order for L2 reuse.
-#include "common.cuh"
+#include "tcgen05.cuh"
+#include "tensor_map.h"
 
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
 
 namespace {
+
+using namespace tc;
 
 constexpr int BM = 128;            // weight rows per tile (tensor-memory lanes)
 constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
@@ -39,7 +38,6 @@ constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzl
 // token tiles; 4 for token tiles of up to 64, whose blocks are small enough for TWO to share an SM, so
 // that a product with a few more tiles than SMs does not pay for a second wave.
 constexpr int SMEM_LIMIT = 227 * 1024;
-constexpr unsigned WAIT_LIMIT = 1u << 22;
 
 enum { EPI_NONE = 0, EPI_XIELU = 1, EPI_F32 = 2, EPI_PARTIAL = 3 };
 
@@ -75,108 +73,6 @@ template <int BN, int MT> struct Cfg {
     static constexpr int TMEM_COLS = ACC_BUFS * MT * BN < 32 ? 32 : ACC_BUFS * MT * BN;
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + OUT_BYTES + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
-
-__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait; false (and a code in *status) when the limit is reached.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
-    for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    atomicCAS(status, 0, code);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-// Shared memory -> global memory; the tensor map clips what lies outside the matrix.
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, unsigned src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-// Until at most `pending` of this thread's stores still have to read their shared memory.
-template <int pending> __device__ __forceinline__ void tma_store_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(pending) : "memory");
-}
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// Orders this thread's ordinary shared-memory writes before later reads by the TMA unit.
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(unsigned dst_smem, unsigned cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(unsigned taddr, unsigned cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
-                                          unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The barrier gets one arrival when every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
-// groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
-__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
-    d |= (unsigned long long)1 << 16;                         // leading byte offset (unused with swizzle)
-    d |= (unsigned long long)(1024 >> 4) << 32;               // stride byte offset
-    d |= (unsigned long long)1 << 46;                         // version
-    d |= (unsigned long long)2 << 61;                         // SWIZZLE_128B
-    return d;
-}
 
 // kind::f16 instruction descriptor: D 32-bit, A and B bfloat16, both K-major, M = 128, N = BN.
 template <int BN> __device__ __forceinline__ constexpr unsigned instr_desc() {
@@ -383,61 +279,14 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
 }
 
 // ------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; long long rows, cols, ld; int box_rows, box_cols;
-    bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows && box_cols == o.box_cols;
-    }
-};
-struct MapHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)k.ptr;
-        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols; h = h * 1000003u ^ (size_t)k.ld;
-        return (h * 1000003u ^ (size_t)k.box_rows) * 1000003u ^ (size_t)k.box_cols;
-    }
-};
-
 // A [rows, cols] bfloat16 matrix with row stride ld (elements), moved in boxes of box_rows x box_cols:
 // operand boxes are 64 wide with the 128-byte swizzle (out-of-range elements read as zero), result
 // boxes 32 wide without swizzle (out-of-range elements are not written).
 int tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows, int box_cols = BK) {
-    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
-    static std::mutex mu;
-    MapKey key{ptr, rows, cols, ld, box_rows, box_cols};
-    std::lock_guard<std::mutex> lock(mu);
-    auto hit = cache.find(key);
-    if (hit != cache.end()) { *out = hit->second; return 0; }
-    EncodeTiledFn enc = encode_fn();
-    if (!enc) return ti_fail("gemm: cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == BK ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return ti_fail("gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, *out);
-    return 0;
+    const unsigned long long dims[2] = {(unsigned long long)cols, (unsigned long long)rows};
+    const unsigned long long strides[1] = {(unsigned long long)ld * 2};
+    const unsigned box[2] = {(unsigned)box_cols, (unsigned)box_rows};
+    return ti_tensor_map_bf16(out, ptr, 2, dims, strides, box, box_cols == BK);
 }
 
 template <int BN, int MT>

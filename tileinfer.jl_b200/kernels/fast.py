@@ -129,6 +129,16 @@ def attention(out, q, cache, meta, step, spec) -> bool:
     if group < 1 or group > 128 or spec.num_heads % spec.num_kv_heads:
         return False
     tokens_per_tile = 128 // group
+    # The tensor-core kernel for the sizes it takes (head size 64 or 128, a power-of-two group).
+    blocks = sum(-(-n // (2 * tokens_per_tile)) for n in step.host_q_lens)
+    rc = lib().ti_attention_prefill_tc(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0],
+                                       meta.block_table.data_ptr(), meta.block_table.stride(0), step.seq_slots.data_ptr(),
+                                       step.cu_seqlens.data_ptr(), step.kv_lens.data_ptr(), step.n_seqs, step.n_tokens, blocks,
+                                       spec.scale, spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
+                                       spec.window or 0, status_word().data_ptr(), _stream())
+    if rc != 2:
+        check(rc, "attention_prefill_tc")
+        return True
     total_tiles = sum(-(-n // tokens_per_tile) for n in step.host_q_lens)
     rc = lib().ti_attention_prefill(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                                     meta.block_table.data_ptr(), meta.block_table.stride(0), step.seq_slots.data_ptr(),

@@ -3,7 +3,7 @@
     python -m tileinfer_b200.kernels.microbench gemv    --out 21504 --in 4096 --tokens 1 [--splits S]
     python -m tileinfer_b200.kernels.microbench gemm    --out 21504 --in 4096 --tokens 2048 [--epilogue xielu]
     python -m tileinfer_b200.kernels.microbench decode  --batch 8 --context 1024
-    python -m tileinfer_b200.kernels.microbench prefill --tokens 2048
+    python -m tileinfer_b200.kernels.microbench prefill --tokens 2048 [--kernel mma]
     python -m tileinfer_b200.kernels.microbench timeline --batch 1 --layers 8
     python -m tileinfer_b200.kernels.microbench timeline --tokens 2048 --layers 4      (a prefill step)
 
@@ -115,7 +115,7 @@ def bench_decode_attention(batch, context, once, heads=32, kv_heads=8, head_dim=
           + ("" if nbytes > 126e6 else " (the cache of this case fits L2)"))
 
 
-def bench_prefill_attention(tokens, once, heads=32, kv_heads=8, head_dim=128):
+def bench_prefill_attention(tokens, once, kernel="tc", heads=32, kv_heads=8, head_dim=128):
     L = lib()
     pages = -(-tokens // 64)
     k = torch.randn(pages, kv_heads, 64, head_dim, device="cuda").to(torch.bfloat16)
@@ -127,11 +127,19 @@ def bench_prefill_attention(tokens, once, heads=32, kv_heads=8, head_dim=128):
     lens = torch.tensor([tokens], dtype=torch.int32, device="cuda")
     out = torch.empty(tokens, heads, head_dim, dtype=torch.bfloat16, device="cuda")
     tpt = 128 // (heads // kv_heads)
+    status = fast.status_word()
 
     def call():
-        check(L.ti_attention_prefill(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), table.data_ptr(), table.stride(0),
-                                     slots.data_ptr(), cu.data_ptr(), lens.data_ptr(), 1, -(-tokens // tpt), head_dim ** -0.5, heads,
-                                     kv_heads, head_dim, 64, 0, torch.cuda.current_stream().cuda_stream), "prefill")
+        st = torch.cuda.current_stream().cuda_stream
+        if kernel == "tc":
+            check(L.ti_attention_prefill_tc(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), pages, table.data_ptr(),
+                                            table.stride(0), slots.data_ptr(), cu.data_ptr(), lens.data_ptr(), 1, tokens,
+                                            -(-tokens // (2 * tpt)), head_dim ** -0.5, heads, kv_heads, head_dim, 64, 0,
+                                            status.data_ptr(), st), "prefill_tc")
+        else:
+            check(L.ti_attention_prefill(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), table.data_ptr(), table.stride(0),
+                                         slots.data_ptr(), cu.data_ptr(), lens.data_ptr(), 1, -(-tokens // tpt), head_dim ** -0.5, heads,
+                                         kv_heads, head_dim, 64, 0, st), "prefill")
     if once:
         for _ in range(3):
             call()
@@ -140,7 +148,8 @@ def bench_prefill_attention(tokens, once, heads=32, kv_heads=8, head_dim=128):
         return
     ms = _graph_time([call] * 4)
     flops = 4 * head_dim * heads * tokens * (tokens + 1) / 2
-    print(f"prefill attention tokens={tokens}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s (causal)")
+    fast.check_status()
+    print(f"prefill attention ({kernel}) tokens={tokens}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s (causal)")
 
 
 def timeline(batch, layers, cached=1023, prefill_tokens=0):
@@ -210,6 +219,7 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=8)
+    ap.add_argument("--kernel", default="tc", choices=["tc", "mma"], help="prefill attention: tcgen05 or mma.sync kernel")
     ap.add_argument("--once", action="store_true", help="a few eager launches and no timing (for ncu)")
     a = ap.parse_args(argv)
     if a.what in ("gemv", "gemm"):
@@ -217,7 +227,7 @@ def main(argv=None):
     elif a.what == "decode":
         bench_decode_attention(a.batch, a.context, a.once)
     elif a.what == "prefill":
-        bench_prefill_attention(a.tokens if a.tokens > 1 else 2048, a.once)
+        bench_prefill_attention(a.tokens if a.tokens > 1 else 2048, a.once, a.kernel)
     else:
         timeline(a.batch, a.layers, prefill_tokens=a.tokens if a.tokens > 1 else 0)
     return 0
