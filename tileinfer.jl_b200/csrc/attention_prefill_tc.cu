@@ -73,7 +73,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 1 + 2 * RING + 6);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kvh = blockIdx.y;
+    // Blocks are numbered so that the hardware hands them out longest first: the block index within
+    // the sequences is the slow digit (reversed below), the KV head the fast one.
+    const int kvh = blockIdx.x % p.kv_heads;
     const int tokens_per_tile = ROWS / p.group;
     const int tokens_per_block = 2 * tokens_per_tile;
 
@@ -81,7 +83,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     pdl_launch_dependents();
 
     // Which sequence and which block of its new tokens; later blocks (longer prefixes) run first.
-    int b = 0, blk = (int)gridDim.x - 1 - (int)blockIdx.x;
+    int b = 0, blk = (int)(gridDim.x / p.kv_heads) - 1 - (int)(blockIdx.x / p.kv_heads);
     for (; b < p.n_seqs; ++b) {
         const int n_b = (__ldcg(p.cu_seqlens + b + 1) - __ldcg(p.cu_seqlens + b) + tokens_per_block - 1) / tokens_per_block;
         if (blk < n_b) break;
@@ -327,6 +329,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
             }
         }
     }
+    if (*reinterpret_cast<volatile int*>(p.status) != 0) drain_after_timeout();   // a wait ran out somewhere: let what is in flight land
     tc_fence_before();
     __syncthreads();
     if (warp == 9) {
@@ -344,7 +347,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
         if (e != cudaSuccess) return ti_fail("attention_prefill_tc: %s", cudaGetErrorString(e));
         configured = true;
     }
-    ti_launch(attention_prefill_tc_kernel<D>, dim3(blocks, p.kv_heads), dim3(THREADS), Cfg<D>::SMEM, stream, mq, mk, mv, q, p);
+    ti_launch(attention_prefill_tc_kernel<D>, dim3(blocks * p.kv_heads), dim3(THREADS), Cfg<D>::SMEM, stream, mq, mk, mv, q, p);
     return ti_check_launch("attention_prefill_tc");
 }
 

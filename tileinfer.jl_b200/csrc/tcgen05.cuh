@@ -22,7 +22,7 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
 __device__ __forceinline__ void mbar_arrive(unsigned bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Bounded wait; false (and a code in *status) when the limit is reached.
+// Bounded wait; false (and bit `code` set in *status) when the limit is reached.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
     for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
         unsigned done;
@@ -33,8 +33,14 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* st
             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
     }
-    atomicCAS(status, 0, code);
+    atomicOr(status, 1 << code);
     return false;
+}
+
+// After a wait has run out: give the copies and MMAs this block still has in flight time to land before
+// the block gives up its shared and tensor memory (about a quarter of a millisecond).
+__device__ __forceinline__ void drain_after_timeout() {
+    for (int i = 0; i < 256; ++i) __nanosleep(1000);
 }
 
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {

@@ -65,7 +65,7 @@ def check_status() -> None:
         code = int(_status.item())
         if code:
             _status.zero_()
-            raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}); its results are invalid")
+            raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (waits {[i for i in range(31) if code >> i & 1]}); its results are invalid")
 
 
 def tc_splits(out_features: int, in_features: int, n: int) -> int:
