@@ -194,14 +194,16 @@ def timeline(batch, layers, cached=1023, prefill_tokens=0):
           f"{last[-1].time_range.end - t0:.1f} us from first start to last end")
     prev = None
     first_layer_end = 2 + 2 * 9
+    def short(name):
+        return name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].strip()
     for e in last[:first_layer_end]:
         gap = e.time_range.start - prev if prev is not None else 0.0
-        print(f"  {(e.name.split('(')[0][-44:].replace('void', '').strip() or 'gemm_tcgen05_kernel'):44s} start {e.time_range.start - t0:8.1f}  dur {e.time_range.end - e.time_range.start:6.1f}  "
+        print(f"  {short(e.name)[-44:]:44s} start {e.time_range.start - t0:8.1f}  dur {e.time_range.end - e.time_range.start:6.1f}  "
               f"gap to previous end {gap:6.1f}")
         prev = e.time_range.end
     total, count = collections.Counter(), collections.Counter()
     for e in last:
-        key = e.name.split("<")[0].split("(")[0].replace("void ", "") or "gemm_tcgen05_kernel"
+        key = short(e.name).split("<")[0]
         total[key] += e.time_range.end - e.time_range.start
         count[key] += 1
     for key, v in total.most_common():
