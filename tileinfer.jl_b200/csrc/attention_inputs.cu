@@ -91,79 +91,92 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, cons
 // The same for head sizes 64 and 128 in bfloat16 from a stored projection: a lane owns VPL = D/32
 // consecutive elements (one 4- or 8-byte access), the rotation partner i +- D/2 lives in lane +- 16 and
 // comes by shuffle, so no shared memory and no strided loops are needed.
-template <int VPL>
+template <int VPL, int HPW>
 __global__ void attention_inputs_vec_kernel(const bf16* qkv, long long qkv_stride, bf16* __restrict__ q_out,
                                             bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                             const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float eps,
                                             const float* __restrict__ cos_sin, const int* positions, const int* slots,
                                             int nq, int nkv, int page_size, int write_kv) {
+    // A warp takes HPW consecutive heads of one token, with all its loads in flight at once and the
+    // token's rotation row read once: a step of many tokens is bound by memory traffic, and the rotation
+    // row (as long as four heads) would otherwise be read again for every head.
     constexpr int D = 32 * VPL;
     typedef typename std::conditional<VPL == 4, uint2, unsigned>::type Pack;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
-    const int head = blockIdx.y * AI_WARPS + warp;
+    const int head0 = (blockIdx.y * AI_WARPS + warp) * HPW;
     const int slot_t = slots != nullptr ? __ldcg(slots + t) : 0;
     const int pos_t = __ldcg(positions + t);
-    pdl_enter();
-    if (head >= heads_total) return;
-    const bool is_q = head < nq;
-    const bool is_k = !is_q && head < nq + nkv;
-    const int kvh = is_q ? 0 : (is_k ? head - nq : head - nq - nkv);
-    bf16* dst;
-    if (is_q) {
-        dst = q_out + ((size_t)t * nq + head) * D;
-    } else {
-        const int page = slot_t / page_size, off = slot_t - page * page_size;
-        dst = (is_k ? k_cache : v_cache) + (((size_t)page * nkv + kvh) * page_size + off) * D;
-    }
-    const Pack raw = __ldcg(reinterpret_cast<const Pack*>(qkv + (size_t)t * qkv_stride + (size_t)head * D) + lane);
-    if (!is_q && !is_k) {                    // value head: a copy
-        reinterpret_cast<Pack*>(dst)[lane] = raw;
-        return;
-    }
-    float v[VPL];
-    {
-        const unsigned* w = reinterpret_cast<const unsigned*>(&raw);
-#pragma unroll
-        for (int i = 0; i < VPL / 2; ++i) {
-            v[2 * i] = __uint_as_float(w[i] << 16);
-            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-        }
-    }
-    const bf16* nw = is_q ? q_norm_w : k_norm_w;
-    if (nw != nullptr) {
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < VPL; ++i) ss = fmaf(v[i], v[i], ss);
-        ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-        const Pack wraw = reinterpret_cast<const Pack*>(nw)[lane];
-        const unsigned* w = reinterpret_cast<const unsigned*>(&wraw);
-#pragma unroll
-        for (int i = 0; i < VPL / 2; ++i) {
-            v[2 * i] = rnd<bf16>(__uint_as_float(w[i] << 16) * rnd<bf16>(v[2 * i] * inv));
-            v[2 * i + 1] = rnd<bf16>(__uint_as_float(w[i] & 0xffff0000u) * rnd<bf16>(v[2 * i + 1] * inv));
-        }
-    }
+    float2 cs[VPL];
     if (cos_sin != nullptr) {
-        const float2* cs = reinterpret_cast<const float2*>(cos_sin + (size_t)pos_t * D) + (lane & 15) * VPL;
+        const float2* row = reinterpret_cast<const float2*>(cos_sin + (size_t)pos_t * D) + (lane & 15) * VPL;
 #pragma unroll
-        for (int i = 0; i < VPL; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-            const float rot = lane < 16 ? -other : other;
-            const float2 c = cs[i];
-            v[i] = rnd<bf16>(v[i] * c.x) + rnd<bf16>(rot * c.y);
+        for (int e = 0; e < VPL; ++e) cs[e] = row[e];
+    }
+    pdl_enter();
+    if (head0 >= heads_total) return;
+    Pack raw[HPW];
+#pragma unroll
+    for (int i = 0; i < HPW; ++i) {
+        const int head = min(head0 + i, heads_total - 1);
+        raw[i] = __ldcg(reinterpret_cast<const Pack*>(qkv + (size_t)t * qkv_stride + (size_t)head * D) + lane);
+    }
+    const int page = slot_t / page_size, off = slot_t - page * page_size;
+#pragma unroll
+    for (int i = 0; i < HPW; ++i) {
+        const int head = head0 + i;
+        if (head >= heads_total) break;
+        const bool is_q = head < nq;
+        const bool is_k = !is_q && head < nq + nkv;
+        const int kvh = is_q ? 0 : (is_k ? head - nq : head - nq - nkv);
+        bf16* dst = is_q ? q_out + ((size_t)t * nq + head) * D
+                         : (is_k ? k_cache : v_cache) + (((size_t)page * nkv + kvh) * page_size + off) * D;
+        if (!is_q && !is_k) {                    // value head: a copy
+            reinterpret_cast<Pack*>(dst)[lane] = raw[i];
+            continue;
         }
-    }
-    Pack outp;
-    unsigned* o = reinterpret_cast<unsigned*>(&outp);
+        float v[VPL];
+        {
+            const unsigned* w = reinterpret_cast<const unsigned*>(&raw[i]);
 #pragma unroll
-    for (int i = 0; i < VPL / 2; ++i) {
-        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-        o[i] = *reinterpret_cast<const unsigned*>(&h);
+            for (int e = 0; e < VPL / 2; ++e) {
+                v[2 * e] = __uint_as_float(w[e] << 16);
+                v[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+            }
+        }
+        const bf16* nw = is_q ? q_norm_w : k_norm_w;
+        if (nw != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) ss = fmaf(v[e], v[e], ss);
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+            const Pack wraw = reinterpret_cast<const Pack*>(nw)[lane];
+            const unsigned* w = reinterpret_cast<const unsigned*>(&wraw);
+#pragma unroll
+            for (int e = 0; e < VPL / 2; ++e) {
+                v[2 * e] = rnd<bf16>(__uint_as_float(w[e] << 16) * rnd<bf16>(v[2 * e] * inv));
+                v[2 * e + 1] = rnd<bf16>(__uint_as_float(w[e] & 0xffff0000u) * rnd<bf16>(v[2 * e + 1] * inv));
+            }
+        }
+        if (cos_sin != nullptr) {
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
+                const float rot = lane < 16 ? -other : other;
+                v[e] = rnd<bf16>(v[e] * cs[e].x) + rnd<bf16>(rot * cs[e].y);
+            }
+        }
+        Pack outp;
+        unsigned* o = reinterpret_cast<unsigned*>(&outp);
+#pragma unroll
+        for (int e = 0; e < VPL / 2; ++e) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+            o[e] = *reinterpret_cast<const unsigned*>(&h);
+        }
+        reinterpret_cast<Pack*>(dst)[lane] = outp;
     }
-    reinterpret_cast<Pack*>(dst)[lane] = outp;
 }
 
 extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, const float* partials, int n_partials,
@@ -181,14 +194,14 @@ extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, const 
     if (dtype == TI_BF16 && qkv != nullptr && (D == 64 || D == 128) && qkv_stride % 4 == 0 && aligned16(qkv) && aligned16(q_out) &&
         (!write_kv || (aligned16(k_cache) && aligned16(v_cache))) && (q_norm_w == nullptr || aligned16(q_norm_w)) &&
         (k_norm_w == nullptr || aligned16(k_norm_w)) && (cos_sin == nullptr || aligned16(cos_sin))) {
-        if (D == 128)
-            ti_launch(attention_inputs_vec_kernel<4>, grid, dim3(AI_WARPS * 32), 0, stream, (const bf16*)qkv, qkv_stride, (bf16*)q_out,
-                      (bf16*)k_cache, (bf16*)v_cache, (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, cos_sin, positions, slots, nq,
-                      nkv, page_size, write_kv);
-        else
-            ti_launch(attention_inputs_vec_kernel<2>, grid, dim3(AI_WARPS * 32), 0, stream, (const bf16*)qkv, qkv_stride, (bf16*)q_out,
-                      (bf16*)k_cache, (bf16*)v_cache, (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, cos_sin, positions, slots, nq,
-                      nkv, page_size, write_kv);
+#define AI_VEC_LAUNCH(VPL, HPW)                                                                                                     \
+    ti_launch(attention_inputs_vec_kernel<VPL, HPW>, dim3(n_tokens, ((heads_total + HPW - 1) / HPW + AI_WARPS - 1) / AI_WARPS),         \
+              dim3(AI_WARPS * 32), 0, stream, (const bf16*)qkv, qkv_stride, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache,               \
+              (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, cos_sin, positions, slots, nq, nkv, page_size, write_kv)
+        // Few tokens: one head per warp (latency counts); many: four heads per warp (memory traffic counts).
+        if (D == 128) { if (n_tokens <= 64) AI_VEC_LAUNCH(4, 1); else AI_VEC_LAUNCH(4, 4); }
+        else          { if (n_tokens <= 64) AI_VEC_LAUNCH(2, 1); else AI_VEC_LAUNCH(2, 4); }
+#undef AI_VEC_LAUNCH
         return ti_check_launch("attention_inputs");
     }
     TI_DISPATCH_DTYPE(dtype, (ti_launch(attention_inputs_kernel<T>, dim3(grid), dim3(AI_WARPS * 32), smem, stream, 
