@@ -505,23 +505,77 @@ int launch(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensor
     return ti_check_launch("gemm_tcgen05");
 }
 
-int launch_pair(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& my, const Params& p, int sm_count, cudaStream_t stream) {
+// How many pairs of blocks of the pair kernel the device holds at once (0: none, the kernel is not used).
+int pair_clusters(int sm_count) {
     static int clusters = -1;
     if (clusters < 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairCfg::SMEM);
-        if (e != cudaSuccess) return ti_fail("gemm_tcgen05 (pairs): %s", cudaGetErrorString(e));
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(sm_count & ~1); cfg.blockDim = dim3(PairCfg::THREADS); cfg.dynamicSmemBytes = PairCfg::SMEM;
-        int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel, &cfg);
-        if (e != cudaSuccess || n <= 0) { cudaGetLastError(); n = 0; }
-        clusters = n;
+        clusters = 0;
+        if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairCfg::SMEM) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(sm_count & ~1); cfg.blockDim = dim3(PairCfg::THREADS); cfg.dynamicSmemBytes = PairCfg::SMEM;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel, &cfg) == cudaSuccess && n > 0) clusters = n;
+        }
+        cudaGetLastError();
     }
-    if (clusters == 0) return 2;
+    return clusters;
+}
+
+int launch_pair(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& my, const Params& p, cudaStream_t stream) {
+    const int clusters = pair_clusters(0);
     const int tiles = p.m_tiles * p.n_tiles;
     const int pairs = tiles < clusters ? tiles : clusters;
     ti_launch(gemm_tcgen05_pair_kernel, dim3(2 * pairs), dim3(PairCfg::THREADS), PairCfg::SMEM, stream, mw, mx, my, y, p);
     return ti_check_launch("gemm_tcgen05 (pairs)");
+}
+
+// Chooses the tile shape and kernel for one product. (Giving the rows of a ragged last wave to a second
+// launch with smaller tiles was measured and is slower: the few tiles of a last wave run faster than
+// those of a full one, with the memory system and the power budget to themselves.)
+int gemm_dispatch(void* y, long long ldy, const void* x, long long ldx, const void* W, int n, int out, int in, int splits, int epilogue,
+                  const XieluParams& act, int* status, cudaStream_t stream, int sm_count) {
+    const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
+    Params p;
+    p.N = n; p.K = in;
+    // Wide token tiles take 256 weight rows per block when that is the cheaper way to cover the
+    // product: a 256-row tile costs about 1.5 times a 128-row tile (its MMAs are better fed), plus an
+    // epilogue that is not overlapped. With xIELU in it that epilogue is long, and only a long k
+    // amortises it (measured at k = 4096: 302 us against 296 us for the up projection of 2048 tokens).
+    int mt = 1;
+    const long long n_t = (n + bn - 1) / bn;
+    if (bn == 256 && splits <= 1 && (epilogue != EPI_XIELU || in >= 8192)) {
+        const long long waves1 = (((out + BM - 1) / BM) * n_t + sm_count - 1) / sm_count;
+        const long long waves2 = (((out + 2 * BM - 1) / (2 * BM)) * n_t + sm_count - 1) / sm_count;
+        if (3 * waves2 < 2 * waves1) mt = 2;
+    }
+    // Where 256-row blocks do not pay, two SMs share a 256 x 256 tile instead (cta_group::2): the same
+    // shared-memory fill per MMA, with both accumulator buffers kept for the epilogue to overlap
+    // (measured on 2048 tokens: up projection with xIELU 285 us against 296 us, q|k|v 80 us against 82 us).
+    const bool pair = mt == 1 && bn == 256 && splits <= 1 && out >= 2 * BM && pair_clusters(sm_count) > 0;
+    if (pair) mt = 2;
+    p.M = out;
+    p.m_tiles = (out + mt * BM - 1) / (mt * BM);
+    p.n_tiles = (int)n_t;
+    p.k_blocks = (in + BK - 1) / BK;
+    p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
+    TI_REQUIRE(p.splits == 1 || epilogue == EPI_PARTIAL, "gemm_tcgen05: a split product leaves partial sums");
+    p.ldy = ldy; p.epilogue = epilogue; p.act = act; p.status = status;
+    CUtensorMap mw, mx, my;
+    if (int rc = tensor_map(&mw, W, out, in, in, BM)) return rc;
+    if (int rc = tensor_map(&mx, x, n, in, ldx, pair ? bn / 2 : bn)) return rc;   // a pair's blocks load half a token tile each
+    p.tma_out = bn >= 128 && (epilogue == EPI_NONE || epilogue == EPI_XIELU) && ldy % 8 == 0 && !((uintptr_t)y & 15);
+    if (p.tma_out) {
+        if (int rc = tensor_map(&my, y, n, out, ldy, 32, 32)) return rc;
+    } else {
+        my = mx;                   // not read
+    }
+    if (pair) return launch_pair(y, mw, mx, my, p, stream);
+    switch (bn) {
+        case 256: return mt == 2 ? launch<256, 2>(y, mw, mx, my, p, sm_count, stream) : launch<256, 1>(y, mw, mx, my, p, sm_count, stream);
+        case 128: return launch<128, 1>(y, mw, mx, my, p, sm_count, stream);
+        case 64: return launch<64, 1>(y, mw, mx, my, p, sm_count, stream);
+        default: return launch<32, 1>(y, mw, mx, my, p, sm_count, stream);
+    }
 }
 
 }  // namespace
@@ -546,48 +600,5 @@ extern "C" int ti_gemm_tcgen05(void* y, long long ldy, const void* x, long long 
         cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
         if (sm_count <= 0) sm_count = 148;
     }
-    const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
-    Params p;
-    p.M = out; p.N = n; p.K = in;
-    // Wide token tiles take 256 weight rows per block when that is the cheaper way to cover the
-    // product: a 256-row tile costs about 1.5 times a 128-row tile (its MMAs are better fed), plus an
-    // epilogue that is not overlapped. With xIELU in it that epilogue is long, and only a long k
-    // amortises it (measured at k = 4096: 302 us against 296 us for the up projection of 2048 tokens).
-    int mt = 1;
-    if (bn == 256 && splits <= 1 && (epilogue != EPI_XIELU || in >= 8192)) {
-        const long long n_t = (n + bn - 1) / bn;
-        const long long waves1 = (((out + BM - 1) / BM) * n_t + sm_count - 1) / sm_count;
-        const long long waves2 = (((out + 2 * BM - 1) / (2 * BM)) * n_t + sm_count - 1) / sm_count;
-        if (3 * waves2 < 2 * waves1) mt = 2;
-    }
-    // Where 256-row blocks do not pay, two SMs share a 256 x 256 tile instead (cta_group::2): the same
-    // shared-memory fill per MMA, with both accumulator buffers kept for the epilogue to overlap
-    // (measured on 2048 tokens: up projection with xIELU 285 us against 296 us, q|k|v 80 us against 82 us).
-    const bool pair = mt == 1 && bn == 256 && splits <= 1 && out >= 2 * BM;
-    if (pair) mt = 2;
-    p.m_tiles = (out + mt * BM - 1) / (mt * BM);
-    p.n_tiles = (n + bn - 1) / bn;
-    p.k_blocks = (in + BK - 1) / BK;
-    p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
-    TI_REQUIRE(p.splits == 1 || epilogue == EPI_PARTIAL, "gemm_tcgen05: a split product leaves partial sums");
-    p.ldy = ldy; p.epilogue = epilogue; p.act = XieluParams{alpha_p, alpha_n, beta, eps}; p.status = status;
-    CUtensorMap mw, mx, my;
-    if (int rc = tensor_map(&mw, W, out, in, in, BM)) return rc;
-    if (int rc = tensor_map(&mx, x, n, in, ldx, pair ? bn / 2 : bn)) return rc;   // a pair's blocks load half a token tile each
-    p.tma_out = bn >= 128 && (epilogue == EPI_NONE || epilogue == EPI_XIELU) && ldy % 8 == 0 && !((uintptr_t)y & 15);
-    if (p.tma_out) {
-        if (int rc = tensor_map(&my, y, n, out, ldy, 32, 32)) return rc;
-    } else {
-        my = mx;                   // not read
-    }
-    if (pair) {
-        const int rc = launch_pair(y, mw, mx, my, p, sm_count, stream);
-        if (rc != 2) return rc;
-    }
-    switch (bn) {
-        case 256: return mt == 2 ? launch<256, 2>(y, mw, mx, my, p, sm_count, stream) : launch<256, 1>(y, mw, mx, my, p, sm_count, stream);
-        case 128: return launch<128, 1>(y, mw, mx, my, p, sm_count, stream);
-        case 64: return launch<64, 1>(y, mw, mx, my, p, sm_count, stream);
-        default: return launch<32, 1>(y, mw, mx, my, p, sm_count, stream);
-    }
+    return gemm_dispatch(y, ldy, x, ldx, W, n, out, in, splits, epilogue, XieluParams{alpha_p, alpha_n, beta, eps}, status, stream, sm_count);
 }
