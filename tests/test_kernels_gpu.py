@@ -287,18 +287,21 @@ def test_argmax_ties_go_to_the_smaller_id(ops):
     assert out.tolist() == [int(logits[0].argmax()), 30, 0, 999, 0]
 
 
+@pytest.mark.parametrize("V", [1531, 6007])
 @pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 5, 1.0), (0.7, 50, 0.9), (1.3, 0, 0.5), (1.0, 1, 1.0), (0.5, 200, 0.95)])
-def test_device_sampler_follows_the_host_rule(ops, temperature, top_k, top_p):
+def test_device_sampler_follows_the_host_rule(ops, temperature, top_k, top_p, V):
     """Same token as the plain rule for the same (logits, settings, u), except where u × total or top_p
     falls within 1e-5 of a boundary of the cumulative distribution (the reference's own filter,
-    test/ops/tile.jl:264-298)."""
+    test/ops/tile.jl:264-298). In the larger vocabulary the flat row and the row of ties put more tokens
+    into one histogram bin than the kernel's fast path gathers, so those rows take its exact path."""
     torch.manual_seed(8)
-    V, rows = 1531, 24
+    rows = 24
     logits = torch.randn(rows, V) * 2.5
     logits[0] = 0.0                                   # flat
     logits[1, 100] = logits[1, 900] = logits[1].max() + 1     # ties at the top
     logits[2, :] = -30.0; logits[2, V - 1] = 5.0             # everything in the last token
     logits[3, ::7] = logits[3, 0]                            # many ties across the k-th
+    logits[4, 5:] = logits[4, 5]                             # a few tokens, then one crowd of equals
     seeds = [(1234567 * (r + 1)) & 0xFFFFFFFF for r in range(rows)]
     from tileinfer_b200.sampling.device import _as_i32
     sd = _as_i32(seeds).cuda()

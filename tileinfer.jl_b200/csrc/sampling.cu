@@ -8,11 +8,17 @@
 // counter) (sampler.jl:34-47). The reference samples on the device only for top_k <= 64 and
 // sends the logits to the host otherwise; here every setting runs on the device.
 //
-// Method: no sort. Each token gets a 56-bit key (descending-ordered logit bits, then id), so
-// best-first order is ascending key order, and "the first key whose cumulative weight
-// reaches X" is found by a radix select over that key, 8 bits a pass, with a histogram of
-// weights. Weights are 2^40 fixed-point integers, so sums do not depend on the order of the
-// atomic additions and the result is deterministic.
+// Method: no sort of the vocabulary. Each token gets a 56-bit key (descending-ordered logit bits, then
+// id), so best-first order is ascending key order, and every step of the rule is "the first key whose
+// cumulative weight reaches X". Weights are 2^40 fixed-point integers, so sums do not depend on the
+// order of the atomic additions and the result is deterministic.
+//   Fast path: ONE pass over the row builds a histogram of weights and counts over 4096 bins of the
+//   scaled distance from the maximum, (max - l) / T in steps of 1/128 (the bin is monotone in the
+//   key, and weights vanish beyond 28.4). A selection then scans the bins for the one that holds its
+//   target, gathers that bin's few tokens in a second pass, sorts them by key in shared memory and
+//   scans them. top-k, top-p and the draw share the histogram: it is cut off at each bound found.
+//   Exact path: a bin with more than 4096 tokens (a flat row of a large vocabulary) sends the row to a
+//   radix select over the key, 8 bits a pass, with a histogram of weights per pass.
 #include "common.cuh"
 
 typedef unsigned long long u64;
@@ -147,6 +153,14 @@ extern "C" int ti_argmax(const float* logits, long long ld, int n_rows, int voca
 }
 
 // ------------------------------------------------------------------------------ sampling
+// ceil(u x total) with u = r24 / 2^24, without leaving integers: total < 2^58 and r24 < 2^24 need 128 bits.
+__device__ __forceinline__ u64 draw_target(u64 total, u32 r24) {
+    const u64 hi = __umul64hi(total, (u64)r24), lo = total * (u64)r24;
+    u64 target = (hi << 40) | (lo >> 24);
+    if (lo & 0xFFFFFFull) target += 1;
+    return target;
+}
+
 struct Selected {
     u64 key;          // the selected token's 56-bit key
     u64 before;       // weight of the keys before it (within the set)
@@ -219,23 +233,219 @@ __device__ Selected select_key(const float* row, int vocab, int mode, u64 bound,
     return r;
 }
 
-__global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* logits, long long ld, int vocab,
-                                                            float inv_t, int top_k, float top_p,
-                                                            const u32* seeds, u32* counters,
-                                                            int* __restrict__ out) {
-    extern __shared__ u64 dyn[];
-    u64* hist = dyn;
-    u64* totals = dyn + SM_WARPS * 256;
-    u64* shared = totals + 256;
-    __shared__ float scratch[33];
-    const float* row = logits + (size_t)blockIdx.x * ld;
-    pdl_wait();
-    pdl_launch_dependents();
+// ------------------------------------------------------------------------------ the binned fast path
+// f(index, logit) for every token of the row, the block's threads sharing them out; sixteen values per
+// thread are in flight at a time (one L2 round trip per value would otherwise bound a pass).
+template <typename F> __device__ __forceinline__ void for_each_logit(const float* row, int vocab, F f) {
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        const int n4 = vocab >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int i = threadIdx.x; i < n4; i += 4 * SM_THREADS) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i + u * SM_THREADS < n4) v[u] = __ldcg(row4 + i + u * SM_THREADS);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = i + u * SM_THREADS;
+                if (j < n4) { f(4 * j, v[u].x); f(4 * j + 1, v[u].y); f(4 * j + 2, v[u].z); f(4 * j + 3, v[u].w); }
+            }
+        }
+        done = n4 * 4;
+    }
+    for (int i = done + threadIdx.x; i < vocab; i += 4 * SM_THREADS) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i + u * SM_THREADS < vocab) v[u] = __ldcg(row + i + u * SM_THREADS);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i + u * SM_THREADS < vocab) f(i + u * SM_THREADS, v[u]);
+    }
+}
 
-    float maxl = -INFINITY;
-    for (int i = threadIdx.x; i < vocab; i += SM_THREADS) maxl = fmaxf(maxl, __ldcg(row + i));
-    maxl = block_max(maxl, scratch);
+#define SB_BINS 4096
+#define SB_PER_NAT 128.0f
+#define SB_CAP 4096
 
+struct Binned {
+    u64* mass;        // [SB_BINS] weights per bin
+    u32* count;       // [SB_BINS] tokens per bin
+    u64* cand_key;    // [SB_CAP]
+    u64* cand_w;      // [SB_CAP]
+    u64* scan;        // [SM_WARPS + 8] scratch of the block scans and results
+};
+
+__device__ __forceinline__ int token_bin(float l, float maxl, float inv_t) {
+    const float d = (maxl - l) * inv_t * SB_PER_NAT;
+    return d >= (float)(SB_BINS - 1) ? SB_BINS - 1 : (int)d;             // NaN goes to the last bin as well
+}
+
+// Inclusive block scan of one value per thread; every thread also gets the total. `scratch`: SM_WARPS + 1 words.
+__device__ __forceinline__ u64 block_scan(u64 v, u64* scratch, u64& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const u64 t = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += t;
+    }
+    __syncthreads();
+    if (lane == 31) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        u64 t = lane < SM_WARPS ? scratch[lane] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const u64 u = __shfl_up_sync(0xffffffffu, t, o);
+            if (lane >= o) t += u;
+        }
+        scratch[lane] = t;
+        if (lane == 31) scratch[SM_WARPS] = t;
+    }
+    __syncthreads();
+    total = scratch[SM_WARPS];
+    return v + (warp > 0 ? scratch[warp - 1] : 0);
+}
+
+struct BinSelected {
+    Selected sel;     // key, weight before and through it (over the whole set, in the mode's weights)
+    int bin;          // the bin it lies in
+    u64 mass_in_bin;  // mass and count of the bin's tokens up to and including it
+    u32 count_in_bin;
+    bool overflow;    // the bin held more than SB_CAP tokens: nothing was selected
+};
+
+// The first key (ascending) among keys <= bound whose cumulative weight (mode: counts or masses) reaches
+// target, from the histogram of the set and one gathering pass over the row. All threads get it.
+__device__ BinSelected select_binned(const float* row, int vocab, int mode, u64 bound, u64 target, float maxl, float inv_t,
+                                     const Binned& h) {
+    BinSelected r;
+    if (target == 0) target = 1;
+    // 1. The bin: four bins per thread, block scan.
+    u64 local[4], sum = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int b = threadIdx.x * 4 + e;
+        local[e] = mode == W_COUNT ? (u64)h.count[b] : h.mass[b];
+        sum += local[e];
+    }
+    u64 total;
+    const u64 incl = block_scan(sum, h.scan, total);
+    u64* res = h.scan + SM_WARPS + 1;                  // res[0] bin, res[1] weight before the bin, res[2] last bin with weight
+    if (threadIdx.x == 0) { res[0] = ~0ull; res[2] = 0; }
+    __syncthreads();
+    {
+        u64 cum = incl - sum;
+        int last = -1;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (local[e] && cum < target && cum + local[e] >= target) { res[0] = (u64)(threadIdx.x * 4 + e); res[1] = cum; }
+            if (local[e]) last = threadIdx.x * 4 + e;
+            cum += local[e];
+        }
+        if (last >= 0) atomicMax(&res[2], (u64)last);
+    }
+    __syncthreads();
+    if (res[0] == ~0ull) {                             // the target lies beyond the set: its last bin with weight
+        const int last = (int)res[2];
+        __syncthreads();
+        if (threadIdx.x == last / 4) { res[0] = (u64)last; res[1] = incl - sum; for (int e = 0; e < last % 4; ++e) res[1] += local[e]; }
+        __syncthreads();
+    }
+    const int bin = (int)res[0];
+    const u64 base = res[1];
+    __syncthreads();
+    // 2. Its tokens.
+    u32* n_cand = reinterpret_cast<u32*>(h.scan + SM_WARPS + 6);
+    if (threadIdx.x == 0) *n_cand = 0;
+    __syncthreads();
+    for_each_logit(row, vocab, [&](int i, float l) {
+        if (token_bin(l, maxl, inv_t) != bin) return;
+        const u64 key = ((u64)desc_key(l) << SM_ID_BITS) | (u64)i;
+        if (key > bound) return;
+        const u64 w = token_weight(W_MASS, l, maxl, inv_t);
+        if (mode == W_MASS && w == 0) return;
+        const u32 at = atomicAdd(n_cand, 1u);
+        if (at < SB_CAP) { h.cand_key[at] = key; h.cand_w[at] = w; }
+    });
+    __syncthreads();
+    const int n = (int)*n_cand;
+    r.bin = bin;
+    r.overflow = n > SB_CAP || n == 0;
+    if (r.overflow) { __syncthreads(); return r; }
+    // 3. In key order: bitonic sort of the next power of two, then scans of counts and masses.
+    int n2 = 1;
+    while (n2 < n) n2 <<= 1;
+    for (int i = n + threadIdx.x; i < n2; i += SM_THREADS) { h.cand_key[i] = ~0ull; h.cand_w[i] = 0; }
+    __syncthreads();
+    for (int size = 2; size <= n2; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int t = threadIdx.x; t < (n2 >> 1); t += SM_THREADS) {
+                const int lo = 2 * t - (t & (stride - 1)), hi = lo + stride;
+                const bool up = (lo & size) == 0;
+                const u64 a = h.cand_key[lo], b = h.cand_key[hi];
+                if ((a > b) == up) {
+                    h.cand_key[lo] = b; h.cand_key[hi] = a;
+                    const u64 wa = h.cand_w[lo]; h.cand_w[lo] = h.cand_w[hi]; h.cand_w[hi] = wa;
+                }
+            }
+            __syncthreads();
+        }
+    // Each thread owns four consecutive places; the first place whose cumulative weight reaches the rest of the target.
+    const u64 rest = target - base;
+    u64 wsel[4], wmass[4], ssum = 0, msum = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int i = threadIdx.x * 4 + e;
+        wmass[e] = i < n ? h.cand_w[i] : 0;
+        wsel[e] = i < n ? (mode == W_COUNT ? 1ull : wmass[e]) : 0;
+        ssum += wsel[e]; msum += wmass[e];
+    }
+    u64 stotal, mtotal;
+    const u64 sincl = block_scan(ssum, h.scan, stotal);
+    const u64 mincl = block_scan(msum, h.scan, mtotal);
+    u64* pick = h.scan + SM_WARPS + 1;                 // pick[0] place, [1] weight before, [2] through, [3] mass through
+    if (threadIdx.x == 0) pick[0] = ~0ull;
+    __syncthreads();
+    {
+        u64 cum = sincl - ssum, mcum = mincl - msum;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = threadIdx.x * 4 + e;
+            mcum += wmass[e];
+            if (i < n && cum < rest && cum + wsel[e] >= rest) { pick[0] = (u64)i; pick[1] = cum; pick[2] = cum + wsel[e]; pick[3] = mcum; }
+            cum += wsel[e];
+        }
+    }
+    __syncthreads();
+    if (pick[0] == ~0ull) {                            // beyond the bin's weight: its last token
+        __syncthreads();
+        if (threadIdx.x == (n - 1) / 4) { pick[0] = (u64)(n - 1); pick[1] = stotal - wsel[(n - 1) % 4]; pick[2] = stotal; pick[3] = mtotal; }
+        __syncthreads();
+    }
+    const int place = (int)pick[0];
+    r.sel.key = h.cand_key[place];
+    r.sel.before = base + pick[1];
+    r.sel.through = base + pick[2];
+    r.mass_in_bin = pick[3];
+    r.count_in_bin = (u32)(place + 1);
+    __syncthreads();
+    return r;
+}
+
+// The set shrinks to the keys up to a selected one: its bin keeps what lies before and at it, later bins empty.
+__device__ __forceinline__ void cut_histogram(const Binned& h, const BinSelected& at) {
+    for (int b = threadIdx.x; b < SB_BINS; b += SM_THREADS) {
+        if (b == at.bin) { h.mass[b] = at.mass_in_bin; h.count[b] = at.count_in_bin; }
+        else if (b > at.bin) { h.mass[b] = 0; h.count[b] = 0; }
+    }
+    __syncthreads();
+}
+
+// The rule by the radix select alone (any row; seven passes over the row per selection).
+__device__ int sample_exact(const float* row, int vocab, float inv_t, int top_k, float top_p, u32 r24, float maxl, u64* hist,
+                            u64* totals, u64* shared) {
     u64 bound = ~0ull;
     if (top_k > 0 && top_k < vocab) {
         const Selected k = select_key(row, vocab, W_COUNT, bound, (u64)top_k, maxl, inv_t, hist, totals, shared);
@@ -264,15 +474,91 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* logits,
         bound = p.key;
         total = p.through;
     }
+    const Selected s = select_key(row, vocab, W_MASS, bound, draw_target(total, r24), maxl, inv_t, hist, totals, shared);
+    return (int)(s.key & ((1ull << SM_ID_BITS) - 1));
+}
+
+__global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* logits, long long ld, int vocab,
+                                                            float inv_t, int top_k, float top_p,
+                                                            const u32* seeds, u32* counters,
+                                                            int* __restrict__ out) {
+    extern __shared__ u64 dyn[];
+    __shared__ float scratch[33];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    pdl_wait();
+    pdl_launch_dependents();
+
+    float maxl = -INFINITY;
+    for_each_logit(row, vocab, [&](int, float l) { maxl = fmaxf(maxl, l); });
+    maxl = block_max(maxl, scratch);
     const u32 counter = counters[blockIdx.x];
     const u32 r24 = mix32(mix32(seeds[blockIdx.x]) ^ counter) >> 8;          // u = r24 · 2^-24
-    // ceil(u × total) without leaving integers: total < 2^58 and r24 < 2^24 need 128 bits.
-    const u64 hi = __umul64hi(total, (u64)r24), lo = total * (u64)r24;
-    u64 target = (hi << 40) | (lo >> 24);
-    if (lo & 0xFFFFFFull) target += 1;
-    const Selected s = select_key(row, vocab, W_MASS, bound, target, maxl, inv_t, hist, totals, shared);
+
+    // Fast path: one histogram of the row, cut off at each bound; a crowded bin sends the row to the exact path.
+    Binned h;
+    h.mass = dyn;
+    h.cand_key = dyn + SB_BINS;
+    h.cand_w = h.cand_key + SB_CAP;
+    h.scan = h.cand_w + SB_CAP;
+    h.count = reinterpret_cast<u32*>(h.scan + SM_WARPS + 8);
+    // Masses are summed as two 32-bit halves with the carry passed on by hand: 64-bit additions in shared
+    // memory are compare-and-swap loops, and these atomics bound the pass. The halves borrow the
+    // candidates' place until the pass is over.
+    u32* mass_lo = reinterpret_cast<u32*>(h.cand_key);
+    u32* mass_hi = mass_lo + SB_BINS;
+    for (int b = threadIdx.x; b < SB_BINS; b += SM_THREADS) { mass_lo[b] = 0; mass_hi[b] = 0; h.count[b] = 0; }
+    __syncthreads();
+    const bool need_counts = top_k > 0 && top_k < vocab;
+    for_each_logit(row, vocab, [&](int, float l) {
+        const int b = token_bin(l, maxl, inv_t);
+        const u64 w = token_weight(W_MASS, l, maxl, inv_t);
+        if (w) {
+            const u32 lo = (u32)w;
+            u32 hi = (u32)(w >> 32);
+            if (lo) {
+                const u32 old = atomicAdd(&mass_lo[b], lo);
+                hi += (old + lo < old) ? 1u : 0u;
+            }
+            if (hi) atomicAdd(&mass_hi[b], hi);
+        }
+        if (need_counts) atomicAdd(&h.count[b], 1u);      // only top-k reads the counts
+    });
+    __syncthreads();
+    for (int b = threadIdx.x; b < SB_BINS; b += SM_THREADS) h.mass[b] = ((u64)mass_hi[b] << 32) | (u64)mass_lo[b];
+    __syncthreads();
+    int token = -1;
+    do {
+        u64 bound = ~0ull;
+        if (top_k > 0 && top_k < vocab) {
+            const BinSelected k = select_binned(row, vocab, W_COUNT, bound, (u64)top_k, maxl, inv_t, h);
+            if (k.overflow) break;
+            bound = k.sel.key;
+            cut_histogram(h, k);
+        }
+        u64 part = 0, total;
+        for (int b = threadIdx.x; b < SB_BINS; b += SM_THREADS) part += h.mass[b];
+        block_scan(part, h.scan, total);
+        if (top_p < 1.0f) {
+            const u64 target = (u64)ceil((double)top_p * (double)total);
+            const BinSelected p = select_binned(row, vocab, W_MASS, bound, target, maxl, inv_t, h);
+            if (p.overflow) break;
+            bound = p.sel.key;
+            total = p.sel.through;
+            cut_histogram(h, p);
+        }
+        const BinSelected d = select_binned(row, vocab, W_MASS, bound, draw_target(total, r24), maxl, inv_t, h);
+        if (d.overflow) break;
+        token = (int)(d.sel.key & ((1ull << SM_ID_BITS) - 1));
+    } while (false);
+    if (token < 0) {                                       // uniform across the block: every thread saw the same overflow
+        __syncthreads();
+        u64* hist = dyn;
+        u64* totals = dyn + SM_WARPS * 256;
+        u64* shared = totals + 256;
+        token = sample_exact(row, vocab, inv_t, top_k, top_p, r24, maxl, hist, totals, shared);
+    }
     if (threadIdx.x == 0) {
-        out[blockIdx.x] = (int)(s.key & ((1ull << SM_ID_BITS) - 1));
+        out[blockIdx.x] = token;
         counters[blockIdx.x] = counter + 1;
     }
 }
@@ -284,7 +570,9 @@ extern "C" int ti_sample(const float* logits, long long ld, int n_rows, int voca
     TI_REQUIRE(temperature > 0.f, "sample: temperature must be > 0 (use argmax for greedy)");
     TI_REQUIRE(top_k >= 0, "sample: top_k must be >= 0");
     TI_REQUIRE(top_p > 0.f && top_p <= 1.f, "sample: top_p must be in (0, 1]");
-    const size_t smem = (size_t)(SM_WARPS * 256 + 256 + 4) * sizeof(u64);
+    // The binned path's layout (histogram, candidates, scan scratch, counts); the exact path's is smaller and shares it.
+    const size_t smem = (size_t)(SB_BINS + 2 * SB_CAP + SM_WARPS + 8) * sizeof(u64) + (size_t)SB_BINS * sizeof(u32);
+    static_assert((SB_BINS + 2 * SB_CAP + SM_WARPS + 8) >= (SM_WARPS * 256 + 256 + 4), "the exact path must fit the same shared memory");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
