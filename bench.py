@@ -28,7 +28,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Apertus-8B sizes.
+# The configuration the reference quotes its headline numbers on: Apertus-8B sizes.
 APERTUS_8B = {
     "architectures": ["ApertusForCausalLM"], "model_type": "apertus",
     "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
