@@ -40,6 +40,18 @@ TINY_C = {
     "max_position_embeddings": 2048, "attention_bias": False, "mlp_bias": False,
 }
 
+# A fourth one with the head size (64) and a group (2) that the tensor-core prefill attention takes, and
+# widths that the tensor-core products take, so that replay runs through those kernels too.
+TINY_D = {
+    "architectures": ["ApertusForCausalLM"], "model_type": "apertus",
+    "num_hidden_layers": 2, "hidden_size": 136, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 328, "vocab_size": 392, "rope_theta": 1000000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 128,
+                     "low_freq_factor": 1.0, "high_freq_factor": 4.0},
+    "rms_norm_eps": 2e-6, "qk_norm": True, "tie_word_embeddings": False, "hidden_act": "xielu",
+    "max_position_embeddings": 1024, "attention_bias": False, "mlp_bias": False,
+}
+
 
 def reference_fixture_folder(out_dir: str) -> str:
     """The reference's tiny checkpoint, rewritten to the ApertusForCausalLM layout in ``out_dir``:

@@ -222,9 +222,17 @@ def test_one_layer_at_apertus_8b_sizes(dtype):
         refs = [plain.forward(pc, pw, p, pdt) for p in prompts]
         eng = ti.load_model(folder, dtype=dtype, max_context=256, max_seqs=2)
         tol = tolerance(dtype, refs[0])
+        from tileinfer_b200.kernels import library
+        before = dict(library.call_counts)
         a = eng.new_sequence()
         got = eng.step([(a, prompts[0][:142])], [list(range(142))]).cpu()
         assert float((got - refs[0][:142]).abs().max()) <= tol
+        used = {k: v - before.get(k, 0) for k, v in library.call_counts.items() if v > before.get(k, 0)}
+        if dtype == "bfloat16":                                        # the kernels written for these sizes did the work
+            assert used.get("ti_attention_prefill_tc") == 1 and used.get("ti_gemm_tcgen05") == 5         # four of the layer, and the head
+            assert "ti_attention_prefill" not in used and "ti_gemm_plain" not in used and "ti_attention_plain" not in used
+        else:
+            assert "ti_gemm_tcgen05" not in used and "ti_attention_prefill_tc" not in used
         for t in range(142, 150):                                      # the last tokens one by one
             row = eng.step([(a, [prompts[0][t]])]).cpu()[0]
             assert float((row - refs[0][t]).abs().max()) <= tol, t

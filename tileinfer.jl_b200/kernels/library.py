@@ -14,19 +14,24 @@ _lib = None
 # Number of kernels launched through this module so far (a launch inside a CUDA-graph capture counts
 # once; its replays are counted by whoever replays the graph).
 launch_count = 0
+call_counts = {}              # entry point -> calls that launched (tests read which kernels a step used)
 
 
 class _Counted:
-    """A C entry point that launches ``kernels`` kernels per call."""
-    __slots__ = ("fn", "kernels")
+    """A C entry point that launches ``kernels`` kernels per call; a call that refuses its sizes
+    (return code 2) has launched none."""
+    __slots__ = ("fn", "kernels", "name")
 
-    def __init__(self, fn, kernels=1):
-        self.fn, self.kernels = fn, kernels
+    def __init__(self, fn, name, kernels=1):
+        self.fn, self.name, self.kernels = fn, name, kernels
 
     def __call__(self, *args):
         global launch_count
-        launch_count += self.kernels
-        return self.fn(*args)
+        rc = self.fn(*args)
+        if rc != 2:
+            launch_count += self.kernels
+            call_counts[self.name] = call_counts.get(self.name, 0) + 1
+        return rc
 
 
 def add_launches(n: int) -> None:
@@ -81,7 +86,7 @@ def lib():
         fn = getattr(handle, name)
         fn.restype = c_int
         fn.argtypes = args
-        setattr(wrapped, name, _Counted(fn))
+        setattr(wrapped, name, _Counted(fn, name))
     _lib = wrapped
     return wrapped
 
