@@ -8,7 +8,7 @@ import torch
 from . import ops
 from .library import KernelError, add_launches, check, lib
 
-GEMV_MAX_TOKENS = 16
+GEMV_MAX_TOKENS = 8          # from 9 tokens on the tensor-core product is faster (measured per layer: 151 against 162 us at 12 tokens)
 SM_COUNT = 148
 
 
