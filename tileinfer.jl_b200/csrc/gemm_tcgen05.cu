@@ -293,16 +293,19 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
 // A cluster of two blocks owns a tile of 256 weight rows x 256 tokens with tcgen05.mma.cta_group::2:
 // each block stages its own 128 weight rows and HALF of the tokens (the tensor cores read the other
 // half from the partner's shared memory), and each block's tensor memory receives its 128 rows of the
-// result. A k block thus costs each SM 32 KB of shared-memory fill for 512 tensor-core cycles (48 KB with
+// result. 64 of k thus cost each SM 32 KB of shared-memory fill for 512 tensor-core cycles (48 KB with
 // one SM per tile), with both accumulator buffers kept, so the epilogue still overlaps the next tile.
+// A stage holds 128 of k (64 KB, three stages): one barrier round trip per 1,024 tensor-core cycles.
 // Block 0 of the pair issues the MMAs; its `full` barriers count the bytes of both blocks' loads; commits
 // arrive on both blocks' barriers; the partner's epilogue warps arrive on block 0's accumulator barrier.
 struct PairCfg {
     static constexpr int BN = 256;                     // tokens per tile
     static constexpr int EPI_WARPS = 8;
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
-    static constexpr int A_BYTES = BM * BK * 2;        // this block's 128 weight rows
-    static constexpr int B_BYTES = (BN / 2) * BK * 2;  // this block's half of the tokens
+    static constexpr int KB = 2;                       // 64-wide (one swizzle row) k blocks per stage: 128 of k
+    static constexpr int ATOM_BYTES = 128 * BK * 2;    // 128 rows of one swizzle row each
+    static constexpr int A_BYTES = KB * ATOM_BYTES;    // this block's 128 weight rows
+    static constexpr int B_BYTES = KB * ATOM_BYTES;    // this block's half (128) of the tokens
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int OUT_BYTES = EPI_WARPS * 2 * OUT_TILE_BYTES;
     static constexpr int STAGES = (SMEM_LIMIT - 2048 - OUT_BYTES) / STAGE_BYTES;
@@ -401,8 +404,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                     if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * C::STAGE_BYTES);
                     const unsigned bar = map_to_block(full0 + 8 * stage, 0);
                     const unsigned a_dst = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
-                    tma_load_2d_pair(a_dst, &map_w, kb * BK, (it.m * 2 + (int)rank) * BM, bar);
-                    tma_load_2d_pair(a_dst + C::A_BYTES, &map_x, kb * BK, it.n * BN + (int)rank * (BN / 2), bar);
+#pragma unroll
+                    for (int a = 0; a < C::KB; ++a) {
+                        tma_load_2d_pair(a_dst + a * C::ATOM_BYTES, &map_w, (kb * C::KB + a) * BK, (it.m * 2 + (int)rank) * BM, bar);
+                        tma_load_2d_pair(a_dst + C::A_BYTES + a * C::ATOM_BYTES, &map_x, (kb * C::KB + a) * BK,
+                                         it.n * BN + (int)rank * (BN / 2), bar);
+                    }
                 }
                 __syncwarp();
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -428,11 +435,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
                 tc_fence_after();
                 if (lane == 0) {
                     const unsigned a_addr = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
-                    const unsigned long long da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + C::A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_bf16_pair(d_tmem, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), IDESC,
+                    for (int k = 0; k < C::KB * BK / 16; ++k) {        // 16 k = 32 bytes along the swizzled row; 64 k = the next block of rows
+                        const unsigned off = (k / 4) * C::ATOM_BYTES + (k % 4) * 32;
+                        umma_bf16_pair(d_tmem, smem_desc_sw128(a_addr + off), smem_desc_sw128(a_addr + C::A_BYTES + off), IDESC,
                                        (kb > it.kb_lo || k > 0) ? 1u : 0u);
+                    }
                     umma_commit_pair(empty0 + 8 * stage);  // the stage is free in both blocks once these MMAs have read it
                 }
                 __syncwarp();
@@ -537,26 +545,26 @@ int gemm_dispatch(void* y, long long ldy, const void* x, long long ldx, const vo
     const int bn = n > 128 ? 256 : n > 64 ? 128 : n > 32 ? 64 : 32;
     Params p;
     p.N = n; p.K = in;
-    // Wide token tiles take 256 weight rows per block when that is the cheaper way to cover the
-    // product: a 256-row tile costs about 1.5 times a 128-row tile (its MMAs are better fed), plus an
-    // epilogue that is not overlapped. With xIELU in it that epilogue is long, and only a long k
-    // amortises it (measured at k = 4096: 302 us against 296 us for the up projection of 2048 tokens).
+    // Wide token tiles (more than 128 tokens): two SMs share a tile of 256 weight rows x 256 tokens
+    // (cta_group::2): per MMA each SM fills 32 KB of shared memory instead of 48 KB, both accumulator buffers
+    // stay, so the epilogue (xIELU included) overlaps the next tile, and a stage of 128 of k means one barrier
+    // round trip per 1,024 tensor-core cycles. Measured on 2048 tokens: up projection with xIELU 257 us
+    // (296 us with 128-row blocks of one SM), q|k|v 72 us (82 us), o 49 us (55 us).
+    // With a long k (the down projection) one block per SM with 256 weight rows, whose epilogue is not
+    // overlapped but rare, is a little faster still (233 us against 239 us), where it needs fewer waves.
     int mt = 1;
     const long long n_t = (n + bn - 1) / bn;
-    if (bn == 256 && splits <= 1 && (epilogue != EPI_XIELU || in >= 8192)) {
+    if (bn == 256 && splits <= 1 && in >= 8192) {
         const long long waves1 = (((out + BM - 1) / BM) * n_t + sm_count - 1) / sm_count;
         const long long waves2 = (((out + 2 * BM - 1) / (2 * BM)) * n_t + sm_count - 1) / sm_count;
         if (3 * waves2 < 2 * waves1) mt = 2;
     }
-    // Where 256-row blocks do not pay, two SMs share a 256 x 256 tile instead (cta_group::2): the same
-    // shared-memory fill per MMA, with both accumulator buffers kept for the epilogue to overlap
-    // (measured on 2048 tokens: up projection with xIELU 285 us against 296 us, q|k|v 80 us against 82 us).
     const bool pair = mt == 1 && bn == 256 && splits <= 1 && out >= 2 * BM && pair_clusters(sm_count) > 0;
     if (pair) mt = 2;
     p.M = out;
     p.m_tiles = (out + mt * BM - 1) / (mt * BM);
     p.n_tiles = (int)n_t;
-    p.k_blocks = (in + BK - 1) / BK;
+    p.k_blocks = pair ? (in + PairCfg::KB * BK - 1) / (PairCfg::KB * BK) : (in + BK - 1) / BK;     // the pair kernel's stages hold 128 of k
     p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
     TI_REQUIRE(p.splits == 1 || epilogue == EPI_PARTIAL, "gemm_tcgen05: a split product leaves partial sums");
     p.ldy = ldy; p.epilogue = epilogue; p.act = act; p.status = status;
