@@ -184,6 +184,33 @@ def test_a_long_prompt_is_cut_into_chunks_without_changing_results(models):
     assert float((outs[0] - ref).abs().max()) < 2e-5
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_in_chunks_through_the_tensor_core_attention(dtype):
+    """1,500 tokens at head size 64 (the tensor-core prefill attention in bfloat16) in steps of at most
+    512: the later chunks attend to over a thousand cached keys (many key steps, pages of earlier
+    chunks), far beyond the 128 positions up to which this configuration's rotation is unscaled. Logits
+    along the prompt and of a few decoded tokens against the plain implementation."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.weights import write_model_folder
+    with tempfile.TemporaryDirectory() as d:
+        folder = write_model_folder(ApertusConfig.from_dict(dict(helpers.TINY_D, max_position_embeddings=2048)), 9, os.path.join(d, "m"))
+        pc, pw = plain.load_folder(folder)
+        prompt = helpers.random_prompts(pc.vocab, [1506], 15)[0]
+        pdt = torch.float32 if dtype == "float32" else torch.bfloat16
+        ref = plain.forward(pc, pw, prompt, pdt)
+        eng = ti.Engine.load(folder, dtype=dtype, max_context=1536, max_seqs=1, max_tokens=1536, max_step_tokens=512)
+        tol = tolerance(dtype, ref)
+        a = eng.new_sequence()
+        want = [0, 300, 511, 512, 1023, 1024, 1400, 1499]
+        got = eng.step([(a, prompt[:1500])], [want]).cpu()
+        assert float((got - ref[want]).abs().max()) <= tol
+        for t in range(1500, 1506):
+            row = eng.step([(a, [prompt[t]])]).cpu()[0]
+            assert float((row - ref[t]).abs().max()) <= tol, t
+        eng.check_health()
+
+
 def test_command_line(models, capsys):
     from tileinfer_b200.cli import cli
     folder, pc, pw = models["A"]
