@@ -38,3 +38,29 @@ def test_mix32_is_lowbias32_and_sequence_seeds_differ():
     assert mix32(0) == 0 and mix32(1) == 0x6E5CB2E1 or True
     seeds = {sequence_seed(5, i) for i in range(100)}
     assert len(seeds) == 100 and sequence_seed(5, 3) != sequence_seed(6, 3)
+
+
+def test_decode_work_slots_are_shared_out_by_length():
+    """Every sequence gets at least one part and at most 32 and not more than it has pages; the parts of
+    all sequences fit the slots; a sequence's slots are consecutive and numbered; equal lengths give
+    every sequence the same number of parts; a long sequence among short ones gets most of them."""
+    import numpy as np
+    from tileinfer_b200.engine.step import split_tables
+    rng = np.random.default_rng(0)
+    for B, splits in ((1, 32), (3, 9), (8, 4), (8, 1), (37, 8), (64, 4)):
+        for lengths in (np.full(B, 1023), rng.integers(1, 40000, B), np.array([1] * (B - 1) + [30000])):
+            work, seq = split_tables(lengths.astype(np.int64), splits, 64)
+            T = B * splits
+            assert work.shape == (T, 2) and len(seq) == B
+            first, parts = seq >> 8, seq & 255
+            pages = -(-lengths // 64)
+            assert (parts >= 1).all() and (parts <= 32).all() and (parts <= np.maximum(pages, 1)).all()
+            assert int(parts.sum()) <= T and (first == np.cumsum(parts) - parts).all()
+            for b in range(B):
+                for s in range(int(parts[b])):
+                    assert work[first[b] + s].tolist() == [(b << 16) | (s << 8) | int(parts[b]), int(lengths[b])]
+            assert (work[int(parts.sum()):, 0] == -1).all()
+        work, seq = split_tables(np.full(B, 5000, dtype=np.int64), splits, 64)
+        assert ((seq & 255) == min(splits, 32)).all()
+    work, seq = split_tables(np.array([100, 100, 100, 30000], dtype=np.int64), 8, 64)
+    assert (seq & 255).tolist()[3] >= 25

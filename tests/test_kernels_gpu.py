@@ -460,6 +460,43 @@ def test_attention_window_edge(ops):
     close(out3[0], want[L - 1], dtype, ulps=5.0)
 
 
+def test_attention_decode_with_shared_out_slots(ops):
+    """Decode attention over sequences of very unequal lengths with the work slots shared out by length
+    (the long sequence read by many blocks, the short ones by one), against exact attention and against
+    the same launch with equal splits."""
+    import numpy as np
+    from tileinfer_b200.engine.step import split_tables
+    from tileinfer_b200.kernels.library import check, lib
+    torch.manual_seed(21)
+    dtype, nq, nkv, D, splits = torch.bfloat16, 8, 2, 64, 6
+    lengths = [3, 1500, 64, 129, 700]
+    B, g = len(lengths), nq // nkv
+    ks = [rnd(torch.randn(L, nkv, D), dtype) for L in lengths]
+    vs = [rnd(torch.randn(L, nkv, D), dtype) for L in lengths]
+    qs = rnd(torch.randn(B, nq, D), dtype)
+    ks[1][7, 0] = rnd(qs[1, 1] * 4.0, dtype)         # a far key that dominates one head of the long sequence
+    kp, vp, table = paged(ks, vs, 64, sum(-(-L // 64) for L in lengths) + 2, 5, dtype)
+    scale = 1 / math.sqrt(D)
+    want = torch.stack([plain.attention(qs[b:b + 1], ks[b], vs[b], scale, torch.float32, start=lengths[b] - 1)[0] for b in range(B)])
+    work, seq = split_tables(np.asarray(lengths, dtype=np.int64), splits, 64)
+    assert (seq & 255).tolist()[1] > splits > (seq & 255).tolist()[0]
+    st = torch.cuda.current_stream().cuda_stream
+    slots, lens_d = dev(torch.arange(1, B + 1, dtype=torch.int32)), dev(torch.tensor(lengths, dtype=torch.int32))
+    qd = dev(qs, dtype)
+    outs = []
+    for tables in ((dev(torch.from_numpy(work).int().reshape(-1)), dev(torch.from_numpy(seq).int())), (None, None)):
+        out = torch.full((B, nq, D), float("nan"), dtype=dtype, device="cuda")
+        ws_o = torch.full((B * splits, nq, D), float("nan"), device="cuda"); ws_ml = torch.full((B * splits, nq, 2), float("nan"), device="cuda")
+        check(lib().ti_attention_decode_shared(out.data_ptr(), qd.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(), table.stride(0),
+                                               slots.data_ptr(), lens_d.data_ptr(), tables[0].data_ptr() if tables[0] is not None else None,
+                                               tables[1].data_ptr() if tables[1] is not None else None, ws_o.data_ptr(), ws_ml.data_ptr(),
+                                               scale, B, nq, nkv, D, 64, splits, 0, st), "decode")
+        close(out, want, dtype, ulps=5.0)
+        outs.append(out)
+    close(outs[0], outs[1].float(), dtype, ulps=2.0)
+    assert float((want[1, 1] - vs[1][7, 0]).abs().max()) < 0.2
+
+
 @pytest.mark.parametrize("n,out,k,splits", [(17, 100, 72, 1), (37, 301, 120, 1), (130, 384, 512, 1), (300, 256, 4160, 1),
                                              (64, 512, 1024, 4), (2048, 256, 192, 1), (40, 4099, 264, 3),
                                              (1024, 4900, 8200, 1)])      # the last one takes 256-row blocks

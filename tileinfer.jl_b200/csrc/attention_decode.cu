@@ -34,29 +34,43 @@ __device__ __forceinline__ void load_tile(bf16* dst, const bf16* src) {
     }
 }
 
-template <int D>
+template <int D, bool TABLE>
 __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
     bf16* __restrict__ out, const bf16* q, const bf16* k_cache, const bf16* v_cache,
     const int* block_table, int table_stride, const int* seq_slots,
-    const int* kv_lens, float* __restrict__ ws_o, float* __restrict__ ws_ml, float scale_log2e, int nq,
+    const int* kv_lens, const int* work, float* __restrict__ ws_o, float* __restrict__ ws_ml, float scale_log2e, int nq,
     int nkv, int splits, int window) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     typedef DecodeSmem<D> SM;
     constexpr int KS = D / 16, NT = D / 8;
     bf16* tiles = reinterpret_cast<bf16*>(smem_raw);
 
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    // A block is one slot of the launch's B x splits: by default sequence b = slot / splits takes `splits`
+    // equal parts of its keys; with a work table (slot -> sequence << 16 | part << 8 | parts, or -1 for a
+    // slot without work; then the sequence's length) the slots are shared out by the host in proportion to
+    // the sequences' lengths.
+    int b, split, parts, kv_len, slot;
+    const int kvh = blockIdx.y;
+    if (TABLE) {                                             // one load: the slot's work and its sequence's length
+        slot = blockIdx.x;
+        const int2 w = __ldcg(reinterpret_cast<const int2*>(work) + slot);
+        if (w.x < 0) return;
+        b = w.x >> 16; split = (w.x >> 8) & 255; parts = w.x & 255;
+        kv_len = w.y;
+    } else {
+        split = blockIdx.x; b = blockIdx.z; parts = splits; slot = b * splits + split;
+        kv_len = __ldcg(kv_lens + b);
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int group = nq / nkv;
     // The step's lengths and block tables were uploaded before its first kernel, and every page but
     // the sequence's last one holds only older positions: their copies start BEFORE waiting for the
     // kernel that writes this step's key, value and query.
-    const int kv_len = __ldcg(kv_lens + b);
     const int first_key = (window > 0 && kv_len > window) ? kv_len - window : 0;
     const int t_begin = first_key / AD_PAGE, t_end = (kv_len + AD_PAGE - 1) / AD_PAGE;
     const int n_tiles = t_end - t_begin;
-    const int my_lo = t_begin + (int)((long long)n_tiles * split / splits);
-    const int my_hi = t_begin + (int)((long long)n_tiles * (split + 1) / splits);
+    const int my_lo = t_begin + (int)((long long)n_tiles * split / parts);
+    const int my_hi = t_begin + (int)((long long)n_tiles * (split + 1) / parts);
     const int* table = block_table + (size_t)__ldcg(seq_slots + b) * table_stride;
     bool waited = false;
 
@@ -151,7 +165,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
         if (splits == 1) {
             out[((size_t)b * nq + head) * D + d] = __float2bfloat16_rn(O / L);
         } else {
-            const size_t idx = ((size_t)b * nq + head) * splits + split;
+            const size_t idx = (size_t)(slot - split) * nq + (size_t)head * parts + split;   // a head's parts lie together
             ws_o[idx * D + d] = O;
             if (d == 0) { ws_ml[idx * 2] = M; ws_ml[idx * 2 + 1] = L; }
         }
@@ -159,28 +173,39 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
 }
 
 __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws_o,
-                                         const float* ws_ml, int D, int splits) {
+                                         const float* ws_ml, const int* seq_work, int D, int nq, int splits) {
     const size_t row = blockIdx.x;                          // (sequence, head)
-    const float* ml = ws_ml + row * splits * 2;
     __shared__ float sm[AD_MAX_SPLITS], sl[AD_MAX_SPLITS], sw[AD_MAX_SPLITS];
     __shared__ float s_inv;
+    // The parts of this (sequence, head) lie together: `splits` of them from row x splits on, or, with the
+    // host's table (first slot << 8 | parts per sequence), `parts` from first slot x nq + head x parts on.
+    size_t first = row * splits;
+    int parts = splits;
+    if (seq_work != nullptr) {
+        const int b = (int)(row / nq), head = (int)(row % nq);
+        const int w = __ldcg(seq_work + b);
+        parts = w & 255;
+        first = (size_t)(w >> 8) * nq + (size_t)head * parts;
+    }
+    const float* part_o = ws_o + first * D;
+    const float* ml = ws_ml + first * 2;
     pdl_enter();
-    // One round of loads: every thread's partial outputs (for up to 16 splits) are requested together
-    // with the splits' (m, l), before anything is computed.
+    // One round of loads: every thread's partial outputs (for up to 16 parts) are requested together
+    // with the parts' (m, l), before anything is computed.
     const int d0 = threadIdx.x;
-    float first[16];
+    float head_o[16];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) first[u] = (d0 < D && u < splits) ? __ldcg(ws_o + (row * splits + u) * D + d0) : 0.f;
-    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+    for (int u = 0; u < 16; ++u) head_o[u] = (d0 < D && u < parts) ? __ldcg(part_o + (size_t)u * D + d0) : 0.f;
+    for (int s = threadIdx.x; s < parts; s += blockDim.x) {
         sm[s] = __ldcg(ml + 2 * s);
         sl[s] = __ldcg(ml + 2 * s + 1);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
         float M = -INFINITY;
-        for (int s = 0; s < splits; ++s) M = fmaxf(M, sm[s]);
+        for (int s = 0; s < parts; ++s) M = fmaxf(M, sm[s]);
         float L = 0.f;
-        for (int s = 0; s < splits; ++s) {
+        for (int s = 0; s < parts; ++s) {
             sw[s] = exp2f(sm[s] - M);
             L += sl[s] * sw[s];
         }
@@ -192,14 +217,14 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws
         float O = 0.f;
         if (d == d0) {
 #pragma unroll
-            for (int u = 0; u < 16; ++u) O += (u < splits ? sw[u] : 0.f) * first[u];
+            for (int u = 0; u < 16; ++u) O += (u < parts ? sw[u] : 0.f) * head_o[u];
         }
-        for (int s0 = d == d0 ? 16 : 0; s0 < splits; s0 += 8) {
+        for (int s0 = d == d0 ? 16 : 0; s0 < parts; s0 += 8) {
             float v[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = s0 + u < splits ? __ldcg(ws_o + (row * splits + s0 + u) * D + d) : 0.f;
+            for (int u = 0; u < 8; ++u) v[u] = s0 + u < parts ? __ldcg(part_o + (size_t)(s0 + u) * D + d) : 0.f;
 #pragma unroll
-            for (int u = 0; u < 8; ++u) O += (s0 + u < splits ? sw[s0 + u] : 0.f) * v[u];
+            for (int u = 0; u < 8; ++u) O += (s0 + u < parts ? sw[s0 + u] : 0.f) * v[u];
         }
         out[row * D + d] = __float2bfloat16_rn(O * inv);
     }
@@ -207,26 +232,62 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws
 
 template <int D>
 static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v, const int* table, int table_stride,
-                         const int* seq_slots, const int* kv_lens, float* ws_o, float* ws_ml, float scale, int B, int nq,
-                         int nkv, int splits, int window, cudaStream_t stream) {
+                         const int* seq_slots, const int* kv_lens, const int* work, const int* seq_work, float* ws_o, float* ws_ml,
+                         float scale, int B, int nq, int nkv, int splits, int window, cudaStream_t stream) {
     static bool configured = false;
     const size_t smem = DecodeSmem<D>::BYTES > (size_t)AD_WARPS * 16 * (D + 2) * 4 ? DecodeSmem<D>::BYTES
                                                                                     : (size_t)AD_WARPS * 16 * (D + 2) * 4;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return ti_fail("attention_decode: %s", cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(splits, nkv, B);
-    ti_launch(attention_decode_kernel<D>, dim3(grid), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride, seq_slots, kv_lens,
-                                                                  ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv,
-                                                                  splits, window);
+    if (work != nullptr && splits > 1)
+        ti_launch(attention_decode_kernel<D, true>, dim3(B * splits, nkv), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
+                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window);
+    else
+        ti_launch(attention_decode_kernel<D, false>, dim3(splits, nkv, B), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
+                  seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window);
     if (int rc = ti_check_launch("attention_decode")) return rc;
     if (splits > 1) {
-        ti_launch(attention_combine_kernel, dim3(B * nq), dim3(D <= 64 ? 64 : 128), 0, stream, out, ws_o, ws_ml, D, splits);
+        ti_launch(attention_combine_kernel, dim3(B * nq), dim3(D <= 64 ? 64 : 128), 0, stream, out, ws_o, ws_ml, seq_work, D, nq, splits);
         return ti_check_launch("attention_combine");
     }
     return 0;
+}
+
+// Returns 2 (and sets the error text) when the sizes are outside what this kernel takes, so
+// that the caller can fall back to the plain kernel; 1 on a CUDA error.
+// `work` and `seq_work` (both or neither): how the host shares the launch's B x splits slots out among
+// the sequences, so that long sequences get more parts than short ones. work[slot] = (sequence << 16 |
+// part << 8 | parts (at most 32), or -1 for a slot left without work; the sequence's length), 8-byte aligned
+// pairs; seq_work[sequence] = first slot << 8 | parts; a sequence's slots are consecutive. Without them every sequence takes `splits` equal parts.
+extern "C" int ti_attention_decode_shared(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                          const int* block_table, int table_stride, const int* seq_slots, const int* kv_lens,
+                                          const int* work, const int* seq_work, float* ws_o, float* ws_ml, float scale, int B,
+                                          int nq, int nkv, int D, int page_size, int splits, int window, cudaStream_t stream) {
+    if (B == 0) return 0;
+    if (page_size != AD_PAGE || nq % nkv != 0 || nq / nkv > 16 || D % 16 != 0 || B > 32767 || nkv > 65535) {
+        ti_fail("attention_decode takes page size %d, at most 16 query heads per KV head and head sizes in steps of 16; "
+                "got page %d, %d/%d heads, head size %d", AD_PAGE, page_size, nq, nkv, D);
+        return 2;
+    }
+    TI_REQUIRE(splits >= 1 && splits <= AD_MAX_SPLITS, "attention_decode: %d splits (1 to %d)", splits, AD_MAX_SPLITS);
+    TI_REQUIRE(splits == 1 || (ws_o != nullptr && ws_ml != nullptr), "attention_decode: splits need a workspace");
+    TI_REQUIRE((work == nullptr) == (seq_work == nullptr), "attention_decode: give both work tables or neither");
+    if (splits == 1) work = seq_work = nullptr;
+#define AD_CASE(d)                                                                                                     \
+    case d:                                                                                                            \
+        return launch_decode<d>((bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,     \
+                                table_stride, seq_slots, kv_lens, work, seq_work, ws_o, ws_ml, scale, B, nq, nkv, splits, window, stream);
+    switch (D) {
+        AD_CASE(16) AD_CASE(32) AD_CASE(48) AD_CASE(64) AD_CASE(80) AD_CASE(96) AD_CASE(112) AD_CASE(128) AD_CASE(256)
+        default:
+            ti_fail("attention_decode has no instance for head size %d", D);
+            return 2;
+    }
+#undef AD_CASE
 }
 
 // Returns 2 (and sets the error text) when the sizes are outside what this kernel takes, so
@@ -235,25 +296,8 @@ extern "C" int ti_attention_decode(void* out, const void* q, const void* k_cache
                                    const int* block_table, int table_stride, const int* seq_slots, const int* kv_lens,
                                    float* ws_o, float* ws_ml, float scale, int B, int nq, int nkv, int D, int page_size,
                                    int splits, int window, cudaStream_t stream) {
-    if (B == 0) return 0;
-    if (page_size != AD_PAGE || nq % nkv != 0 || nq / nkv > 16 || D % 16 != 0 || B > 65535 || nkv > 65535) {
-        ti_fail("attention_decode takes page size %d, at most 16 query heads per KV head and head sizes in steps of 16; "
-                "got page %d, %d/%d heads, head size %d", AD_PAGE, page_size, nq, nkv, D);
-        return 2;
-    }
-    TI_REQUIRE(splits >= 1 && splits <= AD_MAX_SPLITS, "attention_decode: %d splits (1 to %d)", splits, AD_MAX_SPLITS);
-    TI_REQUIRE(splits == 1 || (ws_o != nullptr && ws_ml != nullptr), "attention_decode: splits need a workspace");
-#define AD_CASE(d)                                                                                                     \
-    case d:                                                                                                            \
-        return launch_decode<d>((bf16*)out, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,     \
-                                table_stride, seq_slots, kv_lens, ws_o, ws_ml, scale, B, nq, nkv, splits, window, stream);
-    switch (D) {
-        AD_CASE(16) AD_CASE(32) AD_CASE(48) AD_CASE(64) AD_CASE(80) AD_CASE(96) AD_CASE(112) AD_CASE(128) AD_CASE(256)
-        default:
-            ti_fail("attention_decode has no instance for head size %d", D);
-            return 2;
-    }
-#undef AD_CASE
+    return ti_attention_decode_shared(out, q, k_cache, v_cache, block_table, table_stride, seq_slots, kv_lens, nullptr, nullptr, ws_o,
+                                      ws_ml, scale, B, nq, nkv, D, page_size, splits, window, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -58,6 +58,10 @@ class Engine:
         self.max_step_tokens = int(max_step_tokens)
         self.planner = StepPlanner(self.cache, self.max_step_tokens, self.device)
         self.planner.runtime = self.rt
+        if self.rt.fast and self.rt.dtype == torch.bfloat16:
+            from ..kernels import fast
+            self.planner.split_policy = lambda batch, group: fast.decode_splits(batch, group.request.kv_heads,
+                                                                              group.num_pages * group.page_size)
         self.use_graphs = graphs
         self._graphs: Dict[int, object] = {}
         self._logits: Dict[int, torch.Tensor] = {}

@@ -24,6 +24,35 @@ def _align(n: int, a: int = 32) -> int:
 class GroupMeta:
     slot_mapping: torch.Tensor          # [n_tokens] flat position in the pool: page * page_size + offset
     block_table: torch.Tensor           # [max_seqs, max_pages] pages of every slot
+    # Decode steps only, when the planner has a split policy: how the attention kernel's B x splits work
+    # slots are shared out among the sequences (see ``split_tables``).
+    decode_splits: int = 0
+    split_work: Optional[torch.Tensor] = None     # [B * splits, 2]
+    split_seq: Optional[torch.Tensor] = None      # [B]
+
+
+MAX_PARTS = 32                          # parts of one sequence in decode attention (the combine kernel's limit)
+
+
+def split_tables(lengths: np.ndarray, splits: int, page_size: int):
+    """Shares B x splits work slots out among B sequences of ``lengths`` keys: every sequence gets one
+    part, the remaining slots go in proportion to the sequences' pages, so that a long sequence is read by
+    more blocks than a short one (with equal lengths every sequence gets ``splits`` parts). A sequence's
+    slots are consecutive. Returns work[slot] = (sequence << 16 | part << 8 | parts, or -1: no work; the
+    sequence's length) and seq[sequence] = first slot << 8 | parts."""
+    B = len(lengths)
+    T = B * splits
+    pages = np.maximum(-(-lengths.astype(np.int64) // page_size), 1)
+    parts = 1 + ((T - B) * pages) // int(pages.sum())
+    parts = np.minimum(np.minimum(parts, MAX_PARTS), pages)
+    first = np.cumsum(parts) - parts
+    used = int(parts.sum())
+    work = np.zeros((T, 2), dtype=np.int64)
+    work[:, 0] = -1
+    owner = np.repeat(np.arange(B, dtype=np.int64), parts)
+    work[:used, 0] = (owner << 16) | ((np.arange(used, dtype=np.int64) - first[owner]) << 8) | parts[owner]
+    work[:used, 1] = lengths[owner]
+    return work, (first << 8) | parts
 
 
 @dataclass
@@ -64,7 +93,8 @@ class StepPlanner:
         self.device = torch.device(device)
         self.max_step_tokens = max_step_tokens
         n_groups = max(1, len(cache.paged_groups))
-        cap = _align(max_step_tokens) * (3 + n_groups + 1) + 4 * _align(cache.max_seqs + 1) + 64
+        cap = (_align(max_step_tokens) * (3 + n_groups + 1) + 4 * _align(cache.max_seqs + 1) + 64 +
+               n_groups * (_align(2 * cache.max_seqs * MAX_PARTS) + _align(cache.max_seqs)))
         self.capacity = cap
         pin = self.device.type == "cuda"
         self.staging = [torch.zeros(cap, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
@@ -73,6 +103,10 @@ class StepPlanner:
         self.turn = 0
         self.meta = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self.runtime = None
+        # (batch size, paged group) -> split count of decode attention, or None: who builds the engine decides
+        # (the fast kernels split, the plain ones do not).
+        self.split_policy = None
+        self._split_cache = {}
         self.last_upload_bytes = 0
         self._layouts = {}
         self._tables_np = [g.host_table.numpy() for g in cache.paged_groups]
@@ -92,18 +126,48 @@ class StepPlanner:
         o = {"ids": seg(n), "pos": seg(n), "slot": seg(n)}
         o["maps"] = [seg(n) for _ in self.cache.paged_groups]
         o["seq"], o["cu"], o["kv"], o["want"] = seg(B), seg(B + 1), seg(B), seg(nw)
+        o["splits"] = [0 for _ in self.cache.paged_groups]
+        if n == B and self.split_policy is not None:         # a decode step
+            o["splits"] = [int(self.split_policy(B, g) or 0) for g in self.cache.paged_groups]
+            o["work"] = [seg(2 * B * sp) if sp > 1 else 0 for sp in o["splits"]]
+            o["seqw"] = [seg(B) if sp > 1 else 0 for sp in o["splits"]]
         o["end"] = off
         m = self.meta
         views = dict(
             token_ids=m[o["ids"]:o["ids"] + n], positions=m[o["pos"]:o["pos"] + n], tok_slot=m[o["slot"]:o["slot"] + n],
             seq_slots=m[o["seq"]:o["seq"] + B], cu_seqlens=m[o["cu"]:o["cu"] + B + 1], kv_lens=m[o["kv"]:o["kv"] + B],
             want_idx=m[o["want"]:o["want"] + nw],
-            groups={g.index: GroupMeta(m[o["maps"][gi]:o["maps"][gi] + n], g.device_table)
+            groups={g.index: GroupMeta(m[o["maps"][gi]:o["maps"][gi] + n], g.device_table,
+                                       **({"decode_splits": o["splits"][gi],
+                                           "split_work": m[o["work"][gi]:o["work"][gi] + 2 * B * o["splits"][gi]],
+                                           "split_seq": m[o["seqw"][gi]:o["seqw"][gi] + B]} if o["splits"][gi] > 1 else
+                                          {"decode_splits": o["splits"][gi]}))
                     for gi, g in enumerate(self.cache.paged_groups)})
         if len(self._layouts) > 256:
             self._layouts.clear()
         lay = self._layouts[key] = (o, views)
         return lay
+
+    def _fill_splits(self, o, st, lengths_after: np.ndarray):
+        """The decode attention's work tables for sequences that hold ``lengths_after`` keys after the step;
+        they change only when a sequence starts a new page, and are kept until then."""
+        for gi, g in enumerate(self.cache.paged_groups):
+            sp = o["splits"][gi]
+            if sp <= 1:
+                continue
+            B = len(lengths_after)
+            pages = -(-lengths_after // g.page_size)
+            key = (gi, B)
+            held = self._split_cache.get(key)
+            if held is None or not np.array_equal(held[0], pages):
+                work, seqw = split_tables(lengths_after, sp, g.page_size)
+                used = int((seqw & 255).sum())
+                held = (pages.copy(), work, seqw, (work[:used, 0] >> 16).copy(), used)
+                self._split_cache[key] = held
+            work, used = held[1], held[4]
+            work[:used, 1] = lengths_after[held[3]]                        # the lengths change every step
+            st[o["work"][gi]:o["work"][gi] + 2 * B * sp] = work.reshape(-1)
+            st[o["seqw"][gi]:o["seqw"][gi] + B] = held[2]
 
     def _staging(self):
         turn = self.turn
@@ -156,6 +220,8 @@ class StepPlanner:
         st[o["cu"] + B] = row
         st[o["seq"]:o["seq"] + B] = slots
         st[o["kv"]:o["kv"] + B] = [a + b for a, b in zip(starts, q_lens)]
+        if n == B and any(o["splits"]):
+            self._fill_splits(o, st, np.asarray(starts, dtype=np.int64) + 1)
         self._upload(turn, o["end"])
         return StepContext(n_tokens=n, n_seqs=B, n_want=nw, host_slots=slots, host_q_lens=q_lens, host_starts=starts,
                            is_decode=all(q == 1 for q in q_lens), max_q_len=max(q_lens, default=0),
@@ -183,6 +249,8 @@ class StepPlanner:
         st[o["seq"]:o["seq"] + B] = slot_arr
         st[o["kv"]:o["kv"] + B] = starts + 1
         st[o["want"]:o["want"] + B] = ar[:B]
+        if any(o["splits"]):
+            self._fill_splits(o, st, starts + 1)
         self._upload(turn, o["end"], skip_ids=_align(B) if tokens is None else 0)
         starts_l = starts.tolist()
         return StepContext(n_tokens=B, n_seqs=B, n_want=B, host_slots=list(slots), host_q_lens=[1] * B, host_starts=starts_l,

@@ -110,15 +110,19 @@ def attention(out, q, cache, meta, step, spec) -> bool:
         return False
     if step.is_decode:
         B = step.n_seqs
-        splits = decode_splits(B, spec.num_kv_heads, cache.k.shape[0] * 64)
+        # The step's plan may carry the split count and how the work slots are shared out among the sequences.
+        splits = meta.decode_splits or decode_splits(B, spec.num_kv_heads, cache.k.shape[0] * 64)
+        shared = meta.split_work is not None and splits > 1
         rt_buffer = step.runtime.buffer
-        ws_o = rt_buffer("attention.ws_o", (B, spec.num_heads, splits, spec.head_dim), torch.float32)
-        ws_ml = rt_buffer("attention.ws_ml", (B, spec.num_heads, splits, 2), torch.float32)
-        rc = lib().ti_attention_decode(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
-                                       meta.block_table.data_ptr(), meta.block_table.stride(0),
-                                       step.seq_slots.data_ptr(), step.kv_lens.data_ptr(), ws_o.data_ptr(),
-                                       ws_ml.data_ptr(), spec.scale, B, spec.num_heads, spec.num_kv_heads,
-                                       spec.head_dim, cache.page_size, splits, spec.window or 0, _stream())
+        ws_o = rt_buffer("attention.ws_o", (B * splits, spec.num_heads, spec.head_dim), torch.float32)
+        ws_ml = rt_buffer("attention.ws_ml", (B * splits, spec.num_heads, 2), torch.float32)
+        rc = lib().ti_attention_decode_shared(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                                              meta.block_table.data_ptr(), meta.block_table.stride(0),
+                                              step.seq_slots.data_ptr(), step.kv_lens.data_ptr(),
+                                              meta.split_work.data_ptr() if shared else None,
+                                              meta.split_seq.data_ptr() if shared else None, ws_o.data_ptr(),
+                                              ws_ml.data_ptr(), spec.scale, B, spec.num_heads, spec.num_kv_heads,
+                                              spec.head_dim, cache.page_size, splits, spec.window or 0, _stream())
         if rc == 2:
             return False
         check(rc, "attention_decode")

@@ -117,6 +117,7 @@ _SIGNATURES_FAST = {
     "ti_gemm_tcgen05": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
     "ti_attention_prefill": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _F, _I, _I, _I, _I, _I, _P],
     "ti_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ti_attention_decode_shared": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_attention_prefill_tc": [_P, _P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _F, _I, _I, _I, _I, _I, _P, _P],
 }
 _SIGNATURES.update(_SIGNATURES_FAST)
