@@ -70,10 +70,15 @@ def check_status() -> None:
 
 
 def tc_splits(out_features: int, in_features: int, n: int) -> int:
+    """How many slices of k the tensor-core product of a decode batch is cut into when its consumer can
+    add partial sums: as many as fill the device's block slots (two per SM for token tiles of up to 64), at
+    most 8, each at least 512 of k. Measured at 64 tokens: down projection 46 us in 3 slices, 35 us in 8;
+    o 17 us in 2, 11 us in 8."""
     tiles = -(-out_features // 128) * -(-n // (256 if n > 128 else 128 if n > 64 else 64 if n > 32 else 32))
-    if n > 256 or tiles >= SM_COUNT:
+    slots = SM_COUNT * (2 if n <= 64 else 1)
+    if n > 256 or tiles >= slots:
         return 1
-    return max(1, min(8, SM_COUNT // tiles, (in_features // 64) // 8))
+    return max(1, min(8, slots // tiles, (in_features // 64) // 8))
 
 
 def _tcgen05(lin, x, out, epilogue, act, allow_partials):
