@@ -105,6 +105,11 @@ class DecoderModel:
 
     def forward(self, step, cache, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the step's tokens; write the logits of ``step.want_idx`` rows to ``logits``."""
+        from ..kernels.library import stream_scope
+        with stream_scope():
+            return self._forward(step, cache, logits)
+
+    def _forward(self, step, cache, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         rt, spec = self.rt, self.spec
         n = step.n_tokens
         x = rt.buffer("model.x", (n, spec.hidden_size))

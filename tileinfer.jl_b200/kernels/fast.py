@@ -5,6 +5,8 @@ from __future__ import annotations
 
 import torch
 
+from . import library as _library
+
 from . import ops
 from .library import KernelError, add_launches, check, lib
 
@@ -13,7 +15,7 @@ SM_COUNT = 148
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _library.current_stream()
 
 
 def gemv_splits(out_features: int, in_features: int) -> int:

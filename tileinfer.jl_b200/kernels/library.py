@@ -14,6 +14,7 @@ _lib = None
 # Number of kernels launched through this module so far (a launch inside a CUDA-graph capture counts
 # once; its replays are counted by whoever replays the graph).
 launch_count = 0
+pinned_stream = None          # the stream handle for the launches of a forward pass (see ``stream_scope``)
 call_counts = {}              # entry point -> calls that launched (tests read which kernels a step used)
 
 
@@ -32,6 +33,31 @@ class _Counted:
             launch_count += self.kernels
             call_counts[self.name] = call_counts.get(self.name, 0) + 1
         return rc
+
+
+def current_stream() -> int:
+    """The CUDA stream the next launch goes to: the one pinned for the running forward pass, else torch's
+    current stream (looking that up costs more than a launch, so a pass looks it up once)."""
+    if pinned_stream is not None:
+        return pinned_stream
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+class stream_scope:
+    """Pins torch's current stream for the launches made inside (a forward pass makes hundreds)."""
+
+    def __enter__(self):
+        global pinned_stream
+        import torch
+        self.before = pinned_stream
+        pinned_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global pinned_stream
+        pinned_stream = self.before
+        return False
 
 
 def add_launches(n: int) -> None:

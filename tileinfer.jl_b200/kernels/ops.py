@@ -10,6 +10,8 @@ from typing import Optional
 
 import torch
 
+from . import library as _library
+
 from .library import KernelError, check, lib
 
 F32, BF16 = 0, 1
@@ -25,7 +27,7 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    return _library.current_stream()
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:

@@ -22,6 +22,7 @@ class Runtime:
         # "plain": only the simple CUDA-core kernels, also in bfloat16. The 32-bit path always uses them.
         self.kernels = "plain" if dtype == torch.float32 else kernels
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}     # (name, shape, dtype) -> the view handed out last time
         # Counts (re)allocations of scratch buffers: a captured CUDA graph holds the addresses of the
         # buffers it was captured with and must be dropped when this number changes.
         self.generation = 0
@@ -32,6 +33,10 @@ class Runtime:
 
     def buffer(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype = None) -> torch.Tensor:
         dtype = dtype or self.dtype
+        key = (name, shape, dtype)
+        view = self._views.get(key)
+        if view is not None:                        # the same request as before: the same view (making one costs microseconds)
+            return view
         count = 1
         for s in shape:
             count *= int(s)
@@ -42,7 +47,12 @@ class Runtime:
             buf = torch.empty(max(count, 1), dtype=dtype, device=self.device)
             self._buffers[name] = buf
             self.generation += 1
-        return buf[:count].view(*shape)
+            for k in [k for k in self._views if k[0] == name]:
+                del self._views[k]
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = self._views[key] = buf[:count].view(*shape)
+        return view
 
     def param(self, t: torch.Tensor, keep_dtype: bool = False) -> torch.Tensor:
         """A checkpoint tensor on the device, in the element type the kernels compute with."""
