@@ -137,14 +137,16 @@ def xielu(x: torch.Tensor, a, dtype: torch.dtype) -> torch.Tensor:
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, dtype: torch.dtype,
-              start: int = 0) -> torch.Tensor:
+              start: int = 0, window: int = 0) -> torch.Tensor:
     """Causal grouped-query attention over whole sequences.
 
     q [n, nq, D] are the queries at positions start..start+n-1; k, v [start+n, nkv, D] are all
     keys/values. Query head h reads KV head h div g (src/ops/reference.jl:108-112); key i is
     visible to the query at position p iff i <= p (reference.jl:98-107). Scores and softmax
     stay in 32-bit; P is rounded only for the PV product, the sum is 32-bit, O is rounded
-    (the kernels' convention, src/ops/tile/attention.jl:1-3, 34-59)."""
+    (the kernels' convention, src/ops/tile/attention.jl:1-3, 34-59). ``window`` > 0 lets a query
+    see only its last ``window`` keys, itself included; the reference refuses such models
+    (src/config.jl:60-62), the library's cache groups with a window are tested with it."""
     n, nq, D = q.shape
     total, nkv, _ = k.shape
     g = nq // nkv
@@ -154,12 +156,14 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, d
     qpos = torch.arange(start, start + n)[:, None]
     kpos = torch.arange(total)[None, :]
     s = s.masked_fill((kpos > qpos)[None], float("-inf"))
+    if window:
+        s = s.masked_fill((kpos <= qpos - window)[None], float("-inf"))
     e = torch.exp(s - s.max(-1, keepdim=True).values)
     o = torch.einsum("hqk,khd->qhd", rnd(e, dtype), vv) / e.sum(-1).t()[:, :, None]
     return rnd(o, dtype)
 
 
-def attention_block(h, W, p, cfg, positions, dtype):
+def attention_block(h, W, p, cfg, positions, dtype, window: int = 0):
     """q/k/v projections, per-head q/k RMSNorm before RoPE, attention, output projection
     (src/model/decoder.jl:176-180; src/ops/interface.jl:161-177)."""
     n = h.shape[0]
@@ -172,7 +176,7 @@ def attention_block(h, W, p, cfg, positions, dtype):
         k = rmsnorm(k, rnd(W[p + "self_attn.k_norm.weight"], dtype), cfg.eps, dtype)
     cos, sin = rope_tables(cfg, positions, dtype)
     q, k = rope(q, cos, sin, dtype), rope(k, cos, sin, dtype)
-    o = attention(q, k, v, 1.0 / math.sqrt(D), dtype)          # scale fixed in code: decoder.jl:169
+    o = attention(q, k, v, 1.0 / math.sqrt(D), dtype, window=window)          # scale fixed in code: decoder.jl:169
     return linear(o.reshape(n, cfg.heads * D), W[p + "self_attn.o_proj.weight"], dtype)
 
 
@@ -183,15 +187,18 @@ def feed_forward(h, W, p, dtype):
     return linear(xielu(linear(h, W[p + "mlp.up_proj.weight"], dtype), a, dtype), W[p + "mlp.down_proj.weight"], dtype)
 
 
-def forward(cfg, W: Dict[str, torch.Tensor], ids: Sequence[int], dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """Logits [n, vocab] (32-bit) of one whole sequence (src/model/decoder.jl:165-196)."""
+def forward(cfg, W: Dict[str, torch.Tensor], ids: Sequence[int], dtype: torch.dtype = torch.float32,
+            windows: Sequence[int] = ()) -> torch.Tensor:
+    """Logits [n, vocab] (32-bit) of one whole sequence (src/model/decoder.jl:165-196). ``windows``:
+    an attention window for each layer (0: none), see :func:`attention`."""
     W = {k: (rnd(v, dtype) if v.dim() >= 1 and v.numel() > 1 else v) for k, v in W.items()}
     positions = torch.arange(len(ids))
     x = embed(W["model.embed_tokens.weight"][: cfg.vocab], ids)
     for l in range(cfg.layers):
         p = f"model.layers.{l}."
         h = rmsnorm(x, W[p + "attention_layernorm.weight"], cfg.eps, dtype)
-        x = rnd(x + attention_block(h, W, p, cfg, positions, dtype), dtype)      # src/ops/tile/norm.jl:53-55
+        window = windows[l] if windows else 0
+        x = rnd(x + attention_block(h, W, p, cfg, positions, dtype, window), dtype)      # src/ops/tile/norm.jl:53-55
         h = rmsnorm(x, W[p + "feedforward_layernorm.weight"], cfg.eps, dtype)
         x = rnd(x + feed_forward(h, W, p, dtype), dtype)
     h = rmsnorm(x, W["model.norm.weight"], cfg.eps, dtype)

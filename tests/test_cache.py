@@ -129,3 +129,101 @@ def test_random_traffic_keeps_the_books_straight():
         assert g.pages.held + g.pages.free == g.num_pages            # none lost
         assert all(len(g.tables.get(s, [])) == -(-n // 4) for s, n in live.items())
         assert c.slots.held == len(live)
+
+
+def test_a_windowed_group_gives_pages_back_as_they_fall_out_of_the_window():
+    """Window 10, pages of 4, release unit 2 pages: after L positions the next query sees keys from
+    L - 9 on, so pages before floor((L - 9) / 4) rounded down to an even index are free again."""
+    c = Cache([kv(), kv(window=10)], torch.float32, "cpu", max_tokens=64, max_seqs=2, page_size=4, release_granule=2)
+    full, win = c.paged_groups
+    s = c.alloc_slot()
+    c.reserve([(s, 13)]); c.advance(s, 13)
+    assert win.tables[s] == [0, 1, 2, 3] and win.first.get(s, 0) == 0          # key 4 is still seen: page 1, unit 0
+    c.reserve([(s, 4)]); c.advance(s, 4)                                      # L = 17: first key 8, page 2
+    assert win.tables[s] == [None, None, 2, 3, 4] and win.first[s] == 2 and win.pages.held == 3
+    assert win.pages.take() == 0                                              # page 0 is free again
+    win.pages.give(0)
+    assert full.tables[s] == [0, 1, 2, 3, 4]                                  # the other group keeps everything
+    for _ in range(30):
+        c.reserve([(s, 1)]); c.advance(s, 1)
+        held = [p for p in win.tables[s] if p is not None]
+        assert len(held) == win.pages.held <= 5 and len(set(held)) == len(held)
+        assert win.first[s] == (c.length(s) - 9) // 4 // 2 * 2
+        # every key that the next query sees lies on a held page
+        assert all(win.tables[s][k // 4] is not None for k in range(c.length(s) - 9, c.length(s)))
+    with pytest.raises(ValueError, match="roll back"):
+        c.truncate(s, c.length(s) - 8)
+    c.truncate(s, c.length(s) - 1)                                            # within the held pages: fine
+    c.free_slot(s)
+    assert win.pages.held == 0 and full.pages.held == 0 and win.first == {} and win.tables == {}
+
+
+def test_a_windowed_pool_is_sized_for_windows_and_one_step_and_long_steps_run_in_chunks():
+    c = Cache([kv(window=10)], torch.float32, "cpu", max_tokens=400, max_seqs=2, page_size=4, max_step_tokens=16,
+              release_granule=2)
+    (win,) = c.paged_groups
+    assert win.num_pages == 2 * (3 + 2 + 1) + 4 < c.num_pages
+    a, b = c.alloc_slot(), c.alloc_slot()
+    growth = [(a, 150), (b, 90)]
+    with pytest.raises(OutOfPagesError):
+        c.reserve(growth)                                                     # whole, it does not fit
+    assert win.pages.held == 0
+    c.reserve(growth, chunk_tokens=16)                                        # chunk by chunk it does
+    assert win.pages.held == 0
+    # run the chunks as the engine does: tokens in order, 16 at a time
+    peak, room, chunk = 0, 16, []
+    def run(chunk):
+        nonlocal peak
+        c.prepare(chunk)
+        peak = max(peak, win.pages.held)
+        for s, n in chunk:
+            c.advance(s, n)
+    for s, n in growth:
+        done = 0
+        while done < n:
+            take = min(room, n - done)
+            chunk.append((s, take)); done += take; room -= take
+            if room == 0:
+                run(chunk); chunk, room = [], 16
+    if chunk:
+        run(chunk)
+    assert c.length(a) == 150 and c.length(b) == 90 and peak <= win.num_pages
+    # decoding on from there stays within the pool for ever
+    for _ in range(100):
+        c.reserve([(a, 1), (b, 1)]); c.advance(a, 1); c.advance(b, 1)
+    assert win.pages.held <= 2 * 5
+    c.free_slot(a); c.free_slot(b)
+    assert win.pages.held == 0 and win.pages.free == win.num_pages
+
+
+def test_the_peak_of_a_chunked_step_is_what_running_it_takes():
+    rng = random.Random(1)
+    for _ in range(50):
+        window, chunk = rng.randint(1, 40), rng.randint(1, 50)
+        c = Cache([kv(window=window)], torch.float32, "cpu", max_tokens=4000, max_seqs=3, page_size=4, release_granule=2)
+        (win,) = c.paged_groups
+        slots = [c.alloc_slot() for _ in range(3)]
+        for s in slots:                                                       # some history first
+            n = rng.randint(0, 60)
+            if n:
+                c.reserve([(s, n)]); c.advance(s, n)
+        growth = [(s, rng.randint(1, 120)) for s in slots]
+        before = win.pages.held
+        predicted = win.peak_pages(growth, c.lengths, chunk)
+        c.reserve(growth, chunk_tokens=chunk)
+        peak, room, cur = before, chunk, []
+        for s, n in growth:
+            done = 0
+            while done < n:
+                take = min(room, n - done)
+                cur.append((s, take)); done += take; room -= take
+                if room == 0:
+                    c.prepare(cur); peak = max(peak, win.pages.held)
+                    for x, m in cur:
+                        c.advance(x, m)
+                    cur, room = [], chunk
+        if cur:
+            c.prepare(cur); peak = max(peak, win.pages.held)
+            for x, m in cur:
+                c.advance(x, m)
+        assert peak - before == predicted

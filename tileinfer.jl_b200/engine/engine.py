@@ -54,7 +54,7 @@ class Engine:
         self.model = factory(self.spec, tensors, self.rt, max_context)
         self.cache = Cache(self.model.cache_requests(), self.dtype, self.device, max_tokens=max_tokens,
                            max_seqs=max_seqs, page_size=page_size, max_seq_len=max_context,
-                           share=self.model.cache_shares())
+                           share=self.model.cache_shares(), max_step_tokens=int(max_step_tokens))
         self.max_step_tokens = int(max_step_tokens)
         self.planner = StepPlanner(self.cache, self.max_step_tokens, self.device)
         self.planner.runtime = self.rt
@@ -124,7 +124,7 @@ class Engine:
                 raise ValueError(f"sequence would reach {self.cache.length(slot) + len(toks)} positions; "
                                  f"max context is {self.max_context}")
         # All pages first: a step that cannot be held changes nothing.
-        self.cache.reserve([(s, len(t)) for s, t in entries])
+        self.cache.reserve([(s, len(t)) for s, t in entries], chunk_tokens=self.max_step_tokens)
         n_want = sum(len(w) for w in want)
         n_total = sum(len(t) for _, t in entries)
         decode = all(len(t) == 1 for _, t in entries) and all(w == [0] for w in want)
@@ -140,6 +140,7 @@ class Engine:
         row = 0
         for chunk_entries, chunk_want in self._chunks(entries, want):
             nw = sum(len(w) for w in chunk_want)
+            self.cache.prepare([(s, len(t)) for s, t in chunk_entries])
             ctx = self.planner.plan(chunk_entries, chunk_want)
             self.model.forward(ctx, self.cache, logits[row:row + nw] if nw else None)
             for s, t in chunk_entries:
@@ -210,7 +211,7 @@ class Engine:
             else:
                 graph.replay()
         for s in slots:
-            self.cache.lengths[s] += 1
+            self.cache.advance(s, 1)
         return logits
 
     def decode_launches(self, batch: int) -> int:
