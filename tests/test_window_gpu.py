@@ -41,9 +41,10 @@ def windowed_architecture():
     return WindowedConfig
 
 
-def poison_free_pages(engine, value=3.0e4):
+def poison_free_pages(engine, value=float("nan")):
     """Whatever no sequence holds is overwritten: a kernel that still reads a page which was given back
-    (or one that was never taken) shows at once. Finite, since masked keys take part with weight 0."""
+    (or one that was never taken) shows at once, and so does a page whose last user's values reach the
+    next one."""
     for g in engine.cache.paged_groups:
         free = torch.tensor(sorted(g.pages._free), dtype=torch.long, device=g.k.device)
         if len(free):

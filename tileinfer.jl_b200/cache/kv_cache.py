@@ -82,6 +82,10 @@ class PagedGroup:
         table.extend(new)
         self.host_table[slot, a:a + need] = torch.tensor(new, dtype=torch.int32)
         self.device_table[slot, a:a + need].copy_(self.host_table[slot, a:a + need], non_blocking=True)
+        # A page's last user may have left anything in it. Keys beyond a sequence's length are masked by
+        # selection, but their values take part in P V with weight 0, and 0 times a stale infinity or NaN
+        # is NaN: values are zeroed when a page is taken.
+        self.v.index_fill_(1, self.device_table[slot, a:a + need].long(), 0)
 
     def first_needed_page(self, length: int) -> int:
         """Logical index of the first page that a query at position ``length`` or later can read."""
