@@ -269,3 +269,55 @@ def test_one_layer_at_apertus_8b_sizes(dtype):
         want = torch.stack([refs[0][0], refs[0][149], refs[1][36]])
         assert float((got - want).abs().max()) <= tol
         eng.check_health()
+
+
+def _odd(**kw):
+    c = {k: v for k, v in helpers.TINY_A.items() if k != "eos_token_id"}
+    c.update(kw)
+    return c
+
+
+ODD_SIZES = {
+    "width 100 (a multiple of 4 only)": _odd(hidden_size=100, num_attention_heads=3, num_key_value_heads=1, head_dim=32,
+                                           intermediate_size=172, vocab_size=333),
+    "odd width, feed-forward and vocabulary": _odd(hidden_size=77, num_attention_heads=2, num_key_value_heads=2, head_dim=16,
+                                                   intermediate_size=203, vocab_size=99),
+    "head 80": _odd(hidden_size=160, num_attention_heads=4, num_key_value_heads=2, head_dim=80),
+    "head 96, 3 per group": _odd(hidden_size=192, num_attention_heads=6, num_key_value_heads=2, head_dim=96),
+    "head 112, 7 per group": _odd(hidden_size=128, num_attention_heads=7, num_key_value_heads=1, head_dim=112),
+    "head 24 (no multiple of 16)": _odd(hidden_size=96, num_attention_heads=4, num_key_value_heads=2, head_dim=24),
+    "head 256": _odd(hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=256),
+    "head 512": _odd(hidden_size=512, num_attention_heads=2, num_key_value_heads=1, head_dim=512),
+    "32 per group": _odd(hidden_size=256, num_attention_heads=32, num_key_value_heads=1, head_dim=64),
+    "40 heads in 8 groups of head 128": _odd(hidden_size=256, num_attention_heads=40, num_key_value_heads=8, head_dim=128),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("case", sorted(ODD_SIZES))
+def test_every_size_is_taken_or_handed_to_a_kernel_that_takes_it(case, dtype):
+    """Sizes outside what the tensor-core and vector kernels take (widths that are no multiple of 8, head
+    sizes that are no multiple of 16 or above 256, groups that are no power of two) run through the
+    general kernels instead: a prompt of two unequal sequences, then 8 tokens one by one."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.weights import write_model_folder
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    with tempfile.TemporaryDirectory() as d:
+        folder = write_model_folder(ApertusConfig.from_dict(ODD_SIZES[case]), 1, os.path.join(d, "m"))
+        cfg, W = plain.load_folder(folder)
+        prompts = helpers.random_prompts(cfg.vocab, [150, 37], 3)
+        refs = [plain.forward(cfg, W, p, tdt) for p in prompts]
+        eng = ti.load_model(folder, dtype=dtype, max_context=256, max_seqs=2)
+        slots = [eng.new_sequence() for _ in prompts]
+        head = [len(p) - 8 for p in prompts]
+        out = eng.step([(s, p[:h]) for s, p, h in zip(slots, prompts, head)], [list(range(h)) for h in head]).cpu()
+        row = 0
+        for ref, h in zip(refs, head):
+            assert float((out[row:row + h] - ref[:h]).abs().max()) <= tolerance(dtype, ref)
+            row += h
+        for t in range(8):
+            out = eng.step([(s, [p[h + t]]) for s, p, h in zip(slots, prompts, head)]).cpu()
+            for i, (ref, h) in enumerate(zip(refs, head)):
+                assert float((out[i] - ref[h + t]).abs().max()) <= tolerance(dtype, ref), (t, i)
+        eng.check_health()
