@@ -4,8 +4,9 @@
 //
 // A block serves one KV head of one sequence and TWO query tiles of 128 rows each (a row is a
 // (token, query head of the group) pair, so the heads of a group share the K and V they read). Warps 0-3
-// are the softmax of tile 0, warps 4-7 of tile 1, warp 8 loads (TMA), warp 9 issues the MMAs. While the
-// softmax of one tile runs, the tensor core works on the other tile. Per step of 128 keys:
+// are the softmax of tile 0, warps 4-7 of tile 1; one thread of warp 8 loads (TMA), one thread of warp 9
+// issues the MMAs of both tiles in turn (a tile's two products back to back: issued from two threads
+// they would share the tensor core and both finish late). While the softmax of one tile runs, the tensor core works on the other tile. Per step of 128 keys:
 //   S_x = Q_x Kᵀ              (SS MMA, both operands K-major in 128-byte-swizzled shared memory)
 //   softmax: row maximum, p = 2^(s·c − m) in 32-bit, row sum; P rounded to bfloat16 and written over
 //            S in tensor memory
@@ -57,6 +58,25 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Two 32-bit floats in one 64-bit register, for the packed FMA-pipe instructions of sm_100 (one issue
+// slot for two lanes of work).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
 template <int D>
 __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                           const __grid_constant__ CUtensorMap map_k,
@@ -114,49 +134,48 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     const unsigned tmem_base = *tmem_slot;
 
     if (warp == 8) {
-        // ---------------------------------------------------------------- loads (lane 0 issues)
+        // ---------------------------------------------------------------- loads (one thread)
         if (lane == 0) {
             mbar_expect_tx(q_full, 2 * C::Q_TILE_BYTES);
             for (int x = 0; x < 2; ++x)
                 for (int h = 0; h < C::HALVES; ++h)
                     tma_load_3d(smem_addr(q_tiles + x * C::Q_TILE_BYTES + h * C::HALF_BYTES), &map_q, h * 64, kvh * p.group,
                                 tok_begin + t0 + x * tokens_per_tile, q_full);
-        }
-        __syncwarp();
-        bool ok = true;
-        int fill = 0;                                           // K_j is fill 2(j - j_lo), V_j the next one
-        for (int j = j_lo; ok && j < j_hi; ++j) {
-            for (int kv = 0; kv < 2; ++kv, ++fill) {
-                const int buf = fill % RING;
-                const unsigned phase = (unsigned)(fill / RING) & 1u;
-                ok = __all_sync(0xffffffffu, mbar_wait(kv_empty0 + 8 * buf, phase ^ 1, p.status, 1));
-                if (!ok) break;
-                if (lane == 0) {
+            // A page past the sequence's last one is replaced by the last one: its keys are masked, but
+            // what stands in shared memory must be finite.
+            const int* table = p.table + (long long)slot * p.table_stride;
+            int page[KEYS / PAGE], next_page[KEYS / PAGE];
+            for (int pg = 0; pg < KEYS / PAGE; ++pg) page[pg] = __ldcg(table + min(j_lo * (KEYS / PAGE) + pg, n_pages - 1));
+            bool ok = true;
+            int fill = 0;                                       // K_j is fill 2(j - j_lo), V_j the next one
+            for (int j = j_lo; ok && j < j_hi; ++j) {
+                // The next step's page numbers are on their way while this step's tiles are waited for.
+                for (int pg = 0; pg < KEYS / PAGE; ++pg)
+                    next_page[pg] = j + 1 < j_hi ? __ldcg(table + min((j + 1) * (KEYS / PAGE) + pg, n_pages - 1)) : 0;
+                for (int kv = 0; kv < 2; ++kv, ++fill) {
+                    const int buf = fill % RING;
+                    const unsigned phase = (unsigned)(fill / RING) & 1u;
+                    ok = mbar_wait(kv_empty0 + 8 * buf, phase ^ 1, p.status, 1);
+                    if (!ok) break;
                     const unsigned bar = kv_full0 + 8 * buf;
                     mbar_expect_tx(bar, C::KV_TILE_BYTES);
                     const unsigned dst = smem_addr(kv_tiles + (size_t)buf * C::KV_TILE_BYTES);
                     for (int pg = 0; pg < KEYS / PAGE; ++pg) {
-                        // A page past the sequence's last one is replaced by the last one: its keys are
-                        // masked, but what stands in shared memory must be finite.
-                        const int page_index = min(j * (KEYS / PAGE) + pg, n_pages - 1);
-                        const int page = __ldcg(p.table + (long long)slot * p.table_stride + page_index);
-                        const int row = (page * p.kv_heads + kvh) * PAGE;
+                        const int row = (page[pg] * p.kv_heads + kvh) * PAGE;
                         for (int h = 0; h < C::HALVES; ++h)
                             tma_load_2d(dst + h * C::HALF_BYTES + pg * (PAGE * 128), kv ? &map_v : &map_k, h * 64, row, bar);
                     }
                 }
-                __syncwarp();
+                for (int pg = 0; pg < KEYS / PAGE; ++pg) page[pg] = next_page[pg];
             }
         }
     } else if (warp == 9) {
-        // ---------------------------------------------------------------- MMA issuer (lane 0 issues)
-        constexpr unsigned IDESC_QK = instr_desc_bf16(ROWS, KEYS, false);
-        constexpr unsigned IDESC_PV = instr_desc_bf16(ROWS, D, true);
-        bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0, p.status, 2));
-        tc_fence_after();
-        // S_x = Q_x K_jᵀ into tensor-memory columns [128 x, 128 x + 128).
-        auto issue_qk = [&](int x, int buf) {
-            if (lane == 0) {
+        // ---------------------------------------------------------------- MMA issue (one thread)
+        if (lane == 0) {
+            constexpr unsigned IDESC_QK = instr_desc_bf16(ROWS, KEYS, false);
+            constexpr unsigned IDESC_PV = instr_desc_bf16(ROWS, D, true);
+            // S_x = Q_x K_jᵀ into tensor-memory columns [128 x, 128 x + 128).
+            auto issue_qk = [&](int x, int buf) {
                 const unsigned qa = smem_addr(q_tiles + x * C::Q_TILE_BYTES);
                 const unsigned ka = smem_addr(kv_tiles + (size_t)buf * C::KV_TILE_BYTES);
 #pragma unroll
@@ -165,55 +184,41 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
                     umma_bf16(tmem_base + x * KEYS, smem_desc_sw128(qa + off), smem_desc_sw128(ka + off), IDESC_QK, s > 0 ? 1u : 0u);
                 }
                 umma_commit(s_full0 + 8 * x);
-            }
-            __syncwarp();
-        };
-        int fill = 0;
-        if (ok && j_lo < j_hi) {
-            ok = __all_sync(0xffffffffu, mbar_wait(kv_full0, 0, p.status, 3));
-            tc_fence_after();
-            if (ok) {
-                issue_qk(0, 0);
-                issue_qk(1, 0);
-                if (lane == 0) umma_commit(kv_empty0);
-                __syncwarp();
-            }
-        }
-        for (int j = j_lo; ok && j < j_hi; ++j, fill += 2) {
-            const int vbuf = (fill + 1) % RING, knext = (fill + 2) % RING;
-            const unsigned vphase = (unsigned)((fill + 1) / RING) & 1u, kphase = (unsigned)((fill + 2) / RING) & 1u;
-            ok = __all_sync(0xffffffffu, mbar_wait(kv_full0 + 8 * vbuf, vphase, p.status, 4));
-            if (!ok) break;
-            const unsigned jphase = (unsigned)(j - j_lo) & 1u;
-            for (int x = 0; x < 2; ++x) {
-                ok = __all_sync(0xffffffffu, mbar_wait(p_ready0 + 8 * x, jphase, p.status, 5));
-                if (!ok) break;
+            };
+            bool ok = mbar_wait(q_full, 0, p.status, 2);
+            if (ok && j_lo < j_hi) {
+                ok = mbar_wait(kv_full0, 0, p.status, 3);
                 tc_fence_after();
-                if (lane == 0) {
-                    const unsigned va = smem_addr(kv_tiles + (size_t)vbuf * C::KV_TILE_BYTES);
+                if (ok) {
+                    issue_qk(0, 0);
+                    issue_qk(1, 0);
+                    umma_commit(kv_empty0);
+                }
+            }
+            int fill = 0;
+            for (int j = j_lo; ok && j < j_hi; ++j, fill += 2) {
+                const int vbuf = (fill + 1) % RING, knext = (fill + 2) % RING;
+                const unsigned vphase = (unsigned)((fill + 1) / RING) & 1u, kphase = (unsigned)((fill + 2) / RING) & 1u;
+                const unsigned jphase = (unsigned)(j - j_lo) & 1u;
+                ok = mbar_wait(kv_full0 + 8 * vbuf, vphase, p.status, 4);
+                if (ok && j + 1 < j_hi) ok = mbar_wait(kv_full0 + 8 * knext, kphase, p.status, 6);
+                if (!ok) break;
+                const unsigned va = smem_addr(kv_tiles + (size_t)vbuf * C::KV_TILE_BYTES);
+                for (int x = 0; x < 2; ++x) {
+                    ok = mbar_wait(p_ready0 + 8 * x, jphase, p.status, 5);
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll
                     for (int s = 0; s < KEYS / 16; ++s)         // 16 keys = 16 rows of 128 bytes further on
                         umma_bf16_ts(tmem_base + C::O_COL + x * D, tmem_base + x * KEYS + s * 8,
                                      smem_desc_mn_sw128(va + s * 2048, C::HALF_BYTES, 1024), IDESC_PV, (j > j_lo || s > 0) ? 1u : 0u);
                     umma_commit(o_done0 + 8 * x);
+                    if (j + 1 < j_hi) issue_qk(x, knext);
                 }
-                __syncwarp();
-                if (j + 1 < j_hi) {
-                    if (x == 0) {
-                        ok = __all_sync(0xffffffffu, mbar_wait(kv_full0 + 8 * knext, kphase, p.status, 6));
-                        if (!ok) break;
-                        tc_fence_after();
-                    }
-                    issue_qk(x, knext);
-                    if (x == 1) {
-                        if (lane == 0) umma_commit(kv_empty0 + 8 * knext);
-                        __syncwarp();
-                    }
-                }
+                if (!ok) break;
+                umma_commit(kv_empty0 + 8 * vbuf);
+                if (j + 1 < j_hi) umma_commit(kv_empty0 + 8 * knext);
             }
-            if (!ok) break;
-            if (lane == 0) umma_commit(kv_empty0 + 8 * vbuf);
-            __syncwarp();
         }
     } else {
         // ---------------------------------------------------------------- softmax, one thread per row
@@ -280,22 +285,30 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
                 }
                 tmem_st_wait();
             }
-            float l4[4] = {0.f, 0.f, 0.f, 0.f};
-            const float neg_m = -m_used;
+            f32x2 l2[2] = {0ull, 0ull};                          // two chains of packed sums
+            const f32x2 scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(-m_used, -m_used);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 unsigned packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = ex2(fmaf(__uint_as_float(r[c][i]), p.scale_log2, neg_m));
-                    const float p1 = ex2(fmaf(__uint_as_float(r[c][i + 1]), p.scale_log2, neg_m));
-                    l4[(i >> 1) & 3] += p0 + p1;
+                    const f32x2 x2 = fma2(pack2(__uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1])), scale2, neg_m2);
+                    float p0, p1;
+                    unpack2(x2, p0, p1);
+                    p0 = ex2(p0);
+                    p1 = ex2(p1);
+                    l2[(i >> 1) & 1] = add2(l2[(i >> 1) & 1], pack2(p0, p1));
                     const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                     packed[i / 2] = *reinterpret_cast<const unsigned*>(&pk);
                 }
                 tmem_st16(s_addr + c * 16, packed);             // P over S, which is in registers by now
             }
-            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            {
+                float a0, a1, b0, b1;
+                unpack2(l2[0], a0, a1);
+                unpack2(l2[1], b0, b1);
+                l += (a0 + a1) + (b0 + b1);
+            }
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
