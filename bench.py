@@ -3,6 +3,7 @@
 model with random weights (bfloat16), plus prefill throughput and roofline fractions.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+    python bench.py --preset 8b-long | 70b        (the other two sizes the reference names; a line each)
 
 Prints one JSON line. A "step" is one decode step of the whole batch (default batch 8, every
 sequence after 1,023 cached positions, context 4,096). ``value`` is decoded tokens per second
@@ -38,6 +39,9 @@ APERTUS_8B = {
     "rms_norm_eps": 1e-5, "qk_norm": True, "tie_word_embeddings": False, "hidden_act": "xielu",
     "max_position_embeddings": 4096, "attention_bias": False, "mlp_bias": False,
 }
+# Apertus-70B sizes: 141 GB of weights on one GPU.
+APERTUS_70B = dict(APERTUS_8B, num_hidden_layers=80, hidden_size=8192, num_attention_heads=64, intermediate_size=43008,
+                   max_position_embeddings=2048)
 CONTEXT = 4096
 CACHED = 1023           # positions every sequence holds before the timed decode steps
 PREFILL_TOKENS = 2048
@@ -178,6 +182,126 @@ def time_e2e(engine, batch, steps, vocab):
     return batch * n_steps / span, n_steps
 
 
+def decode_from(engine, slots_list, logits, steps, warmup):
+    """ms per step of ``steps`` decode steps after ``warmup`` of them, through the library's decode loop,
+    for sequences that were prefilled (``logits`` are those of the prompts' last tokens)."""
+    import torch
+    from tileinfer_b200.engine.generate import _decode_batch
+    from tileinfer_b200.sampling import DeviceSampler, SamplingParams
+    batch = len(slots_list)
+    sampler = DeviceSampler(batch, engine.device)
+    slots = dict(enumerate(slots_list))
+    results = [[] for _ in range(batch)]
+    marks = {}
+
+    def on_token(request, token):
+        if request == 0 and len(results[0]) in (warmup, warmup + steps):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks[len(results[0])] = ev
+    _decode_batch(engine, sampler, SamplingParams(), list(range(batch)), slots, logits, results, warmup + steps + 2, set(), on_token)
+    torch.cuda.synchronize()
+    return marks[warmup].elapsed_time(marks[warmup + steps]) / steps
+
+
+def timed_step(engine, entries):
+    import torch
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    logits = engine.step(entries)
+    b.record()
+    torch.cuda.synchronize()
+    return logits, a.elapsed_time(b)
+
+
+def run_long_context(args, pk, pk_source):
+    """Apertus-8B sizes with 65,536 positions: 8 prompts of unequal lengths drawn uniformly from
+    [512, 32,768], prefilled together (in chunks of 8,192 tokens), then 256 decode steps."""
+    import torch
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.engine import Engine
+    cfg_dict = dict(APERTUS_8B, max_position_embeddings=65536)
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    cfg = ApertusConfig.from_dict(cfg_dict)
+    gen = torch.Generator().manual_seed(4)
+    lengths = torch.randint(512, 32769, (8,), generator=gen).tolist()
+    steps, warmup = 256 - 8, 6
+    room = sum(-(-(n + 256 + 2) // 64) * 64 for n in lengths)
+    engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=65536, max_seqs=8, max_tokens=room, max_step_tokens=8192)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in lengths]
+    warm = engine.new_sequence()                         # sizes the scratch buffers and loads the kernels
+    engine.step([(warm, prompts[0][:8192] * 2)])
+    engine.free_sequence(warm)
+    slots = [engine.new_sequence() for _ in prompts]
+    logits, prefill_ms = timed_step(engine, list(zip(slots, prompts)))
+    ms_step = decode_from(engine, slots, logits, steps, warmup)
+    engine.check_health()
+    weight_bytes = engine.weight_bytes() - engine.model.embed.numel() * engine.model.embed.element_size()
+    kv_bytes = (sum(lengths) + 8 * (warmup + 1 + steps / 2)) * engine.kv_bytes_per_position()
+    achieved = (weight_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9
+    H, I, D, nq, nkv = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    flops = cfg.num_hidden_layers * sum(2 * n * (H * (nq + 2 * nkv) * D + nq * D * H + 2 * H * I) + 4 * D * nq * n * (n + 1) // 2
+                                        for n in lengths)
+    print(json.dumps({
+        "metric": "decode tok/s (Apertus-8B bf16, 8 sequences of 512 to 32,768 positions)", "value": round(8000.0 / ms_step, 1),
+        "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms_step, 4), "dtype": "bf16",
+        "data": "synthetic: random weights, uniform random token ids",
+        "config": {"model": "Apertus-8B shapes", "layers": cfg.num_hidden_layers, "layers_full": 32, "global_batch": 8,
+                   "prompt_tokens": sum(lengths), "longest": max(lengths), "shortest": min(lengths), "max_positions": 65536,
+                   "prefill_chunk": 8192, "peaks": pk_source},
+        "prefill": {"value": round(sum(lengths) * 1000.0 / prefill_ms, 1), "tokens": sum(lengths), "ms": round(prefill_ms, 2),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)}}))
+    return 0
+
+
+def run_70b(args, pk, pk_source):
+    """Apertus-70B sizes (141 GB of weights): a 1,024-token prompt each, then decode at batch 1 and 8."""
+    import torch
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.engine import Engine
+    cfg_dict = dict(APERTUS_70B)
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    cfg = ApertusConfig.from_dict(cfg_dict)
+    engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=2048, max_seqs=8, max_tokens=8 * 1344, max_step_tokens=8192)
+    weight_bytes = engine.weight_bytes() - engine.model.embed.numel() * engine.model.embed.element_size()
+    gen = torch.Generator().manual_seed(5)
+    steps, warmup = max(8, args.steps), max(args.warmup, 3)
+    out = {}
+    for batch in (1, 8):
+        prompts = [torch.randint(0, cfg.vocab_size, (1024,), generator=gen).tolist() for _ in range(batch)]
+        slots = [engine.new_sequence() for _ in prompts]
+        logits, prefill_ms = timed_step(engine, list(zip(slots, prompts)))
+        if batch == 1:                                   # again, with the scratch buffers sized
+            engine.free_sequence(slots[0])
+            slots = [engine.new_sequence()]
+            logits, prefill_ms = timed_step(engine, list(zip(slots, prompts)))
+            out["prefill_1024"] = prefill_ms
+        ms = decode_from(engine, slots, logits, steps, warmup)
+        kv = batch * (1024 + warmup + 1 + steps / 2) * engine.kv_bytes_per_position()
+        out[batch] = (ms, (weight_bytes + kv) / (ms * 1e-3) / 1e9)
+    engine.check_health()
+    H, I, D, nq, nkv = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    flops = cfg.num_hidden_layers * (2 * 1024 * (H * (nq + 2 * nkv) * D + nq * D * H + 2 * H * I) + 4 * D * nq * 1024 * 1025 // 2)
+    print(json.dumps({
+        "metric": "decode tok/s (Apertus-70B bf16, batch 8, 1,024 cached positions)", "value": round(8000.0 / out[8][0], 1),
+        "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(out[8][0], 4), "dtype": "bf16",
+        "data": "synthetic: random weights, uniform random token ids",
+        "config": {"model": "Apertus-70B shapes", "layers": cfg.num_hidden_layers, "layers_full": 80, "hidden": H, "heads": nq,
+                   "kv_heads": nkv, "head_dim": D, "intermediate": I, "vocab": cfg.vocab_size,
+                   "weight_gb": round(engine.weight_bytes() / 1e9, 1), "peaks": pk_source},
+        "points": {"decode_b1": round(1000.0 / out[1][0], 2), "decode_b1_hbm_frac": round(out[1][1] / pk["hbm_gbs"], 4)},
+        "prefill": {"value": round(1024 * 1000.0 / out["prefill_1024"], 1), "tokens": 1024, "ms": round(out["prefill_1024"], 2),
+                    "frac": round(flops / (out["prefill_1024"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(out[8][1], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(out[8][1] / pk["hbm_gbs"], 4)}}))
+    return 0
+
+
 def flops_prefill(cfg, n_layers, tokens):
     H, I, D = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
@@ -194,6 +318,9 @@ def main(argv=None) -> int:
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0: all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick checks)")
+    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b"],
+                    help="8b: the headline line (default); 8b-long: 8 unequal sequences of up to 32,768 positions; "
+                         "70b: Apertus-70B sizes, 141 GB of weights")
     args = ap.parse_args(argv)
 
     if args.impl == "reference":
@@ -209,6 +336,10 @@ def main(argv=None) -> int:
     from tileinfer_b200.config import ApertusConfig
     from tileinfer_b200.engine import Engine
 
+    if args.preset == "8b-long":
+        return run_long_context(args, *peaks())
+    if args.preset == "70b":
+        return run_70b(args, *peaks())
     cfg_dict = dict(APERTUS_8B)
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
