@@ -183,14 +183,33 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    // Barriers and tensor memory are set up while the previous kernel drains; its results (the
-    // activations, and the output buffer it may still read) are touched only after this wait.
+    TileIter it;
+    it.id = blockIdx.x; it.step = gridDim.x; it.total = p.m_tiles * p.n_tiles * p.splits;
+
+    // Barriers and tensor memory are set up while the previous kernel drains, and the weights do not
+    // depend on it: the loads of the first tile's first weight blocks (as many as the pipeline has
+    // stages) are on their way before the wait. The previous kernel's results (the activations, and the
+    // output buffer it may still read) are touched only after it.
+    int ahead = 0;
+    if (warp == 0) {
+        TileIter first = it;
+        if (first.next(p)) {
+            ahead = min(C::STAGES, first.kb_hi - first.kb_lo);
+            if (lane == 0)
+                for (int s = 0; s < ahead; ++s) {
+                    const unsigned bar = full0 + 8 * s;
+                    mbar_expect_tx(bar, C::STAGE_BYTES);
+                    const unsigned a_dst = smem_addr(tiles + (size_t)s * C::STAGE_BYTES);
+#pragma unroll
+                    for (int h = 0; h < MT; ++h)
+                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, (first.kb_lo + s) * BK, (first.m * MT + h) * BM, bar);
+                }
+            __syncwarp();
+        }
+    }
     pdl_wait();
     pdl_launch_dependents();
     const unsigned tmem_base = *tmem_slot;
-
-    TileIter it;
-    it.id = blockIdx.x; it.step = gridDim.x; it.total = p.m_tiles * p.n_tiles * p.splits;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer (TMA)
@@ -198,17 +217,20 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
         int stage = 0;
         unsigned phase = 0;
         bool ok = true;
+        int issued = 0;                                     // k blocks of this block so far
         while (ok && it.next(p)) {
-            for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
+            for (int kb = it.kb_lo; kb < it.kb_hi; ++kb, ++issued) {
                 ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1));
                 if (!ok) break;
                 if (lane == 0) {
                     const unsigned bar = full0 + 8 * stage;
-                    mbar_expect_tx(bar, C::STAGE_BYTES);
                     const unsigned a_dst = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
+                    if (issued >= ahead) {                  // else the weights of this stage are already on their way
+                        mbar_expect_tx(bar, C::STAGE_BYTES);
 #pragma unroll
-                    for (int h = 0; h < MT; ++h)
-                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, kb * BK, (it.m * MT + h) * BM, bar);
+                        for (int h = 0; h < MT; ++h)
+                            tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, kb * BK, (it.m * MT + h) * BM, bar);
+                    }
                     tma_load_2d(a_dst + C::A_BYTES, &map_x, kb * BK, it.n * BN, bar);
                 }
                 __syncwarp();
