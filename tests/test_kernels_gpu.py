@@ -124,6 +124,39 @@ def paged(k, v, page_size, n_pages_total, perm_seed, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,D,n,splits", [(8, 2, 128, 70, 6), (4, 4, 64, 9, 3), (6, 2, 64, 200, 11), (5, 1, 48, 33, 4)])
+def test_attention_inputs_from_partial_sums(ops, dtype, nq, nkv, D, n, splits):
+    """A projection that was split over k hands its 32-bit partial sums [s, n, features] over; the kernel
+    adds them in split order and rounds once, so the result is bit for bit that of the stored projection
+    rnd(sum). Head sizes 64 and 128 in bfloat16 take the vector kernel, the rest the general one."""
+    torch.manual_seed(11)
+    from tileinfer_b200.config.spec import PositionSpec
+    from tileinfer_b200.parts import Runtime
+    from tileinfer_b200.parts.rope import RotaryEmbedding
+    F = (nq + 2 * nkv) * D
+    parts = torch.randn(splits, n, F) * torch.logspace(0, -3, splits)[:, None, None]
+    total = parts[0].clone()
+    for s in range(1, splits):
+        total = total + parts[s]                                   # float32, in split order
+    stored = rnd(total, dtype)
+    rope = RotaryEmbedding(PositionSpec("rope", D, 10000.0, None, 1024), Runtime(dtype), 1024)
+    qn, kn = dev(rnd(1 + 0.2 * torch.randn(D), dtype), dtype), dev(rnd(1 + 0.2 * torch.randn(D), dtype), dtype)
+    pos = torch.randint(0, 1024, (n,)).int().cuda()
+    pages = -(-n // 64) + 1
+    smap = torch.randperm(pages * 64)[:n].int().cuda()
+    outs = []
+    for src in (dev(stored, dtype), dev(parts)):
+        q = torch.zeros(n, nq, D, dtype=dtype, device="cuda")
+        kp = torch.zeros(pages, nkv, 64, D, dtype=dtype, device="cuda")
+        vp = torch.zeros(pages, nkv, 64, D, dtype=dtype, device="cuda")
+        ops.attention_inputs(src, q, kp, vp, qn, kn, 1e-5, rope.cos_sin, pos, smap, nq, nkv, D, 64)
+        outs.append((q, kp, vp))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    assert float(outs[0][0].float().abs().max()) > 0.1 and float(outs[0][2].float().abs().max()) > 0.1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,D,page", [(6, 3, 32, 64), (5, 1, 48, 16), (8, 2, 128, 64)])
 def test_attention_inputs_and_plain_attention(ops, dtype, nq, nkv, D, page):
     """q/k norm + rotation + cache write, then attention over the cache, for two sequences of which one

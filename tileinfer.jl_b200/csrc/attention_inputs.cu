@@ -88,11 +88,12 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, cons
     }
 }
 
-// The same for head sizes 64 and 128 in bfloat16 from a stored projection: a lane owns VPL = D/32
+// The same for head sizes 64 and 128 in bfloat16: a lane owns VPL = D/32
 // consecutive elements (one 4- or 8-byte access), the rotation partner i +- D/2 lives in lane +- 16 and
 // comes by shuffle, so no shared memory and no strided loops are needed.
 template <int VPL, int HPW>
-__global__ void attention_inputs_vec_kernel(const bf16* qkv, long long qkv_stride, bf16* __restrict__ q_out,
+__global__ void attention_inputs_vec_kernel(const bf16* qkv, long long qkv_stride, const float* partials, int n_partials,
+                                            long long partial_stride, bf16* __restrict__ q_out,
                                             bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                             const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float eps,
                                             const float* __restrict__ cos_sin, const int* positions, const int* slots,
@@ -117,10 +118,43 @@ __global__ void attention_inputs_vec_kernel(const bf16* qkv, long long qkv_strid
     pdl_enter();
     if (head0 >= heads_total) return;
     Pack raw[HPW];
+    if (partials == nullptr) {
 #pragma unroll
-    for (int i = 0; i < HPW; ++i) {
-        const int head = min(head0 + i, heads_total - 1);
-        raw[i] = __ldcg(reinterpret_cast<const Pack*>(qkv + (size_t)t * qkv_stride + (size_t)head * D) + lane);
+        for (int i = 0; i < HPW; ++i) {
+            const int head = min(head0 + i, heads_total - 1);
+            raw[i] = __ldcg(reinterpret_cast<const Pack*>(qkv + (size_t)t * qkv_stride + (size_t)head * D) + lane);
+        }
+    } else {
+        // The projection was split over k: its 32-bit partial sums [s][token][feature] are added in split
+        // order and rounded once, like any product (eight splits' loads in flight at a time).
+        typedef typename std::conditional<VPL == 4, float4, float2>::type PackF;
+#pragma unroll
+        for (int i = 0; i < HPW; ++i) {
+            const int head = min(head0 + i, heads_total - 1);
+            const float* ps = partials + (size_t)t * qkv_stride + (size_t)head * D + lane * VPL;
+            float acc[VPL];
+#pragma unroll
+            for (int e = 0; e < VPL; ++e) acc[e] = 0.f;
+            for (int s0 = 0; s0 < n_partials; s0 += 8) {
+                PackF part[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (s0 + u < n_partials) part[u] = __ldcg(reinterpret_cast<const PackF*>(ps + (size_t)(s0 + u) * partial_stride));
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (s0 + u < n_partials) {
+                        const float* f = reinterpret_cast<const float*>(&part[u]);
+#pragma unroll
+                        for (int e = 0; e < VPL; ++e) acc[e] = (s0 + u == 0) ? f[e] : acc[e] + f[e];
+                    }
+            }
+            unsigned* w = reinterpret_cast<unsigned*>(&raw[i]);
+#pragma unroll
+            for (int e = 0; e < VPL / 2; ++e) {
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+                w[e] = *reinterpret_cast<const unsigned*>(&h2);
+            }
+        }
     }
     const int page = slot_t / page_size, off = slot_t - page * page_size;
 #pragma unroll
@@ -191,12 +225,14 @@ extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, const 
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     dim3 grid(n_tokens, (heads_total + AI_WARPS - 1) / AI_WARPS);
     const size_t smem = (size_t)AI_WARPS * D * sizeof(float);
-    if (dtype == TI_BF16 && qkv != nullptr && (D == 64 || D == 128) && qkv_stride % 4 == 0 && aligned16(qkv) && aligned16(q_out) &&
+    if (dtype == TI_BF16 && (D == 64 || D == 128) && qkv_stride % 4 == 0 && aligned16(q_out) &&
+        (qkv != nullptr ? aligned16(qkv) : (aligned16(partials) && partial_stride % 4 == 0)) &&
         (!write_kv || (aligned16(k_cache) && aligned16(v_cache))) && (q_norm_w == nullptr || aligned16(q_norm_w)) &&
         (k_norm_w == nullptr || aligned16(k_norm_w)) && (cos_sin == nullptr || aligned16(cos_sin))) {
 #define AI_VEC_LAUNCH(VPL, HPW)                                                                                                     \
     ti_launch(attention_inputs_vec_kernel<VPL, HPW>, dim3(n_tokens, ((heads_total + HPW - 1) / HPW + AI_WARPS - 1) / AI_WARPS),         \
-              dim3(AI_WARPS * 32), 0, stream, (const bf16*)qkv, qkv_stride, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache,               \
+              dim3(AI_WARPS * 32), 0, stream, (const bf16*)qkv, qkv_stride, partials, n_partials, partial_stride, (bf16*)q_out,       \
+              (bf16*)k_cache, (bf16*)v_cache,                                                                                             \
               (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, cos_sin, positions, slots, nq, nkv, page_size, write_kv)
         // Few tokens: one head per warp (latency counts); many: four heads per warp (memory traffic counts).
         if (D == 128) { if (n_tokens <= 64) AI_VEC_LAUNCH(4, 1); else AI_VEC_LAUNCH(4, 4); }
