@@ -84,7 +84,7 @@ def bench_product(kind, out, k, n, splits, epilogue, once):
           f"{out * k * 2 / ms / 1e6:.0f} GB/s of weights, {2 * n * out * k / ms / 1e9:.1f} TFLOP/s")
 
 
-def bench_decode_attention(batch, context, once, heads=32, kv_heads=8, head_dim=128):
+def bench_decode_attention(batch, context, once, splits=0, heads=32, kv_heads=8, head_dim=128):
     L = lib()
     pages_per_seq = -(-context // 64)
     pages = batch * pages_per_seq
@@ -94,7 +94,7 @@ def bench_decode_attention(batch, context, once, heads=32, kv_heads=8, head_dim=
     table = torch.randperm(pages, device="cuda").to(torch.int32).view(batch, pages_per_seq)
     slots = torch.arange(batch, dtype=torch.int32, device="cuda")
     lens = torch.full((batch,), context, dtype=torch.int32, device="cuda")
-    splits = fast.decode_splits(batch, kv_heads, context)
+    splits = splits or fast.decode_splits(batch, kv_heads, context)
     out = torch.empty(batch, heads, head_dim, dtype=torch.bfloat16, device="cuda")
     ws_o = torch.empty(batch, heads, splits, head_dim, device="cuda")
     ws_ml = torch.empty(batch, heads, splits, 2, device="cuda")
@@ -216,7 +216,7 @@ def main(argv=None):
     ap.add_argument("--out", type=int, default=21504)
     ap.add_argument("--in", dest="k", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=1)
-    ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--splits", type=int, default=0, help="k slices of a product (default 1); parts of the decode attention (default: the engine's policy)")
     ap.add_argument("--epilogue", default="none", choices=["none", "xielu", "f32"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=1024)
@@ -225,9 +225,9 @@ def main(argv=None):
     ap.add_argument("--once", action="store_true", help="a few eager launches and no timing (for ncu)")
     a = ap.parse_args(argv)
     if a.what in ("gemv", "gemm"):
-        bench_product(a.what, a.out, a.k, a.tokens, a.splits, a.epilogue, a.once)
+        bench_product(a.what, a.out, a.k, a.tokens, max(1, a.splits), a.epilogue, a.once)
     elif a.what == "decode":
-        bench_decode_attention(a.batch, a.context, a.once)
+        bench_decode_attention(a.batch, a.context, a.once, a.splits)
     elif a.what == "prefill":
         bench_prefill_attention(a.tokens if a.tokens > 1 else 2048, a.once, a.kernel)
     else:
