@@ -62,30 +62,47 @@ class PagedGroup:
         self.pages = NumberPool(num_pages, "page")
         self.tables: Dict[int, List[int]] = {}
         self.max_pages_per_seq = max_pages_per_seq
-        pin = torch.device(device).type == "cuda"
-        self.host_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, pin_memory=pin)
+        self._pin = torch.device(device).type == "cuda"
+        self.host_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32)      # the host's copy, read by the step planner
         self.device_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, device=device)
 
     def pages_needed(self, slot: int, new_length: int) -> int:
         have = len(self.tables.get(slot, ()))
         return max(0, -(-new_length // self.page_size) - have)
 
-    def grow(self, slot: int, new_length: int) -> None:
-        need = self.pages_needed(slot, new_length)
-        if not need:
+    def grow_many(self, growth: Sequence[Tuple[int, int]]) -> None:
+        """Pages for each ``(slot, new length)`` (the caller has checked that the pool has them): the block
+        tables' new entries go up in ONE copy and the new pages' values are zeroed by ONE kernel."""
+        rows, cols, numbers = [], [], []
+        for slot, new_length in growth:
+            need = self.pages_needed(slot, new_length)
+            if not need:
+                continue
+            table = self.tables.setdefault(slot, [])
+            if len(table) + need > self.max_pages_per_seq:
+                raise ValueError(f"a sequence of {new_length} positions needs more than {self.max_pages_per_seq} pages")
+            new = self.pages.take_many(need)
+            a = len(table)
+            table.extend(new)
+            self.host_table[slot, a:a + need] = torch.tensor(new, dtype=torch.int32)
+            rows += [slot] * need
+            cols += range(a, a + need)
+            numbers += new
+        if not numbers:
             return
-        table = self.tables.setdefault(slot, [])
-        if len(table) + need > self.max_pages_per_seq:
-            raise ValueError(f"a sequence of {new_length} positions needs more than {self.max_pages_per_seq} pages")
-        new = self.pages.take_many(need)
-        a = len(table)
-        table.extend(new)
-        self.host_table[slot, a:a + need] = torch.tensor(new, dtype=torch.int32)
-        self.device_table[slot, a:a + need].copy_(self.host_table[slot, a:a + need], non_blocking=True)
+        # The upload reads its source when the stream gets there, which may be after a slot has been freed
+        # and handed to another sequence: it has a pinned buffer of its own (the allocator keeps it until the
+        # copy has run), never the host table, which the next owner overwrites at once.
+        packed = torch.tensor([rows, cols, numbers], dtype=torch.int64)
+        packed = (packed.pin_memory() if self._pin else packed).to(self.device_table.device, non_blocking=True)
+        self.device_table[packed[0], packed[1]] = packed[2].to(torch.int32)
         # A page's last user may have left anything in it. Keys beyond a sequence's length are masked by
         # selection, but their values take part in P V with weight 0, and 0 times a stale infinity or NaN
         # is NaN: values are zeroed when a page is taken.
-        self.v.index_fill_(1, self.device_table[slot, a:a + need].long(), 0)
+        self.v.index_fill_(1, packed[2], 0)
+
+    def grow(self, slot: int, new_length: int) -> None:
+        self.grow_many([(slot, new_length)])
 
     def first_needed_page(self, length: int) -> int:
         """Logical index of the first page that a query at position ``length`` or later can read."""
@@ -258,15 +275,13 @@ class Cache:
                 raise OutOfPagesError(need, g.pages.free)
         for g in self.paged_groups:
             if not (g.window and chunked):
-                for slot, n in growth:
-                    g.grow(slot, self.lengths[slot] + n)
+                g.grow_many([(slot, self.lengths[slot] + n) for slot, n in growth])
 
     def prepare(self, growth: Sequence[Tuple[int, int]]) -> None:
         """Before a chunk of a reserved step runs: the pages of this chunk for the groups that take
         them chunk by chunk (``reserve`` has checked that they are there)."""
         for g in self.windowed_groups:
-            for slot, n in growth:
-                g.grow(slot, self.lengths[slot] + n)
+            g.grow_many([(slot, self.lengths[slot] + n) for slot, n in growth])
 
     def advance(self, slot: int, n: int) -> None:
         """The step that wrote ``n`` more positions of ``slot`` has been enqueued."""
