@@ -268,6 +268,13 @@ def test_one_layer_at_apertus_8b_sizes(dtype):
         got = eng.step([(a, prompts[0]), (b, prompts[1])], [[0, 149], [36]]).cpu()
         want = torch.stack([refs[0][0], refs[0][149], refs[1][36]])
         assert float((got - want).abs().max()) <= tol
+        eng.free_sequence(a)
+        before = dict(library.call_counts)
+        a = eng.new_sequence()                                         # 100 tokens: the product with the tokens in the tensor-memory lanes
+        got = eng.step([(a, prompts[0][:100])], [list(range(100))]).cpu()
+        assert float((got - refs[0][:100]).abs().max()) <= tol
+        if dtype == "bfloat16":
+            assert library.call_counts.get("ti_gemm_tcgen05_decode", 0) - before.get("ti_gemm_tcgen05_decode", 0) == 2   # up projection and head
         eng.check_health()
 
 

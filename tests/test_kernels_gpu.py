@@ -560,3 +560,46 @@ def test_gemm_tcgen05(ops, n, out, k, splits):
         call(part, 3, splits)
         close(part.sum(0), want, torch.float32, ulps=64.0)
     fast.check_status()
+
+
+@pytest.mark.parametrize("n,out,k,tile,splits", [(9, 100, 72, 16, 1), (37, 301, 120, 48, 1), (64, 512, 1024, 112, 4), (128, 384, 512, 256, 1),
+                                                 (100, 4099, 264, 160, 3), (17, 2000, 4160, 240, 2), (64, 1000, 584, 0, 1),
+                                                 (33, 3000, 200, 32, 1)])     # the last one: a block walks several tiles
+def test_gemm_tcgen05_decode(ops, n, out, k, tile, splits):
+    """The decode-batch product (tokens in the tensor-memory lanes, weight rows in tiles of any multiple of 16)
+    against a 64-bit product: every epilogue, ragged last tiles, k that is no multiple of 64, k slices."""
+    from tileinfer_b200.kernels import fast
+    from tileinfer_b200.kernels.library import check, lib
+    torch.manual_seed(17)
+    dtype = torch.bfloat16
+    x, w = rnd(torch.randn(n, k), dtype), rnd(torch.randn(out, k) * k ** -0.5, dtype)
+    want = (x.double() @ w.double().t()).float()
+    xd, wd = dev(x, dtype), dev(w, dtype)
+    st = torch.cuda.current_stream().cuda_stream
+    status = fast.status_word()
+    def call(y, epi, s=1, act=(0.0, 0.0, 0.0, 0.0)):
+        check(lib().ti_gemm_tcgen05_decode(y.data_ptr(), out, xd.data_ptr(), k, wd.data_ptr(), n, out, k, tile, s, epi, *act,
+                                           status.data_ptr(), st), "tc decode")
+    y = torch.full((n, out), float("nan"), dtype=dtype, device="cuda")
+    call(y, 0)
+    close(y, rnd(want, dtype), dtype, ulps=1.0)
+    y32 = torch.full((n, out), float("nan"), device="cuda")
+    call(y32, 2)
+    assert torch.equal(y32.cpu(), y.float().cpu())
+    a = plain.xielu_scalars(torch.tensor(18.125), torch.tensor(10.5), torch.tensor(0.5), torch.tensor(-1e-6), dtype)
+    ya = torch.empty_like(y)
+    call(ya, 1, act=(float(a.alpha_p), float(a.alpha_n), float(a.beta), float(a.eps)))
+    assert torch.equal(ya.float().cpu(), plain.xielu(y.float().cpu(), a, dtype))
+    if splits > 1:
+        part = torch.full((splits, n, out), float("nan"), device="cuda")
+        call(part, 3, splits)
+        # 32-bit sums of k products of bfloat16 numbers: the rounding error grows like the square root of k.
+        close(part.sum(0), want, torch.float32, ulps=4.0 * k ** 0.5)
+        close(rnd(part.sum(0).cpu(), dtype), rnd(want, dtype), dtype, ulps=1.0)
+    # Rows past the last token and features past the last row are never written.
+    guard = torch.full((n + 3, out + 5), 7.0, dtype=dtype, device="cuda")
+    check(lib().ti_gemm_tcgen05_decode(guard.data_ptr(), out + 5, xd.data_ptr(), k, wd.data_ptr(), n, out, k, tile, 1, 0, 0.0, 0.0, 0.0, 0.0,
+                                       status.data_ptr(), st), "tc decode")
+    assert torch.equal(guard[:n, :out].float().cpu(), y.float().cpu())
+    assert bool((guard[n:] == 7.0).all()) and bool((guard[:, out:] == 7.0).all())
+    fast.check_status()

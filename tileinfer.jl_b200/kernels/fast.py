@@ -83,9 +83,59 @@ def tc_splits(out_features: int, in_features: int, n: int) -> int:
     return max(1, min(8, slots // tiles, (in_features // 64) // 8))
 
 
+# The product with the tokens in the tensor-memory lanes (gemm_tcgen05_decode.cu) takes up to 128 tokens.
+# The engine uses it from 65 tokens on for the products whose k cannot be cut (activation or logits
+# epilogue). Measured inside a decode step of Apertus-8B layers against the 128-row kernel: at 128 tokens
+# the up projection takes 41.6 us instead of 58.0 (its 168 tiles of 128 rows need a second round of blocks;
+# 135 tiles of 160 rows do not), the layer 229 us instead of 246; at 96 tokens the step is 4 % shorter. Up
+# to 64 tokens the 128-row kernel with two blocks per SM is faster inside the step (1,495 against 1,537 us
+# for 8 layers at 48 tokens), and products that may be cut over k are no faster here, while more slices cost
+# their consumer more (residual add + norm of 128 tokens: 8 us with 4 slices, 15 us with 7).
+DECODE_PRODUCT_MIN_TOKENS = 65
+DECODE_PRODUCT_MAX_TOKENS = 128
+DECODE_PRODUCT_SPLITTABLE = False      # the micro-benchmark's switch: send the products that may be cut over k there too
+_plans = {}
+
+
+def decode_product_plan(n: int, out_features: int, in_features: int, max_splits: int):
+    """(weight rows per tile, k slices) of the decode-batch product, as its own cost model chooses them."""
+    key = (n, out_features, in_features, max_splits)
+    plan = _plans.get(key)
+    if plan is None:
+        import ctypes
+        nt, splits = ctypes.c_int(), ctypes.c_int()
+        check(lib().ti_gemm_tcgen05_decode_plan(n, out_features, in_features, max_splits, SM_COUNT, ctypes.byref(nt),
+                                                ctypes.byref(splits)), "gemm_tcgen05_decode_plan")
+        plan = _plans[key] = (nt.value, splits.value)
+    return plan
+
+
+def _tcgen05_decode(lin, x, out, epilogue, act, allow_partials):
+    n, k = x.shape
+    w = lin.weight
+    may_split = allow_partials and epilogue == ops.EPI_NONE
+    nt, splits = decode_product_plan(n, lin.out_features, k, 8 if may_split else 1)
+    if splits > 1:
+        y = lin.rt.buffer("linear.partials", (splits, n, lin.out_features), torch.float32)
+        ldy, epilogue, act = lin.out_features, 3, (0.0, 0.0, 0.0, 0.0)
+    else:
+        y, ldy = out, out.stride(0)
+    rc = lib().ti_gemm_tcgen05_decode(y.data_ptr(), ldy, x.data_ptr(), x.stride(0), w.data_ptr(), n, lin.out_features, k, nt,
+                                      splits, epilogue, act[0], act[1], act[2], act[3], status_word().data_ptr(), _stream())
+    if rc == 2:
+        return None
+    check(rc, "gemm_tcgen05_decode")
+    return y
+
+
 def _tcgen05(lin, x, out, epilogue, act, allow_partials):
     n, k = x.shape
     w = lin.weight
+    may_split = allow_partials and epilogue == ops.EPI_NONE
+    if DECODE_PRODUCT_MIN_TOKENS <= n <= DECODE_PRODUCT_MAX_TOKENS and (DECODE_PRODUCT_SPLITTABLE or not may_split):
+        y = _tcgen05_decode(lin, x, out, epilogue, act, allow_partials)
+        if y is not None:
+            return y
     st = status_word()
     splits = tc_splits(lin.out_features, k, n) if (allow_partials and epilogue == ops.EPI_NONE) else 1
     if splits > 1:

@@ -101,12 +101,15 @@ def lib():
     handle.ti_sampling_uniform.argtypes = [_U, _U]
     handle.ti_argmax_chunks.restype = c_int
     handle.ti_argmax_chunks.argtypes = [c_int]
+    handle.ti_gemm_tcgen05_decode_plan.restype = c_int
+    handle.ti_gemm_tcgen05_decode_plan.argtypes = [c_int] * 5 + [ctypes.POINTER(c_int)] * 2
     class _Lib:
         pass
     wrapped = _Lib()
     wrapped.ti_last_error = handle.ti_last_error
     wrapped.ti_sampling_uniform = handle.ti_sampling_uniform
     wrapped.ti_argmax_chunks = handle.ti_argmax_chunks
+    wrapped.ti_gemm_tcgen05_decode_plan = handle.ti_gemm_tcgen05_decode_plan
     wrapped.handle = handle
     for name, args in _SIGNATURES.items():
         fn = getattr(handle, name)
@@ -141,6 +144,7 @@ def check(rc: int, what: str) -> None:
 _SIGNATURES_FAST = {
     "ti_gemv_bf16": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P],
     "ti_gemm_tcgen05": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
+    "ti_gemm_tcgen05_decode": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P, _P],
     "ti_attention_prefill": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _F, _I, _I, _I, _I, _I, _P],
     "ti_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_attention_decode_shared": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
