@@ -328,7 +328,14 @@ extern "C" int ti_add_rmsnorm(void* x, const void* delta, const float* partials,
     const bool al = aligned16(x) && aligned16(w) && aligned16(h) && (delta == nullptr || aligned16(delta)) &&
                     (partials == nullptr || (aligned16(partials) && partial_stride % 4 == 0));
     TI_DISPATCH_DTYPE(dtype, {
-        const int vt = al ? vec_threads<T>(size) : 0;
+        int vt = al ? vec_threads<T>(size) : 0;
+        if (vt && partials != nullptr && n_partials > 1) {
+            // The loop over the partial sums of one vector cannot be overlapped with the next vector's (its
+            // length is not known to the compiler): one vector per thread, so that a row is one round of loads.
+            const int vecs = size / Vec16<T>::N;
+            const int one_each = vecs >= 512 ? 512 : (vecs + 31) / 32 * 32;      // 512 threads of this kernel fill an SM's registers
+            if (one_each > vt) vt = one_each;
+        }
         if (vt) ti_launch(add_rmsnorm_vec_kernel<T>, dim3(n_rows), dim3(vt), 0, stream, (T*)x, (const T*)delta, partials, n_partials,
                                                                     (size_t)partial_stride, (const T*)w, (T*)h, size, eps);
         else ti_launch(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), 0, stream, (T*)x, (const T*)delta, partials, n_partials,
