@@ -235,8 +235,11 @@ extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, const 
               (bf16*)k_cache, (bf16*)v_cache,                                                                                             \
               (const bf16*)q_norm_w, (const bf16*)k_norm_w, eps, cos_sin, positions, slots, nq, nkv, page_size, write_kv)
         // Few tokens: one head per warp (latency counts); many: four heads per warp (memory traffic counts).
-        if (D == 128) { if (n_tokens <= 64) AI_VEC_LAUNCH(4, 1); else AI_VEC_LAUNCH(4, 4); }
-        else          { if (n_tokens <= 64) AI_VEC_LAUNCH(2, 1); else AI_VEC_LAUNCH(2, 4); }
+        // Partial sums (steps of up to 256 tokens) always one head per warp: the loop over the slices of one head
+        // cannot be overlapped with the next head's, so four heads would be four rounds of loads.
+        const bool one_head = n_tokens <= 64 || partials != nullptr;
+        if (D == 128) { if (one_head) AI_VEC_LAUNCH(4, 1); else AI_VEC_LAUNCH(4, 4); }
+        else          { if (one_head) AI_VEC_LAUNCH(2, 1); else AI_VEC_LAUNCH(2, 4); }
 #undef AI_VEC_LAUNCH
         return ti_check_launch("attention_inputs");
     }
