@@ -57,7 +57,7 @@ def test_embed_and_gather(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("size", [100, 2560, 4099])
+@pytest.mark.parametrize("size", [100, 2560, 4099, 16392])     # the last: longer than the vector kernels' blocks cover
 def test_rmsnorm_and_add_rmsnorm(ops, dtype, size):
     torch.manual_seed(1)
     x = rnd(torch.randn(7, size) * 3, dtype)

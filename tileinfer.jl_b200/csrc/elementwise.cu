@@ -329,6 +329,7 @@ extern "C" int ti_add_rmsnorm(void* x, const void* delta, const float* partials,
                     (partials == nullptr || (aligned16(partials) && partial_stride % 4 == 0));
     TI_DISPATCH_DTYPE(dtype, {
         int vt = al ? vec_threads<T>(size) : 0;
+        if (vt > 512) vt = 0;                  // the vector kernel's registers allow 512 threads: longer rows take the plain kernel
         if (vt && ((partials != nullptr && n_partials > 1) || (n_rows <= 16 && sizeof(T) == 2))) {
             // The loop over the partial sums of one vector cannot be overlapped with the next vector's (its
             // length is not known to the compiler): one vector per thread, so that a row is one round of loads.
