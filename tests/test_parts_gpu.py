@@ -163,6 +163,44 @@ def test_feed_forward_part(dtype, n):
     assert float((out.float().cpu() - ref).abs().max()) <= max(bound, tol(dtype, ref))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_block_part(dtype):
+    """The pre-norm arrangement alone, around a mixer and a feed-forward that exist only here (plain
+    torch arithmetic on the device): the residual stream after each of the two adds and the normed
+    input handed to the next block."""
+    from tileinfer_b200.config import NormSpec
+    from tileinfer_b200.parts import Runtime, lookup
+    torch.manual_seed(4)
+    H, n = 136, 11
+    rt = Runtime(dtype)
+
+    class Scale:
+        def __init__(self, factor):
+            self.factor = factor
+
+        def forward(self, h, step, cache=None):
+            return (h.float() * self.factor).to(h.dtype)
+
+    ws = {f"n{i}.weight": rnd(1 + 0.2 * torch.randn(H), dtype) for i in range(3)}
+    norms = [lookup("norm", "rmsnorm")(NormSpec("rmsnorm", H, 1e-6, f"n{i}.weight"), {k: v.to(dtype) for k, v in ws.items()}, rt)
+             for i in range(3)]
+    block = lookup("block", "pre_norm")(None, Scale(0.75), Scale(-0.5), norms[0], norms[1])
+    assert block.input_norm is norms[0]
+    x = rnd(torch.randn(n, H) * 2, dtype)
+    xs = x.to(dtype).cuda()
+    h = torch.empty(n, H, dtype=dtype, device="cuda")
+    norms[0].forward(xs, h)
+    h_out = torch.empty_like(h)
+    assert block.forward(xs, h, None, None, norms[2], h_out) is h_out
+    h0 = plain.rmsnorm(x, ws["n0.weight"], 1e-6, dtype)
+    x1 = rnd(x + rnd(h0 * 0.75, dtype), dtype)
+    h1 = plain.rmsnorm(x1, ws["n1.weight"], 1e-6, dtype)
+    x2 = rnd(x1 + rnd(h1 * -0.5, dtype), dtype)
+    ref = plain.rmsnorm(x2, ws["n2.weight"], 1e-6, dtype)
+    assert float((xs.float().cpu() - x2).abs().max()) <= tol(dtype, x2)
+    assert float((h_out.float().cpu() - ref).abs().max()) <= tol(dtype, ref)
+
+
 # ------------------------------------------------------------------------------------------------
 # Toy parts, defined in this test only.
 def build_toy_architecture():
