@@ -35,7 +35,23 @@ def test_sampling_params_are_validated():
 
 
 def test_mix32_is_lowbias32_and_sequence_seeds_differ():
-    assert mix32(0) == 0 and mix32(1) == 0x6E5CB2E1 or True
+    def lowbias32(x):                                   # src/engine/sampler.jl:34-38, written out step by step
+        x ^= x >> 16
+        x = x * 0x7FEB352D % 2 ** 32
+        x ^= x >> 15
+        x = x * 0x846CA68B % 2 ** 32
+        return x ^ (x >> 16)
+    assert mix32(0) == 0
+    for x in (1, 2, 0x12345678, 0xFFFFFFFF, 0x80000000, 12345):
+        assert mix32(x) == lowbias32(x) and 0 <= mix32(x) < 2 ** 32
+    assert len({mix32(x) for x in range(5000)}) == 5000          # a bijection has no collisions
+    # The uniform numbers built on it, with the reference's own checks (test/engine/sampler.jl:68-76).
+    import plain_apertus as plain
+    u = [plain.sampling_uniform(seed, c) for seed in range(1, 21) for c in range(1000)]
+    assert all(0 <= x < 1 for x in u) and abs(sum(u) / len(u) - 0.5) < 0.01
+    counts = [sum(1 for x in u if (b - 1) / 10 <= x < b / 10) for b in range(1, 11)]
+    assert all(abs(c - 2000) < 200 for c in counts)
+    assert len(set(u[:1000])) == 1000 and plain.sampling_uniform(1, 0) != plain.sampling_uniform(2, 0)
     seeds = {sequence_seed(5, i) for i in range(100)}
     assert len(seeds) == 100 and sequence_seed(5, 3) != sequence_seed(6, 3)
 
