@@ -1,0 +1,96 @@
+"""The step's metadata, built on the host (engine/step.py): positions, cache places, sequence ranges and
+wanted rows of batches of unequal sequences, and the short path for one-token steps, which must write
+exactly what the general one writes. Runs on the CPU (the planner only fills integer buffers)."""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from tileinfer_b200.cache import Cache
+from tileinfer_b200.engine.step import StepPlanner, split_tables
+from tileinfer_b200.parts import CacheRequest
+
+
+def make(page_size=4, max_seqs=5, max_tokens=200, window=None):
+    cache = Cache([CacheRequest("paged_kv", kv_heads=2, head_dim=16, window=window)], torch.float32, "cpu",
+                  max_tokens=max_tokens, max_seqs=max_seqs, page_size=page_size)
+    return cache, StepPlanner(cache, 64, "cpu")
+
+
+def place(cache, slot, position):
+    g = cache.paged_groups[0]
+    return int(g.host_table[slot, position // g.page_size]) * g.page_size + position % g.page_size
+
+
+def test_a_batch_of_unequal_sequences():
+    cache, planner = make()
+    a, b, c = cache.alloc_slot(), cache.alloc_slot(), cache.alloc_slot()
+    cache.reserve([(a, 6), (b, 1), (c, 9)])
+    ctx = planner.plan([(a, [1, 2, 3, 4, 5, 6]), (b, [7]), (c, list(range(10, 19)))], [[0, 5], [], [8]])
+    assert (ctx.n_tokens, ctx.n_seqs, ctx.n_want) == (16, 3, 3) and not ctx.is_decode
+    assert ctx.token_ids.tolist() == [1, 2, 3, 4, 5, 6, 7] + list(range(10, 19))
+    assert ctx.positions.tolist() == list(range(6)) + [0] + list(range(9))
+    assert ctx.tok_slot.tolist() == [a] * 6 + [b] + [c] * 9
+    assert ctx.cu_seqlens.tolist() == [0, 6, 7, 16] and ctx.kv_lens.tolist() == [6, 1, 9]
+    assert ctx.want_idx.tolist() == [0, 5, 15]
+    want = [place(cache, a, p) for p in range(6)] + [place(cache, b, 0)] + [place(cache, c, p) for p in range(9)]
+    assert ctx.group(0).slot_mapping.tolist() == want and len(set(want)) == 16          # no two tokens share a place
+    for s, n in ((a, 6), (b, 1), (c, 9)):
+        cache.advance(s, n)
+    # The next step continues where the sequences stand: one token each, the middle one gone.
+    cache.free_slot(b)
+    cache.reserve([(a, 1), (c, 1)])
+    ctx = planner.plan([(a, [40]), (c, [41])], [[0], [0]])
+    assert ctx.is_decode and ctx.positions.tolist() == [6, 9] and ctx.kv_lens.tolist() == [7, 10]
+    assert ctx.group(0).slot_mapping.tolist() == [place(cache, a, 6), place(cache, c, 9)]
+    with pytest.raises(ValueError, match="outside"):
+        planner.plan([(a, [1])], [[1]])
+
+
+def test_the_short_path_for_one_token_steps_writes_what_the_general_one_writes():
+    rng = random.Random(3)
+    cache, planner = make(max_seqs=6, max_tokens=400)
+    planner.split_policy = lambda batch, group: 4                  # decode attention's work tables too
+    slots = [cache.alloc_slot() for _ in range(6)]
+    for s in slots:
+        n = rng.randrange(1, 40)
+        cache.reserve([(s, n)])
+        cache.advance(s, n)
+    for _ in range(30):
+        live = rng.sample(slots, rng.randrange(1, 7))
+        tokens = [rng.randrange(1000) for _ in live]
+        cache.reserve([(s, 1) for s in live])
+        general = planner.plan([(s, [t]) for s, t in zip(live, tokens)], [[0]] * len(live))
+        words = general.n_tokens
+        o, _ = planner._layout(words, words, words)
+        first = planner.meta[:o["end"]].clone()
+        planner.meta.zero_()
+        short = planner.plan_decode(live, tokens)
+        assert torch.equal(planner.meta[:o["end"]], first)
+        assert short.is_decode and short.host_starts == general.host_starts and short.max_kv_len == general.max_kv_len
+        for s in live:
+            cache.advance(s, 1)
+
+
+def test_decode_work_tables_cover_every_page_once():
+    """Every sequence's parts are consecutive slots, there are as many as its entry says, none beyond the
+    launch's B x splits, and long sequences get more of them."""
+    rng = np.random.default_rng(0)
+    for B, splits in ((1, 32), (3, 8), (8, 4), (5, 2)):
+        for _ in range(20):
+            lengths = rng.integers(1, 3000, size=B)
+            work, seq = split_tables(lengths, splits, 64)
+            assert work.shape == (B * splits, 2)
+            used = 0
+            for b in range(B):
+                first, parts = int(seq[b]) >> 8, int(seq[b]) & 255
+                assert first == used and 1 <= parts <= min(32, -(-int(lengths[b]) // 64))
+                for i in range(parts):
+                    w = int(work[first + i, 0])
+                    assert (w >> 16, (w >> 8) & 255, w & 255) == (b, i, parts) and int(work[first + i, 1]) == int(lengths[b])
+                used += parts
+            assert used <= B * splits and all(int(w) == -1 for w in work[used:, 0])
+            order = np.argsort(lengths)
+            parts_of = (seq & 255)[order]
+            assert all(parts_of[i] <= parts_of[i + 1] for i in range(B - 1))           # more keys, no fewer parts
