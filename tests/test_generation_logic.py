@@ -80,3 +80,22 @@ def test_decode_work_slots_are_shared_out_by_length():
         assert ((seq & 255) == min(splits, 32)).all()
     work, seq = split_tables(np.array([100, 100, 100, 30000], dtype=np.int64), 8, 64)
     assert (seq & 255).tolist()[3] >= 25
+
+
+def test_generation_config_json_gives_defaults_and_more_stop_tokens(tmp_path):
+    """do_sample / temperature / top_k / top_p and eos_token_id of generation_config.json, merged with the
+    configuration's EOS ids (src/engine/generate.jl:83-93); greedy without the file or without do_sample."""
+    import json
+    from types import SimpleNamespace
+    from tileinfer_b200.api import generation_defaults
+    engine = SimpleNamespace(spec=SimpleNamespace(eos_token_ids=[2]))
+    sampling, stop = generation_defaults(str(tmp_path), engine)
+    assert sampling.greedy and stop == [2]
+    (tmp_path / "generation_config.json").write_text(json.dumps(
+        {"do_sample": True, "temperature": 0.6, "top_k": 20, "top_p": 0.95, "eos_token_id": [2, 7]}))
+    sampling, stop = generation_defaults(str(tmp_path), engine)
+    assert (sampling.temperature, sampling.top_k, sampling.top_p) == (0.6, 20, 0.95) and stop == [2, 7]
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": 0.6, "eos_token_id": 9}))
+    sampling, stop = generation_defaults(str(tmp_path), engine)
+    assert sampling.greedy and stop == [2, 9]
+    assert engine.spec.eos_token_ids == [2]                      # the configuration's own list is not changed
