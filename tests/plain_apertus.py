@@ -43,7 +43,7 @@ def read_config(c: dict) -> SimpleNamespace:
         head_dim=c.get("head_dim") or c["hidden_size"] // heads,
         eps=c["rms_norm_eps"], theta=theta, scaling=scaling,
         max_pos=c["max_position_embeddings"], tied=c.get("tie_word_embeddings", False),
-        qk_norm=c.get("qk_norm", True),
+        qk_norm=c.get("qk_norm", True), init_std=c.get("initializer_range", 0.02),
         eos=[] if eos is None else [eos] if isinstance(eos, int) else list(eos),
     )
 
@@ -204,6 +204,89 @@ def forward(cfg, W: Dict[str, torch.Tensor], ids: Sequence[int], dtype: torch.dt
     h = rmsnorm(x, W["model.norm.weight"], cfg.eps, dtype)
     head = W["model.embed_tokens.weight"][: cfg.vocab] if cfg.tied else W["lm_head.weight"]
     return linear(h, head, dtype)                                                # rounded, then 32-bit out
+
+
+# ----------------------------------------------------------------------------- random weights
+def random_normal(seed: int, name: str, count: int):
+    """The library's random-weights function, restated: z_i = f(seed, name, i), i < count, as float32.
+
+    The reference has no random-weights mode (its only random model is a fixture script,
+    scripts/gen_apertus_fixtures.py:80-96); the function is this library's own, built on the reference's
+    integer mix (src/engine/sampler.jl:34-47): keys k0 = mix32(mix32(seed) xor fnv1a(name)),
+    k1 = mix32(k0 + 0x9E3779B9); a = mix32(k0 xor i) >> 8, b = mix32(k1 xor i) >> 8; Box-Muller
+    z = sqrt(-2 ln((a + 1) 2^-24)) cos(2 pi b 2^-24), with the logarithm (2 atanh series of the mantissa
+    brought into (sqrt 1/2, sqrt 2]) and the cosine (octants of b, Taylor series on [0, pi/4]) spelled out
+    in single 32-bit operations, so that every machine gets the same bits."""
+    import numpy as np
+    f32, u32 = np.float32, np.uint32
+    name_hash = 0x811C9DC5
+    for byte in name.encode():
+        name_hash = ((name_hash ^ byte) * 0x01000193) % 2 ** 32
+    k0 = mix32(mix32(seed % 2 ** 32) ^ name_hash)
+    k1 = mix32((k0 + 0x9E3779B9) % 2 ** 32)
+
+    def mix(x):
+        x = (x ^ (x >> u32(16))) * u32(0x7FEB352D)
+        x = (x ^ (x >> u32(15))) * u32(0x846CA68B)
+        return x ^ (x >> u32(16))
+
+    def series(coefficients, y):
+        acc = np.full(y.shape, f32(coefficients[0]), f32)
+        for c in coefficients[1:]:
+            acc = acc * y
+            acc = acc + f32(c)
+        return acc
+
+    i = np.arange(count, dtype=u32)
+    a, b = mix(i ^ u32(k0)) >> u32(8), mix(i ^ u32(k1)) >> u32(8)
+    mant, expo = np.frexp((a + u32(1)).astype(f32))            # n = mant 2^expo, mant in [0.5, 1)
+    m, e = mant * f32(2), expo.astype(np.int32) - 1              # m in [1, 2)
+    fold = m > f32(math.sqrt(2.0))
+    m, e = np.where(fold, m * f32(0.5), m), e + fold
+    s = (m - f32(1)) / (m + f32(1))
+    ln_u = (e - 24).astype(f32) * f32(math.log(2.0)) + s * series([2 / 9, 2 / 7, 2 / 5, 2 / 3, 2.0], s * s)
+    radius = np.sqrt(f32(-2) * ln_u)
+    octant = b >> u32(21)
+    frac = (b % u32(1 << 21)).astype(f32) * f32(2.0 ** -21)
+    x = np.where(octant % 2 == 1, f32(1) - frac, frac) * f32(math.pi / 4)
+    sin_x = x * series([1 / 362880, -1 / 5040, 1 / 120, -1 / 6, 1.0], x * x)
+    cos_x = series([-1 / 3628800, 1 / 40320, -1 / 720, 1 / 24, -0.5, 1.0], x * x)
+    c = np.where(np.isin(octant, (1, 2, 5, 6)), sin_x, cos_x)
+    c = np.where(np.isin(octant, (2, 3, 4, 5)), -c, c)
+    return radius * c
+
+
+def random_weights(cfg, seed: int, dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
+    """The model that the library's random-weights mode makes for ``cfg`` and ``seed``, as 32-bit tensors
+    holding values rounded to ``dtype``: matrices N(0, std), norm weights 1 + N(0, std), raw xIELU alphas
+    log(e^0.8 - 1) + N(0, 0.05), beta 0.5, eps -1e-6; value = mean + z std in 32-bit."""
+    import numpy as np
+    H, D, std = cfg.hidden, cfg.head_dim, cfg.init_std
+    shapes = {"model.embed_tokens.weight": ((cfg.vocab, H), 0.0, std), "model.norm.weight": ((H,), 1.0, std)}
+    if not cfg.tied:
+        shapes["lm_head.weight"] = ((cfg.vocab, H), 0.0, std)
+    raw_alpha = math.log(math.expm1(0.8))
+    consts = {}
+    for l in range(cfg.layers):
+        p = f"model.layers.{l}."
+        shapes.update({
+            p + "attention_layernorm.weight": ((H,), 1.0, std), p + "feedforward_layernorm.weight": ((H,), 1.0, std),
+            p + "self_attn.q_proj.weight": ((cfg.heads * D, H), 0.0, std),
+            p + "self_attn.k_proj.weight": ((cfg.kv_heads * D, H), 0.0, std),
+            p + "self_attn.v_proj.weight": ((cfg.kv_heads * D, H), 0.0, std),
+            p + "self_attn.o_proj.weight": ((H, cfg.heads * D), 0.0, std),
+            p + "mlp.up_proj.weight": ((cfg.inter, H), 0.0, std), p + "mlp.down_proj.weight": ((H, cfg.inter), 0.0, std),
+            p + "mlp.act_fn.alpha_p": ((1,), raw_alpha, 0.05), p + "mlp.act_fn.alpha_n": ((1,), raw_alpha, 0.05)})
+        if cfg.qk_norm:
+            shapes.update({p + "self_attn.q_norm.weight": ((D,), 1.0, std), p + "self_attn.k_norm.weight": ((D,), 1.0, std)})
+        consts.update({p + "mlp.act_fn.beta": 0.5, p + "mlp.act_fn.eps": -1e-6})
+    out = {}
+    for name, (shape, mean, sd) in shapes.items():
+        z = random_normal(seed, name, int(np.prod(shape)))
+        out[name] = rnd(torch.from_numpy(np.float32(mean) + z * np.float32(sd)).reshape(shape), dtype)
+    for name, value in consts.items():
+        out[name] = rnd(torch.tensor(value, dtype=torch.float32), dtype)
+    return out
 
 
 # ----------------------------------------------------------------------------- sampling (host rule)

@@ -46,6 +46,43 @@ def test_random_distributions():
     assert "lm_head.weight" not in t            # tied
 
 
+def test_the_generator_is_a_function_of_seed_name_and_index():
+    """value = f(seed, tensor name, element index): a part of a tensor can be made alone, other tensors
+    change nothing, and the plain implementation's restatement of the function gives the same bits."""
+    import numpy as np
+    import plain_apertus as plain
+    from tileinfer_b200.config.spec import TensorDecl
+    from tileinfer_b200.weights.random_init import standard_normal, tensor_keys
+    name = "model.layers.3.mlp.down_proj.weight"
+    k0, k1 = tensor_keys(5, name)
+    z = standard_normal(k0, k1, 0, 70000)
+    assert z.dtype == np.float32 and np.array_equal(z[1234:1300], standard_normal(k0, k1, 1234, 66))
+    assert np.array_equal(z, plain.random_normal(5, name, 70000))
+    # Near the end of the 32-bit counter, and refused beyond it.
+    assert standard_normal(k0, k1, (1 << 32) - 8, 8).shape == (8,)
+    with pytest.raises(ValueError, match="32-bit counter"):
+        standard_normal(k0, k1, (1 << 32) - 8, 9)
+    assert abs(float(z.mean())) < 0.02 and abs(float(z.std()) - 1) < 0.02 and abs(float((z ** 4).mean()) - 3) < 0.2
+    assert tensor_keys(5, name) != tensor_keys(6, name) and tensor_keys(5, name) != tensor_keys(5, name + "x")
+    alone = random_tensors([TensorDecl(name, (7, 9), ("normal", 0.02))], 5)[name]
+    among = random_tensors([TensorDecl("other", (3,), ("normal", 1.0)), TensorDecl(name, (7, 9), ("normal", 0.02))], 5)[name]
+    assert torch.equal(alone, among)
+    want = torch.from_numpy(np.float32(0.0) + z[:63] * np.float32(0.02)).to(torch.bfloat16).view(7, 9)
+    assert torch.equal(alone, want)
+
+
+def test_the_plain_implementation_regenerates_a_random_model(tmp_path):
+    """Folder written by the library == weights restated by the plain implementation, tensor by tensor."""
+    import plain_apertus as plain
+    for cfg_dict, seed in ((helpers.TINY_A, 0), (helpers.TINY_B, 1), (helpers.TINY_C, 2)):
+        cfg, d = _folder(tmp_path / str(seed), cfg_dict, seed)
+        pc, stored = plain.load_folder(d)
+        again = plain.random_weights(pc, seed)
+        assert set(again) == set(stored)
+        for k in stored:
+            assert torch.equal(stored[k].reshape(-1), again[k].reshape(-1)), k
+
+
 def test_stored_types_are_kept(tmp_path):
     tensors = {"a": torch.randn(3, 4).to(torch.bfloat16), "b": torch.randn(3), "c": torch.arange(5),
                "d": torch.randn(2, 2).to(torch.float16)}
@@ -58,7 +95,8 @@ def test_stored_types_are_kept(tmp_path):
     assert t["a"].dtype == torch.bfloat16 and torch.equal(t["a"], tensors["a"])
     assert t["b"].dtype == torch.float32 and torch.equal(t["b"], tensors["b"])
     assert t["c"].dtype == torch.int32 and t["c"].tolist() == [0, 1, 2, 3, 4]
-    assert t["d"].dtype == torch.bfloat16
+    # float16 is kept as stored: the 32-bit path widens it exactly, a bfloat16 run rounds it once.
+    assert t["d"].dtype == torch.float16 and torch.equal(t["d"], tensors["d"])
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):

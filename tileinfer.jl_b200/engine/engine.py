@@ -66,7 +66,6 @@ class Engine:
         self._graphs: Dict[int, object] = {}
         self._logits: Dict[int, torch.Tensor] = {}
         self._graph_launches: Dict[int, int] = {}
-        self._graph_generation = -1
         self.vocab_size = self.spec.vocab_size
 
     # ---- construction
@@ -190,14 +189,17 @@ class Engine:
         if not self.use_graphs:
             self.model.forward(ctx, self.cache, logits)
         else:
-            if self._graph_generation != self.rt.generation:
-                # A scratch buffer was reallocated since the graphs were captured (a larger step came
-                # through): they point at freed memory and are captured again.
-                self._graphs.clear()
-            graph = self._graphs.get(B)
-            if graph is None:
+            held = self._graphs.get(B)
+            if held is not None and held[1] != self.rt.generation:
+                # A scratch buffer was reallocated since this graph was captured (a step of another size
+                # needed a larger one, perhaps the eager first step of another batch size): the graph
+                # points at freed memory and is captured again.
+                held = None
+                del self._graphs[B]
+            if held is None:
                 # First step of this size runs eagerly (it sizes the scratch buffers), then a capture
-                # of the same launches replaces it; the capture recomputes the same values.
+                # of the same launches replaces it; the capture recomputes the same values. The graph is
+                # stored with the buffer generation it saw AFTER the eager step.
                 self.model.forward(ctx, self.cache, logits)
                 torch.cuda.current_stream().synchronize()
                 from ..kernels import library
@@ -205,11 +207,10 @@ class Engine:
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph):
                     self.model.forward(ctx, self.cache, logits)
-                self._graphs[B] = graph
-                self._graph_generation = self.rt.generation
+                self._graphs[B] = (graph, self.rt.generation)
                 self._graph_launches[B] = library.launch_count - before
             else:
-                graph.replay()
+                held[0].replay()
         for s in slots:
             self.cache.advance(s, 1)
         return logits

@@ -43,6 +43,13 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous=True):
         raise KernelError(f"{name} must be contiguous")
 
 
+def random_normal(out, k0: int, k1: int, mean: float, std: float, first: int = 0):
+    """out.flat[j] = mean + std * z(first + j) of the counter-based generator with keys (k0, k1)."""
+    _need(out, "out")
+    check(lib().ti_random_normal(out.data_ptr(), dtype_code(out.dtype), out.numel(), first, k0, k1, mean, std, _stream()),
+          "random_normal")
+
+
 def embed(out, table, ids, status):
     _need(out, "out"); _need(table, "table", out.dtype); _need(ids, "ids", torch.int32); _need(status, "status", torch.int32)
     n, hidden = out.shape

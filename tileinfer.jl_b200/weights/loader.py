@@ -3,9 +3,10 @@
 A model declares the tensors it expects (:class:`TensorDecl`: name, shape); the loader
 reads exactly those from the folder's safetensors files and raises ONE error that lists
 every missing tensor, every unexpected tensor and every wrong shape. Stored dtypes are
-kept: bfloat16 stays bfloat16 (float16 is brought to bfloat16), integer tables become
-int32, and a tensor stored in 32-bit floating point stays 32-bit. Parts cast what their
-kernels need when they are built. The reference raises on the first missing name or wrong
+kept: bfloat16 stays bfloat16, a tensor stored in 32-bit floating point stays 32-bit, float16
+stays float16 (the reference converts the file's type straight to the run type,
+src/hub/loader.jl:43-44: widening float16 to 32-bit is exact, and a bfloat16 run rounds it once),
+and integer tables become int32. Parts cast what their kernels need when they are built. The reference raises on the first missing name or wrong
 size (src/hub/loader.jl:36, 94-97).
 """
 from __future__ import annotations
@@ -35,10 +36,8 @@ class WeightsError(ValueError):
 
 
 def _stored_dtype(t: torch.Tensor) -> torch.Tensor:
-    if t.dtype in (torch.bfloat16, torch.float32):
+    if t.dtype in (torch.bfloat16, torch.float32, torch.float16):
         return t
-    if t.dtype == torch.float16:
-        return t.to(torch.bfloat16)
     if t.dtype == torch.float64:
         return t.to(torch.float32)
     if t.dtype in (torch.int64, torch.int16, torch.int8, torch.uint8, torch.bool, torch.int32):
