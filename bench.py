@@ -2,15 +2,18 @@
 """Benchmark of the serving step on ONE GPU: decode tokens per second of an Apertus-8B-shaped
 model with random weights (bfloat16), plus prefill throughput and roofline fractions.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--dtype bfloat16|float32] [--impl reference]
     python bench.py --preset 8b-long | 70b        (the other two sizes the reference names; a line each)
 
 Prints one JSON line. A "step" is one decode step of the whole batch (default batch 8, every
 sequence after 1,023 cached positions, context 4,096). ``value`` is decoded tokens per second
 timed on the device with CUDA events around K graph-replayed steps; ``e2e`` is the same
 through the Python entry point (``tileinfer_b200.generate``), host token ids in and out.
-``prefill`` is one 2,048-token prompt; ``points`` holds decode at batch 1 and 64; ``roofline``
-relates the decode step's bytes (every weight once + the live cache) to the HBM peak.
+``prefill`` is one 2,048-token prompt; ``roofline`` relates the decode step's bytes (every weight
+the step reads once + the live cache) to the HBM peak. ``points`` holds, flat, decode at batch 1 and
+64 (``decode_bN`` tokens per second, ``decode_bN_ms`` per step, ``decode_bN_frac`` of the HBM peak,
+``e2e_bN`` through the entry point) and the true 32-bit path at batch 8 (``decode_fp32_b8*``).
+``--dtype float32`` makes the 32-bit path the headline instead.
 
 Timing: W >= 3 warm-up steps; every step reads all weights (16 GB), far more than the 126 MB
 L2, so no flush is needed between steps; SM clocks and throttle reasons are sampled with
@@ -46,6 +49,8 @@ CONTEXT = 4096
 CACHED = 1023           # positions every sequence holds before the timed decode steps
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# The 32-bit path runs on the FMA pipe: 148 SMs x 128 lanes x 2 flops x 1.965 GHz (nominal; nothing measures it here).
+FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
 
 def peaks():
@@ -118,7 +123,7 @@ def time_decode(engine, batch, steps, warmup, vocab, count_launches=False):
     loop (greedy sampling on the device, the host one step behind): CUDA events are recorded when the
     tokens of step W and of step W + K reach the host, which brackets exactly K steps on the stream."""
     import torch
-    from tileinfer_b200.engine.generate import _decode_batch
+    from tileinfer_b200.engine.generate import decode_batch
     from tileinfer_b200.sampling import DeviceSampler, SamplingParams
     warmup = max(warmup, 3)
     slots_list = fill_cache(engine, batch, CACHED - 1)
@@ -135,7 +140,7 @@ def time_decode(engine, batch, steps, warmup, vocab, count_launches=False):
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
             marks[len(results[0])] = ev
-    _decode_batch(engine, sampler, SamplingParams(), list(range(batch)), slots, logits, results, warmup + steps + 2, set(), on_token)
+    decode_batch(engine, sampler, SamplingParams(), list(range(batch)), slots, logits, results, warmup + steps + 2, set(), on_token)
     torch.cuda.synchronize()
     ms = marks[warmup].elapsed_time(marks[warmup + steps])
     launches = engine.decode_launches(batch) + 2 if count_launches else 0     # the captured step + sampling + id hand-over
@@ -163,9 +168,13 @@ def time_prefill(engine, tokens, vocab, reps=3):
     return best
 
 
-def time_e2e(engine, batch, steps, vocab):
-    """Decode rate through the public entry point: ``generate`` with host token ids in and out; the
-    clock runs from the first generated token of the batch to the last."""
+def time_e2e(engine, batch, steps, vocab, sample_clocks=False):
+    """Decode rate through the public entry point: ``generate`` with host token ids in and out. The clock
+    runs from the second generated token of the batch to the last (the reference's stats line does the
+    same, src/cli.jl:177-187). Besides the mean, the arrival times give the median step and the mean of
+    the first 16 steps: right after the prompts' step, which runs into the power cap, the SM clock comes
+    back up over some tens of steps, and a gap between mean and median that closes with more steps is that
+    ramp, not host time (host time would show in the median as well)."""
     import torch
     import tileinfer_b200 as ti
     gen = torch.Generator().manual_seed(3)
@@ -175,18 +184,28 @@ def time_e2e(engine, batch, steps, vocab):
     def on_token(request, token):
         if request == 0:
             stamps.append(time.perf_counter())         # the token is on the host: no synchronisation needed
+    clocks = ClockSampler() if sample_clocks else None
+    if clocks:
+        clocks.start()
     ti.generate(engine, prompts, max_new_tokens=steps + 2, stop_ids=[], on_token=on_token)
     torch.cuda.synchronize()
-    span = stamps[-1] - stamps[1]                      # from the second token on, as the reference's stats line
+    clock_info = clocks.stop() if clocks else None
+    gaps = sorted(b - a for a, b in zip(stamps[1:], stamps[2:]))
+    first = [b - a for a, b in zip(stamps[1:17], stamps[2:18])]
     n_steps = len(stamps) - 2
-    return batch * n_steps / span, n_steps
+    span = stamps[-1] - stamps[1]
+    out = {"value": round(batch * n_steps / span, 1), "unit": "tok/s", "steps": n_steps, "ms_mean": round(1e3 * span / n_steps, 4),
+           "ms_median": round(1e3 * gaps[len(gaps) // 2], 4), "ms_first16": round(1e3 * sum(first) / max(len(first), 1), 4)}
+    if clock_info:
+        out["sm_mhz"] = clock_info["sm_mhz"]
+    return out
 
 
 def decode_from(engine, slots_list, logits, steps, warmup):
     """ms per step of ``steps`` decode steps after ``warmup`` of them, through the library's decode loop,
     for sequences that were prefilled (``logits`` are those of the prompts' last tokens)."""
     import torch
-    from tileinfer_b200.engine.generate import _decode_batch
+    from tileinfer_b200.engine.generate import decode_batch
     from tileinfer_b200.sampling import DeviceSampler, SamplingParams
     batch = len(slots_list)
     sampler = DeviceSampler(batch, engine.device)
@@ -199,7 +218,7 @@ def decode_from(engine, slots_list, logits, steps, warmup):
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
             marks[len(results[0])] = ev
-    _decode_batch(engine, sampler, SamplingParams(), list(range(batch)), slots, logits, results, warmup + steps + 2, set(), on_token)
+    decode_batch(engine, sampler, SamplingParams(), list(range(batch)), slots, logits, results, warmup + steps + 2, set(), on_token)
     torch.cuda.synchronize()
     return marks[warmup].elapsed_time(marks[warmup + steps]) / steps
 
@@ -235,10 +254,13 @@ def run_long_context(args, pk, pk_source):
     engine.step([(warm, prompts[0][:8192] * 2)])
     engine.free_sequence(warm)
     slots = [engine.new_sequence() for _ in prompts]
+    clocks = ClockSampler()
+    clocks.start()
     logits, prefill_ms = timed_step(engine, list(zip(slots, prompts)))
     ms_step = decode_from(engine, slots, logits, steps, warmup)
+    clock_info = clocks.stop()
     engine.check_health()
-    weight_bytes = engine.weight_bytes() - engine.model.embed.numel() * engine.model.embed.element_size()
+    weight_bytes = engine.weight_bytes()
     kv_bytes = (sum(lengths) + 8 * (warmup + 1 + steps / 2)) * engine.kv_bytes_per_position()
     achieved = (weight_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9
     H, I, D, nq, nkv = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
@@ -251,6 +273,7 @@ def run_long_context(args, pk, pk_source):
         "config": {"model": "Apertus-8B shapes", "layers": cfg.num_hidden_layers, "layers_full": 32, "global_batch": 8,
                    "prompt_tokens": sum(lengths), "longest": max(lengths), "shortest": min(lengths), "max_positions": 65536,
                    "prefill_chunk": 8192, "peaks": pk_source},
+        "clocks": clock_info,
         "prefill": {"value": round(sum(lengths) * 1000.0 / prefill_ms, 1), "tokens": sum(lengths), "ms": round(prefill_ms, 2),
                     "frac": round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -268,10 +291,12 @@ def run_70b(args, pk, pk_source):
         cfg_dict["num_hidden_layers"] = args.layers
     cfg = ApertusConfig.from_dict(cfg_dict)
     engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=2048, max_seqs=8, max_tokens=8 * 1344, max_step_tokens=8192)
-    weight_bytes = engine.weight_bytes() - engine.model.embed.numel() * engine.model.embed.element_size()
+    weight_bytes = engine.weight_bytes()
     gen = torch.Generator().manual_seed(5)
     steps, warmup = max(8, args.steps), max(args.warmup, 3)
     out = {}
+    clocks = ClockSampler()
+    clocks.start()
     for batch in (1, 8):
         prompts = [torch.randint(0, cfg.vocab_size, (1024,), generator=gen).tolist() for _ in range(batch)]
         slots = [engine.new_sequence() for _ in prompts]
@@ -284,6 +309,7 @@ def run_70b(args, pk, pk_source):
         ms = decode_from(engine, slots, logits, steps, warmup)
         kv = batch * (1024 + warmup + 1 + steps / 2) * engine.kv_bytes_per_position()
         out[batch] = (ms, (weight_bytes + kv) / (ms * 1e-3) / 1e9)
+    clock_info = clocks.stop()
     engine.check_health()
     H, I, D, nq, nkv = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
     flops = cfg.num_hidden_layers * (2 * 1024 * (H * (nq + 2 * nkv) * D + nq * D * H + 2 * H * I) + 4 * D * nq * 1024 * 1025 // 2)
@@ -294,7 +320,9 @@ def run_70b(args, pk, pk_source):
         "config": {"model": "Apertus-70B shapes", "layers": cfg.num_hidden_layers, "layers_full": 80, "hidden": H, "heads": nq,
                    "kv_heads": nkv, "head_dim": D, "intermediate": I, "vocab": cfg.vocab_size,
                    "weight_gb": round(engine.weight_bytes() / 1e9, 1), "peaks": pk_source},
-        "points": {"decode_b1": round(1000.0 / out[1][0], 2), "decode_b1_hbm_frac": round(out[1][1] / pk["hbm_gbs"], 4)},
+        "clocks": clock_info,
+        "points": {"decode_b1": round(1000.0 / out[1][0], 2), "decode_b1_ms": round(out[1][0], 4),
+                   "decode_b1_frac": round(out[1][1] / pk["hbm_gbs"], 4)},
         "prefill": {"value": round(1024 * 1000.0 / out["prefill_1024"], 1), "tokens": 1024, "ms": round(out["prefill_1024"], 2),
                     "frac": round(flops / (out["prefill_1024"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(out[8][1], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -309,6 +337,15 @@ def flops_prefill(cfg, n_layers, tokens):
     return n_layers * per_layer + 2 * H * cfg["vocab_size"]
 
 
+def decode_point(engine, batch, steps, warmup, vocab, pk, count_launches=False):
+    """One decode measurement: tokens per second, ms per step, the bytes the step has to read (every
+    weight once, and the cache of the live sequences) and their rate as a fraction of the HBM peak."""
+    ms, kv_positions, launches = time_decode(engine, batch, steps, warmup, vocab, count_launches=count_launches)
+    step_bytes = engine.weight_bytes() + kv_positions * engine.kv_bytes_per_position()
+    gbs = step_bytes / (ms * 1e-3) / 1e9
+    return {"value": batch * 1000.0 / ms, "ms": ms, "bytes": step_bytes, "gbs": gbs, "frac": gbs / pk["hbm_gbs"], "launches": launches}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -316,6 +353,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0: all)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="float32: the true 32-bit path (strict 32-bit FMA products) as the headline")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick checks)")
     ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b"],
@@ -346,52 +385,67 @@ def main(argv=None) -> int:
         cfg_dict["num_hidden_layers"] = args.layers
     cfg = ApertusConfig.from_dict(cfg_dict)
     pk, pk_source = peaks()
-    batches = sorted({1, args.batch, 64} if not args.skip_points else {args.batch})
-    max_batch = max(batches)
-    engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=CONTEXT, max_seqs=max_batch,
-                           max_tokens=max(max_batch * 1280, PREFILL_TOKENS + 64), max_step_tokens=PREFILL_TOKENS)
+    fp32 = args.dtype == "float32"
     vocab = cfg.vocab_size
-    weight_bytes = engine.weight_bytes() - engine.model.embed.numel() * engine.model.embed.element_size() \
-        if engine.spec.lm_head_name is not None else engine.weight_bytes()
-    kv_per_pos = engine.kv_bytes_per_position()
+    batches = sorted({1, args.batch, 64} if not (args.skip_points or fp32) else {args.batch})
+    max_batch = max(batches)
 
-    prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab)
+    def make_engine(dtype):
+        return Engine.random(cfg, seed=0, dtype=dtype, max_context=CONTEXT, max_seqs=max_batch,
+                             max_tokens=max(max_batch * 1280, PREFILL_TOKENS + 64), max_step_tokens=PREFILL_TOKENS)
+
+    engine = make_engine(args.dtype)
+    prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab, reps=1 if fp32 else 3)
+    e2e_steps = max(min(args.steps, 16), 8) if fp32 else max(args.steps, 128)
     points = {}
     for b in batches:
         if b == args.batch:
             continue
-        ms, _, _ = time_decode(engine, b, max(8, args.steps // 2), args.warmup, vocab)
-        points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+        pt = decode_point(engine, b, max(8, args.steps // 2), args.warmup, vocab, pk)
+        points.update({f"decode_b{b}": round(pt["value"], 1), f"decode_b{b}_ms": round(pt["ms"], 4),
+                       f"decode_b{b}_frac": round(pt["frac"], 4), f"e2e_b{b}": time_e2e(engine, b, e2e_steps, vocab)["value"]})
 
     clocks = ClockSampler()
     clocks.start()
-    ms_step, kv_positions, launches = time_decode(engine, args.batch, args.steps, args.warmup, vocab, count_launches=True)
+    head = decode_point(engine, args.batch, args.steps, args.warmup, vocab, pk, count_launches=True)
     clock_info = clocks.stop()
-    e2e_value, e2e_steps = time_e2e(engine, args.batch, min(args.steps, 64), vocab)
+    e2e = time_e2e(engine, args.batch, e2e_steps, vocab, sample_clocks=True)
+    e2e.update({"h2d_bytes_per_step": engine.planner.last_upload_bytes, "d2h_bytes_per_step": 4 * args.batch})
+    page_size = engine.cache.page_size
+    engine.check_health()
 
-    step_bytes = weight_bytes + kv_positions * kv_per_pos
-    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    if not fp32 and not args.skip_points:
+        # The true 32-bit path at the same sizes: 32-bit weights, activations and cache, strict FMA products.
+        del engine
+        torch.cuda.empty_cache()
+        engine = make_engine("float32")
+        pt = decode_point(engine, args.batch, 8, 3, vocab, pk)
+        points.update({f"decode_fp32_b{args.batch}": round(pt["value"], 1), f"decode_fp32_b{args.batch}_ms": round(pt["ms"], 4),
+                       f"decode_fp32_b{args.batch}_frac": round(pt["frac"], 4)})
+        engine.check_health()
+
     pf_flops = flops_prefill(cfg_dict, cfg.num_hidden_layers, PREFILL_TOKENS)
-    value = args.batch * 1000.0 / ms_step
+    pf_peak = FP32_TFLOPS if fp32 else pk["bf16_tflops"]
+    name = "fp32" if fp32 else "bf16"
     line = {
-        "metric": "decode tok/s (Apertus-8B bf16, batch 8, 1023 cached positions)", "value": round(value, 1),
-        "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "metric": f"decode tok/s (Apertus-8B {name}, batch {args.batch}, {CACHED} cached positions)", "value": round(head["value"], 1),
+        "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(head["ms"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": name,
         "data": "synthetic: random weights, uniform random token ids",
         "config": {"model": "Apertus-8B shapes", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "none",
                    "layers": cfg.num_hidden_layers, "layers_full": full_layers, "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "cached_positions": CACHED,
-                   "prefill_tokens": PREFILL_TOKENS, "rope_theta": cfg.rope_theta, "page_size": engine.cache.page_size,
-                   "l2": "step inputs (16 GB of weights) exceed L2", "peaks": pk_source},
+                   "prefill_tokens": PREFILL_TOKENS, "rope_theta": cfg.rope_theta, "page_size": page_size,
+                   "l2": "step inputs (16 GB of weights) exceed L2",
+                   "peaks": pk_source + (", 32-bit FMA peak nominal" if fp32 else "")},
         "clocks": clock_info,
-        "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "steps": e2e_steps,
-                "h2d_bytes_per_step": engine.planner.last_upload_bytes, "d2h_bytes_per_step": 4 * args.batch},
-        "gpu_launches": launches * args.steps,
+        "e2e": e2e,
+        "gpu_launches": head["launches"] * args.steps,
         "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
-                    "ms": round(prefill_ms, 3), "frac": round(pf_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+                    "ms": round(prefill_ms, 3), "frac": round(pf_flops / (prefill_ms * 1e-3) / (pf_peak * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(head["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(head["frac"], 4), "bytes": int(head["bytes"])},
         "points": points,
     }
     print(json.dumps(line))

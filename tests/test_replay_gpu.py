@@ -16,7 +16,17 @@ from tileinfer_b200.weights import write_model_folder
 
 pytestmark = pytest.mark.gpu
 
+# Two layers with the layer sizes of Apertus-8B and its vocabulary, untied: the sizes the tensor-core products, the
+# weight-streaming product and both attention kernels were written for.
+LAYERS_8B = {
+    "architectures": ["ApertusForCausalLM"], "model_type": "apertus", "num_hidden_layers": 2, "hidden_size": 4096,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 21504, "vocab_size": 131072,
+    "rope_theta": 12000000.0, "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 8192,
+                                              "low_freq_factor": 1.0, "high_freq_factor": 4.0},
+    "rms_norm_eps": 1e-5, "qk_norm": True, "tie_word_embeddings": False, "hidden_act": "xielu", "max_position_embeddings": 4096,
+}
 CASES = {
+    "8B layers": (LAYERS_8B, 4, [3, 70, 130, 33]),
     "A": (helpers.TINY_A, 0, [5, 9, 13, 40, 70, 33, 100]),
     "B": (helpers.TINY_B, 1, [1, 4, 17, 33, 70, 129, 64]),
     "D": (helpers.TINY_D, 3, [3, 70, 130, 200, 64, 257, 31]),       # head size 64: the tensor-core prefill attention
@@ -44,7 +54,7 @@ def build_trace(requests):
     t.tail_one_by_one(requests)
     names = list(requests)
     # Two batches after one another; the second reuses the slots and pages of the first.
-    b1, b2 = names[:4], names[3:]
+    b1, b2 = names[:4], names[3:] if len(names) > 4 else names[1:]
     dec = lambda group: {r: min(len(requests[r]) - 1, 3 + 5 * i) for i, r in enumerate(group)}
     t.batch({r: requests[r] for r in b1}, dec(b1), tag="x")
     t.batch({r: requests[r] for r in b2}, dec(b2), tag="y")

@@ -164,3 +164,18 @@ def test_reads_files_written_by_the_safetensors_package(tmp_path):
     save_file(tensors, str(tmp_path / "ours.safetensors"))
     with safe_open(str(tmp_path / "ours.safetensors"), "pt") as g:
         assert torch.equal(g.get_tensor("w"), tensors["w"]) and g.get_tensor("s").shape == ()
+
+
+def test_weight_bytes_counts_what_a_step_reads():
+    """Every matrix and norm vector once, the head included, a tied head once, the embedding table of an
+    untied model not at all (a step reads one row per token); this is the roofline's weight term."""
+    from tileinfer_b200.engine.model import DecoderModel
+    from tileinfer_b200.parts import Runtime
+    for cfg_dict in (helpers.TINY_A, helpers.TINY_B):
+        cfg = ApertusConfig.from_dict(cfg_dict)
+        spec = cfg.model_spec()
+        tensors = random_tensors(tensor_declarations(spec), 0)
+        model = DecoderModel(spec, tensors, Runtime(torch.bfloat16, "cpu"), 64)
+        read = {k: v for k, v in tensors.items() if v.numel() > 1 and (k != "model.embed_tokens.weight" or cfg.tie_word_embeddings)}
+        assert ("lm_head.weight" in read) == (not cfg.tie_word_embeddings)
+        assert model.weight_bytes() == sum(v.numel() * 2 for v in read.values())

@@ -77,7 +77,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 256
         try:
             sampler.reset([sequence_seed(seed, r) for r in batch])
             logits = engine.step([(slots[r], prompts[r]) for r in batch])
-            _decode_batch(engine, sampler, sampling, list(batch), slots, logits, results, max_new_tokens, stop, on_token)
+            decode_batch(engine, sampler, sampling, list(batch), slots, logits, results, max_new_tokens, stop, on_token)
             engine.check_health()
         finally:
             for r in list(slots):
@@ -85,8 +85,14 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_new_tokens: int = 256
     return results
 
 
-def _decode_batch(engine, sampler, sampling, live, slots, logits, results, max_new_tokens, stop, on_token):
+def decode_batch(engine, sampler, sampling, live, slots, logits, results, max_new_tokens, stop, on_token=None):
     """Decode one batch to its end, with the host one step behind the device.
+
+    ``live``: the requests of the batch, in the order of the rows of ``logits`` (the logits of each
+    request's last token so far); ``slots[r]``: the sequence of request ``r`` (removed, and the
+    sequence freed, when the request ends); ``results[r]``: the list new tokens are appended to.
+    ``generate`` calls this after the prompts' step; a caller that prefilled sequences itself with
+    ``Engine.step`` may call it directly.
 
     Step k+1 is put on the stream BEFORE the host has seen the tokens sampled after step k: its ids are
     gathered on the device from the sampler's output, and its batch is every sequence that still has

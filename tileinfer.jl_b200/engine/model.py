@@ -85,22 +85,33 @@ class DecoderModel:
         return shares
 
     def weight_bytes(self) -> int:
-        """Bytes of every weight a step reads once (a tied head counts once)."""
+        """Bytes of every weight a step reads once: the parts' matrices and vectors and the head (a tied
+        head counts once). The embedding table is not among them: a step reads one row of it per token.
+        Parts are walked through their attributes, lists and dicts included (experts kept in a list
+        count); position encodings hold tables, not weights, and are left out."""
+        from ..parts.base import Part, PositionEncoding
         seen, total = set(), 0
+
         def visit(obj):
             nonlocal total
-            for v in vars(obj).values():
-                if isinstance(v, torch.Tensor) and v.is_floating_point() and v.data_ptr() not in seen and v.numel() > 1:
-                    if isinstance(obj, (DecoderModel,)) and v is self.status:
-                        continue
-                    seen.add(v.data_ptr()); total += v.numel() * v.element_size()
-                elif isinstance(v, Linear):
+            if isinstance(obj, torch.Tensor):
+                if obj.is_floating_point() and obj.numel() > 1 and obj.data_ptr() not in seen:
+                    seen.add(obj.data_ptr())
+                    total += obj.numel() * obj.element_size()
+            elif isinstance(obj, (list, tuple)):
+                for v in obj:
                     visit(v)
+            elif isinstance(obj, dict):
+                for v in obj.values():
+                    visit(v)
+            elif isinstance(obj, (Part, Linear)) and not isinstance(obj, PositionEncoding) and id(obj) not in seen:
+                seen.add(id(obj))
+                for v in vars(obj).values():
+                    visit(v)
+
         for b in self.blocks:
-            for part in (b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm):
-                visit(part)
-        visit(self.final_norm)
-        visit(self.lm_head)
+            visit([b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm])
+        visit([self.final_norm, self.lm_head])
         return total
 
     def forward(self, step, cache, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
