@@ -168,13 +168,47 @@ def test_errors_leave_the_cache_untouched(models):
     assert float((eng.step([(a, [3])]).cpu()[0] - ref).abs().max()) < 2e-5     # still consistent afterwards
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rolling_a_sequence_back_and_feeding_the_tokens_again(models, dtype):
+    """Engine.truncate drops a sequence's last positions; feeding the same tokens again gives the same logits
+    bit for bit, also across a page's border (the page goes back to the pool and is taken again), as the
+    reference does with truncate! + forward! (test/model/forward.jl:65-67)."""
+    import tileinfer_b200 as ti
+    folder, pc, pw = models["B"]
+    eng = ti.Engine.load(folder, dtype=dtype, max_context=256, max_seqs=2, max_tokens=512)
+    seq = helpers.random_prompts(pc.vocab, [70], 21)[0]
+    ref = plain.forward(pc, pw, seq, torch.float32 if dtype == "float32" else torch.bfloat16)
+    a, b = eng.new_sequence(), eng.new_sequence()
+    eng.step([(b, seq[:30])])                                      # a neighbour that must not be disturbed
+    eng.step([(a, seq[:60])])
+    first = [eng.step([(a, [seq[t]]), (b, [seq[30 + t - 60]])]).clone() for t in range(60, 67)]
+    free = eng.cache.free_pages()
+    eng.truncate(a, 66)                                            # one token back
+    assert eng.sequence_length(a) == 66 and eng.cache.free_pages() == free
+    again = eng.step([(a, [seq[66]])])
+    assert float((again[0].cpu() - ref[66]).abs().max()) <= tolerance(dtype, ref)
+    if dtype == "float32":                                         # (in bfloat16 a step of one sequence splits its keys otherwise)
+        assert torch.equal(again[0], first[6][0])
+    eng.truncate(a, 62)                                            # back across the page border at 64
+    assert eng.cache.free_pages() == free + 1
+    redo = eng.step([(a, seq[62:67])], [[0, 1, 2, 3, 4]])          # five tokens in one step this time
+    for j, t in enumerate(range(62, 67)):
+        assert float((redo[j].cpu() - ref[t]).abs().max()) <= tolerance(dtype, ref)
+        if dtype == "float32":
+            assert torch.equal(redo[j], first[t - 60][0])
+    assert float((eng.step([(b, [seq[37]])])[0].cpu() - ref[37]).abs().max()) <= tolerance(dtype, ref)
+    with pytest.raises(ValueError, match="truncate"):
+        eng.truncate(a, 68)
+    eng.check_health()
+
+
 def test_a_long_prompt_is_cut_into_chunks_without_changing_results(models):
     import tileinfer_b200 as ti
     folder, pc, pw = models["C"]
     prompts = helpers.random_prompts(pc.vocab, [150, 40, 99], 13)
     whole = ti.Engine.load(folder, dtype="float32", max_context=256, max_seqs=3, max_tokens=1024)
     cut = ti.Engine.load(folder, dtype="float32", max_context=256, max_seqs=3, max_tokens=1024, max_step_tokens=64)
-    want = [[149], [0, 39], [50, 98]]
+    want = [[149, 3, 70], [39, 0], [50, 98]]             # in any order, also across the chunks' borders
     outs = []
     for eng in (whole, cut):
         slots = [eng.new_sequence() for _ in prompts]

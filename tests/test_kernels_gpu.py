@@ -123,6 +123,19 @@ def paged(k, v, page_size, n_pages_total, perm_seed, dtype):
     return dev(kp, dtype), dev(vp, dtype), dev(table)
 
 
+def plain_rotation(D, theta, scaling, positions, dtype, rotary=None, interleaved=False):
+    """The record the attention-inputs kernel takes, with its table made by the plain implementation
+    (32-bit angles, 64-bit cos/sin, rounded to the element type), not by the library's rope part."""
+    from types import SimpleNamespace
+    rotary = rotary or D
+    cfg = plain.read_config({"vocab_size": 8, "hidden_size": 8, "intermediate_size": 8, "num_hidden_layers": 1,
+                             "num_attention_heads": 1, "head_dim": rotary, "rms_norm_eps": 1e-5, "rope_theta": theta,
+                             "max_position_embeddings": positions, "rope_scaling": scaling})
+    cos, sin = plain.rope_tables(cfg, torch.arange(positions), dtype)                   # [positions, rotary], halves equal
+    table = torch.stack([cos[:, :rotary // 2], sin[:, :rotary // 2]], -1).contiguous().cuda()
+    return SimpleNamespace(cos_sin=table, rotary_dim=rotary, interleaved=interleaved)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,D,n,splits", [(8, 2, 128, 70, 6), (4, 4, 64, 9, 3), (6, 2, 64, 200, 11), (5, 1, 48, 33, 4)])
 def test_attention_inputs_from_partial_sums(ops, dtype, nq, nkv, D, n, splits):
@@ -130,16 +143,13 @@ def test_attention_inputs_from_partial_sums(ops, dtype, nq, nkv, D, n, splits):
     adds them in split order and rounds once, so the result is bit for bit that of the stored projection
     rnd(sum). Head sizes 64 and 128 in bfloat16 take the vector kernel, the rest the general one."""
     torch.manual_seed(11)
-    from tileinfer_b200.config.spec import PositionSpec
-    from tileinfer_b200.parts import Runtime
-    from tileinfer_b200.parts.rope import RotaryEmbedding
     F = (nq + 2 * nkv) * D
     parts = torch.randn(splits, n, F) * torch.logspace(0, -3, splits)[:, None, None]
     total = parts[0].clone()
     for s in range(1, splits):
         total = total + parts[s]                                   # float32, in split order
     stored = rnd(total, dtype)
-    rope = RotaryEmbedding(PositionSpec("rope", D, 10000.0, None, 1024), Runtime(dtype), 1024)
+    rotation = plain_rotation(D, 10000.0, None, 1024, dtype)
     qn, kn = dev(rnd(1 + 0.2 * torch.randn(D), dtype), dtype), dev(rnd(1 + 0.2 * torch.randn(D), dtype), dtype)
     pos = torch.randint(0, 1024, (n,)).int().cuda()
     pages = -(-n // 64) + 1
@@ -149,7 +159,7 @@ def test_attention_inputs_from_partial_sums(ops, dtype, nq, nkv, D, n, splits):
         q = torch.zeros(n, nq, D, dtype=dtype, device="cuda")
         kp = torch.zeros(pages, nkv, 64, D, dtype=dtype, device="cuda")
         vp = torch.zeros(pages, nkv, 64, D, dtype=dtype, device="cuda")
-        ops.attention_inputs(src, q, kp, vp, qn, kn, 1e-5, rope.cos_sin, pos, smap, nq, nkv, D, 64)
+        ops.attention_inputs(src, q, kp, vp, qn, kn, 1e-5, rotation, pos, smap, nq, nkv, D, 64)
         outs.append((q, kp, vp))
     for a, b in zip(*outs):
         assert torch.equal(a, b)
@@ -169,10 +179,8 @@ def test_attention_inputs_and_plain_attention(ops, dtype, nq, nkv, D, page):
                                               "low_freq_factor": 1.0, "high_freq_factor": 4.0}})
     lens = [150, 77]
     qn, kn = rnd(1 + 0.2 * torch.randn(D), dtype), rnd(1 + 0.2 * torch.randn(D), dtype)
-    from tileinfer_b200.config.spec import Llama3RopeScaling, PositionSpec
-    from tileinfer_b200.parts import Runtime
-    from tileinfer_b200.parts.rope import RotaryEmbedding
-    rope = RotaryEmbedding(PositionSpec("rope", D, 10000.0, Llama3RopeScaling(8.0, 1.0, 4.0, 64), 4096), Runtime(dtype), 256)
+    rotation = plain_rotation(D, 10000.0, {"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 64,
+                                           "low_freq_factor": 1.0, "high_freq_factor": 4.0}, 256, dtype)
     qkvs = [rnd(torch.randn(L, (nq + 2 * nkv) * D), dtype) for L in lens]
     n_pages = sum(-(-L // page) for L in lens) + 3
     kp = torch.full((n_pages, nkv, page, D), 3.0, dtype=dtype, device="cuda")
@@ -199,7 +207,7 @@ def test_attention_inputs_and_plain_attention(ops, dtype, nq, nkv, D, page):
         smap = torch.tensor([tables[s][p // page] * page + p % page for s, a, b in entries for p in range(a, b)]).int()
         n = toks.shape[0]
         q_out = torch.empty(n, nq, D, dtype=dtype, device="cuda")
-        ops.attention_inputs(dev(toks, dtype), q_out, kp, vp, dev(qn, dtype), dev(kn, dtype), 1e-5, rope.cos_sin,
+        ops.attention_inputs(dev(toks, dtype), q_out, kp, vp, dev(qn, dtype), dev(kn, dtype), 1e-5, rotation,
                              pos.cuda(), smap.cuda(), nq, nkv, D, page)
         out = torch.empty(n, nq * D, dtype=dtype, device="cuda")
         ops.attention_plain(out, q_out, kp, vp, table, slot.cuda(), pos.cuda(), 1 / math.sqrt(D), nq, nkv, D, page)
@@ -210,6 +218,48 @@ def test_attention_inputs_and_plain_attention(ops, dtype, nq, nkv, D, page):
     close(o1, want_out[0][:100], dtype, **tol)
     close(o2[:50], want_out[0][100:], dtype, **tol)
     close(o2[50:], want_out[1], dtype, **tol)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D,rotary,interleaved", [(64, 64, True), (64, 32, False), (128, 32, True), (48, 20, True), (32, 32, False)])
+def test_attention_inputs_with_a_partial_or_interleaved_rotation(ops, dtype, D, rotary, interleaved):
+    """The rotation may cover only the first `rotary` elements of a head and may pair element 2i with 2i + 1
+    instead of i with i + rotary/2; written out here with the reference's rounding (each product and the
+    sum: src/ops/reference.jl:32-39) and compared exactly."""
+    torch.manual_seed(13)
+    nq, nkv, n = 3, 2, 45
+    rotation = plain_rotation(D, 50000.0, None, 300, dtype, rotary=rotary, interleaved=interleaved)
+    qkv = rnd(torch.randn(n, (nq + 2 * nkv) * D), dtype)
+    qn, kn = rnd(1 + 0.2 * torch.randn(D), dtype), rnd(1 + 0.2 * torch.randn(D), dtype)
+    pos = torch.randint(0, 300, (n,))
+    smap = torch.randperm(128)[:n].int()
+    q_out = torch.zeros(n, nq, D, dtype=dtype, device="cuda")
+    kp = torch.zeros(2, nkv, 64, D, dtype=dtype, device="cuda")
+    vp = torch.zeros(2, nkv, 64, D, dtype=dtype, device="cuda")
+    ops.attention_inputs(dev(qkv, dtype), q_out, kp, vp, dev(qn, dtype), dev(kn, dtype), 1e-5, rotation, pos.int().cuda(),
+                         smap.cuda(), nq, nkv, D, 64)
+    table = rotation.cos_sin.cpu()[pos]                                  # [n, rotary/2, 2]
+    cos, sin = table[..., 0], table[..., 1]
+
+    def rotate(x):                                                       # x [n, heads, D], already normed
+        y = x.clone()
+        half = rotary // 2
+        for i in range(half):
+            a, b = (2 * i, 2 * i + 1) if interleaved else (i, i + half)
+            c, s_ = cos[:, i, None], sin[:, i, None]
+            y[..., a] = rnd(rnd(x[..., a] * c, dtype) + rnd(-x[..., b] * s_, dtype), dtype)
+            y[..., b] = rnd(rnd(x[..., b] * c, dtype) + rnd(x[..., a] * s_, dtype), dtype)
+        return y
+
+    q = qkv[:, :nq * D].view(n, nq, D); k = qkv[:, nq * D:(nq + nkv) * D].view(n, nkv, D); v = qkv[:, (nq + nkv) * D:].view(n, nkv, D)
+    want_q = rotate(plain.rmsnorm(q, qn, 1e-5, dtype))
+    want_k = rotate(plain.rmsnorm(k, kn, 1e-5, dtype))
+    lim = dict(ulps=1.0) if dtype == torch.bfloat16 else dict(ulps=16.0)
+    close(q_out, want_q, dtype, **lim)
+    got_k = kp.view(-1, nkv, 64, D).permute(0, 2, 1, 3).reshape(128, nkv, D)[smap.long()]
+    got_v = vp.view(-1, nkv, 64, D).permute(0, 2, 1, 3).reshape(128, nkv, D)[smap.long()]
+    close(got_k, want_k, dtype, **lim)
+    assert torch.equal(got_v.float().cpu(), v)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -136,6 +136,52 @@ def test_attention_part_whole_then_continued(dtype, qk_norm):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_part_with_another_rotation(dtype):
+    """The attention mixer asks its position encoding for a rotation and knows nothing else about it: here
+    the rope part with interleaved pairs over half of each head (options of its record), a prompt and
+    then single tokens, against the plain functions with that rotation written out."""
+    from tileinfer_b200.config import MixerSpec, PositionSpec
+    from tileinfer_b200.parts import Runtime, lookup
+    torch.manual_seed(6)
+    H, nq, nkv, D, rotary = 72, 4, 2, 64, 32
+    rt = Runtime(dtype)
+    pos_spec = PositionSpec("rope", D, 50000.0, None, 4096, {"rotary_dim": rotary, "pairing": "interleaved"})
+    names = {"q": "q.w", "k": "k.w", "v": "v.w", "o": "o.w", "q_norm": "qn.w", "k_norm": "kn.w"}
+    spec = MixerSpec("attention", "a.", H, nq, nkv, D, True, 1e-6, 1 / math.sqrt(D), None, None, pos_spec, names)
+    cls = lookup("mixer", "attention")
+    W = {d.name: rnd(torch.randn(d.shape) * (0.1 if len(d.shape) == 2 else 0.2) + (0 if len(d.shape) == 2 else 1), dtype)
+         for d in cls.tensors(spec)}
+    position = lookup("position", "rope")(pos_spec, rt, 256)
+    rotation = position.rotation()
+    assert rotation.rotary_dim == rotary and rotation.interleaved and rotation.cos_sin.shape == (256, rotary // 2, 2)
+    mixer = cls(spec, {k: v.to(dtype) for k, v in W.items()}, rt, position)
+    cfg = plain.read_config({"vocab_size": 1, "hidden_size": H, "intermediate_size": 1, "num_hidden_layers": 1,
+                             "num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": rotary, "rms_norm_eps": 1e-6,
+                             "rope_theta": 50000.0, "max_position_embeddings": 4096})
+    n = 90
+    h = rnd(torch.randn(n, H), dtype)
+    cos, sin = plain.rope_tables(cfg, torch.arange(n), dtype)             # frequencies over the rotated width
+
+    def rotate(x):
+        y = x.clone()
+        for i in range(rotary // 2):
+            a, b, c, s_ = 2 * i, 2 * i + 1, cos[:, i, None], sin[:, i, None]
+            y[..., a] = rnd(rnd(x[..., a] * c, dtype) + rnd(-x[..., b] * s_, dtype), dtype)
+            y[..., b] = rnd(rnd(x[..., b] * c, dtype) + rnd(x[..., a] * s_, dtype), dtype)
+        return y
+
+    q = plain.linear(h, W["a.q.w"], dtype).view(n, nq, D)
+    k = plain.linear(h, W["a.k.w"], dtype).view(n, nkv, D)
+    v = plain.linear(h, W["a.v.w"], dtype).view(n, nkv, D)
+    q, k = rotate(plain.rmsnorm(q, W["a.qn.w"], 1e-6, dtype)), rotate(plain.rmsnorm(k, W["a.kn.w"], 1e-6, dtype))
+    ref = plain.linear(plain.attention(q, k, v, 1 / math.sqrt(D), dtype).reshape(n, nq * D), W["a.o.w"], dtype)
+    env = OneStep(mixer, dtype)
+    a = env.cache.alloc_slot()
+    got = [env.run(mixer, [(a, h[:70].to(dtype))], H)] + [env.run(mixer, [(a, h[t:t + 1].to(dtype))], H) for t in range(70, n)]
+    assert float((torch.cat(got) - ref).abs().max()) <= tol(dtype, ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n", [1, 7, 150])
 def test_feed_forward_part(dtype, n):
     from tileinfer_b200.config import FeedForwardSpec

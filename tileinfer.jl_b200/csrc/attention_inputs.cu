@@ -5,7 +5,9 @@
 // untouched (src/ops/interface.jl:161-177, src/ops/tile/fused.jl:20-33, 61-66); the rotation
 // pairs element i with i + D/2 and rounds each product and the sum
 // (src/ops/reference.jl:32-39); slot (page, offset) of the pool [pages][kv_heads][P][D]
-// (src/kv/paged_cache.jl:1-4).
+// (src/kv/paged_cache.jl:1-4). Beyond what the reference has, the rotation may cover only the first
+// `rotary` elements of a head (the rest pass through) and may pair element 2i with 2i + 1 instead
+// (`interleaved`); the table holds (cos, sin) of rotary / 2 pairs per position.
 #include "common.cuh"
 
 #include <type_traits>
@@ -18,9 +20,9 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, cons
                                         long long partial_stride, T* __restrict__ q_out,
                                         T* __restrict__ k_cache, T* __restrict__ v_cache,
                                         const T* __restrict__ q_norm_w, const T* __restrict__ k_norm_w, float eps,
-                                        const float* __restrict__ cos_sin, const int* positions,
-                                        const int* slots, int nq, int nkv, int D, int page_size,
-                                        int write_kv) {
+                                        const float* __restrict__ cos_sin, int rotary, int interleaved,
+                                        const int* positions, const int* slots, int nq, int nkv, int D,
+                                        int page_size, int write_kv) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -78,12 +80,23 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, cons
         for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(buf[d]);
         return;
     }
-    const int half = D >> 1;
-    const float* cs = cos_sin + (size_t)pos_t * D;     // [half][2] = (cos, sin)
+    const int half = rotary >> 1;
+    const float* cs = cos_sin + (size_t)pos_t * rotary;     // [half][2] = (cos, sin)
     for (int d = lane; d < D; d += 32) {
-        const int i = d < half ? d : d - half;
+        if (d >= rotary) {                                   // beyond the rotated part: unchanged
+            dst[d] = from_f32<T>(buf[d]);
+            continue;
+        }
+        int i;
+        float rot;
+        if (interleaved) {
+            i = d >> 1;
+            rot = (d & 1) ? buf[d - 1] : -buf[d + 1];
+        } else {
+            i = d < half ? d : d - half;
+            rot = d < half ? -buf[d + half] : buf[d - half];
+        }
         const float c = cs[2 * i], s = cs[2 * i + 1];
-        const float rot = d < half ? -buf[d + half] : buf[d - half];
         dst[d] = from_f32<T>(rnd<T>(buf[d] * c) + rnd<T>(rot * s));
     }
 }
@@ -216,16 +229,20 @@ __global__ void attention_inputs_vec_kernel(const bf16* qkv, long long qkv_strid
 extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, const float* partials, int n_partials,
                                    long long partial_stride, void* q_out, void* k_cache, void* v_cache,
                                    const void* q_norm_w, const void* k_norm_w, float eps, const float* cos_sin,
-                                   const int* positions, const int* slots, int n_tokens, int nq, int nkv, int D,
-                                   int page_size, int write_kv, int dtype, cudaStream_t stream) {
+                                   int rotary, int interleaved, const int* positions, const int* slots, int n_tokens,
+                                   int nq, int nkv, int D, int page_size, int write_kv, int dtype, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     TI_REQUIRE(D > 0 && D % 2 == 0 && D <= AI_MAX_D, "attention_inputs: head_dim %d must be even and at most %d", D, AI_MAX_D);
     TI_REQUIRE((qkv != nullptr) != (partials != nullptr), "attention_inputs: give the projection's output or its partial sums");
     TI_REQUIRE(nq > 0 && nkv > 0 && page_size > 0, "attention_inputs: bad sizes nq=%d nkv=%d page=%d", nq, nkv, page_size);
+    TI_REQUIRE(cos_sin == nullptr || (rotary >= 2 && rotary % 2 == 0 && rotary <= D),
+               "attention_inputs: a rotation over %d of %d elements (it must be even, from 2 to the head size)", rotary, D);
     const int heads_total = nq + (write_kv ? 2 * nkv : 0);
     dim3 grid(n_tokens, (heads_total + AI_WARPS - 1) / AI_WARPS);
     const size_t smem = (size_t)AI_WARPS * D * sizeof(float);
-    if (dtype == TI_BF16 && (D == 64 || D == 128) && qkv_stride % 4 == 0 && aligned16(q_out) &&
+    // The vector kernel rotates the whole head with rotate-half pairing (the partner sits 16 lanes away).
+    const bool plain_rotation = cos_sin == nullptr || (rotary == D && !interleaved);
+    if (dtype == TI_BF16 && plain_rotation && (D == 64 || D == 128) && qkv_stride % 4 == 0 && aligned16(q_out) &&
         (qkv != nullptr ? aligned16(qkv) : (aligned16(partials) && partial_stride % 4 == 0)) &&
         (!write_kv || (aligned16(k_cache) && aligned16(v_cache))) && (q_norm_w == nullptr || aligned16(q_norm_w)) &&
         (k_norm_w == nullptr || aligned16(k_norm_w)) && (cos_sin == nullptr || aligned16(cos_sin))) {
@@ -245,6 +262,6 @@ extern "C" int ti_attention_inputs(const void* qkv, long long qkv_stride, const 
     }
     TI_DISPATCH_DTYPE(dtype, (ti_launch(attention_inputs_kernel<T>, dim3(grid), dim3(AI_WARPS * 32), smem, stream, 
                                  (const T*)qkv, qkv_stride, partials, n_partials, partial_stride, (T*)q_out, (T*)k_cache, (T*)v_cache, (const T*)q_norm_w,
-                                 (const T*)k_norm_w, eps, cos_sin, positions, slots, nq, nkv, D, page_size, write_kv)));
+                                 (const T*)k_norm_w, eps, cos_sin, rotary, interleaved, positions, slots, nq, nkv, D, page_size, write_kv)));
     return ti_check_launch("attention_inputs");
 }

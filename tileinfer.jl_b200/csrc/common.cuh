@@ -18,6 +18,7 @@ typedef __nv_bfloat16 bf16;
 extern "C" const char* ti_last_error();
 int ti_fail(const char* fmt, ...);
 int ti_check_launch(const char* what);
+extern "C" int ti_sm_count();
 
 // Programmatic dependent launch. Every kernel of a step lets its successor start launching at
 // once (`pdl_launch_dependents`) and waits for its predecessor's results only where it first

@@ -23,6 +23,22 @@ int ti_pdl_enabled = 1;
 // Switch programmatic dependent launch on or off for every later launch (default on).
 extern "C" void ti_set_pdl(int enabled) { ti_pdl_enabled = enabled ? 1 : 0; }
 
+// Streaming multiprocessors of the current device, read once; 148 (a B200) where no device answers, so
+// that the host-side plans can be computed and tested without one.
+extern "C" int ti_sm_count() {
+    static int count = 0;
+    if (!count) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            count = n;
+        else {
+            cudaGetLastError();
+            count = 148;
+        }
+    }
+    return count;
+}
+
 int ti_check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return ti_fail("%s: %s", what, cudaGetErrorString(e));
@@ -115,11 +131,11 @@ extern "C" int ti_xielu(void* out, const void* in, long long count, float alpha_
         constexpr int N = Vec16<T>::N;
         if (count % N == 0 && aligned16(out) && aligned16(in)) {
             long long blocks = (count / N + 255) / 256;
-            if (blocks > 148 * 32) blocks = 148 * 32;
+            if (blocks > ti_sm_count() * 32) blocks = ti_sm_count() * 32;
             ti_launch(xielu_vec_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)out, (const T*)in, (size_t)(count / N), a);
         } else {
             long long blocks = (count + 255) / 256;
-            if (blocks > 148 * 16) blocks = 148 * 16;
+            if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
             ti_launch(xielu_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)out, (const T*)in, (size_t)count, a);
         }
     });
@@ -361,7 +377,7 @@ __global__ void add_kernel(T* x, const T* delta, size_t count) {
 extern "C" int ti_add(void* x, const void* delta, long long count, int dtype, cudaStream_t stream) {
     if (count == 0) return 0;
     long long blocks = (count + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > ti_sm_count() * 16) blocks = ti_sm_count() * 16;
     TI_DISPATCH_DTYPE(dtype, (ti_launch(add_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)x, (const T*)delta, (size_t)count)));
     return ti_check_launch("add");
 }

@@ -90,7 +90,7 @@ extern "C" int ti_random_normal(void* out, int dtype, long long count, long long
     TI_REQUIRE(count > 0 && first >= 0 && first + count <= (1ll << 32),
                "random_normal: elements %lld..%lld are outside the 32-bit counter", first, first + count);
     long long blocks = (count + 255) / 256;
-    if (blocks > 148 * 64) blocks = 148 * 64;
+    if (blocks > ti_sm_count() * 64) blocks = ti_sm_count() * 64;
     TI_DISPATCH_DTYPE(dtype, {
         ti_launch(random_normal_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (T*)out, (size_t)count, (unsigned)first, k0, k1,
                   mean, std);

@@ -97,12 +97,25 @@ class Engine:
     def sequence_length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def truncate(self, slot: int, length: int) -> None:
+        """Forget the positions of a sequence after its first ``length``: the next step continues from
+        there (the reference rolls a sequence back the same way, src/kv/block_manager.jl:74-81, to drop a
+        token that went through the model but is not kept). Pages beyond the new length go back to the
+        pool; nothing is cleared, the next tokens overwrite what was there. Layers with a per-sequence
+        state, or a window whose pages were already given back, cannot roll back and raise."""
+        self.cache.truncate(slot, length)
+
     # ---- the step
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Optional[Sequence[Sequence[int]]] = None,
              out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run ``entries`` = [(slot, next tokens)] as one batch; returns float32 logits
         ``[wanted, vocab]`` in the order of the entries and of ``want`` (offsets into each entry's
-        tokens; default: each entry's last token)."""
+        tokens, in any order; default: each entry's last token).
+
+        A step of one token per sequence that wants exactly those tokens' logits is replayed from a CUDA
+        graph and returns the graph's own output buffer, one per batch size: the next such step of the same
+        batch size overwrites it, so ``clone()`` what must outlive it (or pass ``out``, which is always
+        written by launches of its own). Every other step returns a fresh tensor."""
         entries = [(int(s), list(t)) for s, t in entries]
         if want is None:
             want = [[len(t) - 1] for _, t in entries]
@@ -136,33 +149,42 @@ class Engine:
             for s, t in entries:
                 self.cache.advance(s, len(t))
             return logits
-        row = 0
-        for chunk_entries, chunk_want in self._chunks(entries, want):
-            nw = sum(len(w) for w in chunk_want)
+        for chunk_entries, chunk_want, rows in self._chunks(entries, want):
+            nw = len(rows)
             self.cache.prepare([(s, len(t)) for s, t in chunk_entries])
             ctx = self.planner.plan(chunk_entries, chunk_want)
-            self.model.forward(ctx, self.cache, logits[row:row + nw] if nw else None)
+            if nw and rows == list(range(rows[0], rows[0] + nw)):
+                self.model.forward(ctx, self.cache, logits[rows[0]:rows[0] + nw])
+            elif nw:                                    # wanted places that are not in ascending order: through a buffer
+                part = torch.empty((nw, self.vocab_size), dtype=torch.float32, device=self.device)
+                self.model.forward(ctx, self.cache, part)
+                logits.index_copy_(0, torch.tensor(rows, dtype=torch.long, device=self.device), part)
+            else:
+                self.model.forward(ctx, self.cache, None)
             for s, t in chunk_entries:
                 self.cache.advance(s, len(t))
-            row += nw
         return logits
 
     def _chunks(self, entries, want):
-        """Cut a long step into steps of at most max_step_tokens, in token order."""
-        cur_e, cur_w, room = [], [], self.max_step_tokens
+        """Cut a long step into steps of at most max_step_tokens, in token order. Yields the chunk's entries,
+        their wanted offsets, and the rows of the step's result that those are."""
+        cur_e, cur_w, cur_rows, room = [], [], [], self.max_step_tokens
+        base = 0
         for (slot, toks), w in zip(entries, want):
             a = 0
             while a < len(toks):
                 take = min(room, len(toks) - a)
                 cur_e.append((slot, toks[a:a + take]))
                 cur_w.append([x - a for x in w if a <= x < a + take])
+                cur_rows += [base + k for k, x in enumerate(w) if a <= x < a + take]
                 a += take
                 room -= take
                 if room == 0:
-                    yield cur_e, cur_w
-                    cur_e, cur_w, room = [], [], self.max_step_tokens
+                    yield cur_e, cur_w, cur_rows
+                    cur_e, cur_w, cur_rows, room = [], [], [], self.max_step_tokens
+            base += len(w)
         if cur_e:
-            yield cur_e, cur_w
+            yield cur_e, cur_w, cur_rows
 
     def _decode_step(self, entries, want):
         return self.decode([s for s, _ in entries], [t[0] for _, t in entries], reserved=True)

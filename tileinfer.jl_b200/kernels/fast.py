@@ -11,7 +11,16 @@ from . import ops
 from .library import KernelError, add_launches, check, lib
 
 GEMV_MAX_TOKENS = 8          # from 9 tokens on the tensor-core product is faster (measured per layer: 151 against 162 us at 12 tokens)
-SM_COUNT = 148
+_sm_count = 0
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the device, asked once (148, a B200, where no device answers: the
+    plans below can be computed and tested without one)."""
+    global _sm_count
+    if not _sm_count:
+        _sm_count = int(_library.declare("ti_sm_count", [])())
+    return _sm_count
 
 
 def _stream() -> int:
@@ -24,9 +33,9 @@ def gemv_splits(out_features: int, in_features: int) -> int:
     per SM or more, unsplit is fastest: the down projection of 8 tokens streams at 5.7 TB/s unsplit, 5.4
     in three slices, and its consumer then reads one rounded result instead of three partial sums.)"""
     row_blocks = -(-out_features // 16)
-    if row_blocks >= SM_COUNT:
+    if row_blocks >= sm_count():
         return 1
-    return max(1, min(8, (2 * SM_COUNT) // row_blocks, in_features // 1024))
+    return max(1, min(8, (2 * sm_count()) // row_blocks, in_features // 1024))
 
 
 def linear(lin, x, out, epilogue, act, allow_partials=False):
@@ -77,7 +86,7 @@ def tc_splits(out_features: int, in_features: int, n: int) -> int:
     most 8, each at least 512 of k. Measured at 64 tokens: down projection 46 us in 3 slices, 35 us in 8;
     o 17 us in 2, 11 us in 8."""
     tiles = -(-out_features // 128) * -(-n // (256 if n > 128 else 128 if n > 64 else 64 if n > 32 else 32))
-    slots = SM_COUNT * (2 if n <= 64 else 1)
+    slots = sm_count() * (2 if n <= 64 else 1)
     if n > 256 or tiles >= slots:
         return 1
     return max(1, min(8, slots // tiles, (in_features // 64) // 8))
@@ -104,7 +113,7 @@ def decode_product_plan(n: int, out_features: int, in_features: int, max_splits:
     if plan is None:
         import ctypes
         nt, splits = ctypes.c_int(), ctypes.c_int()
-        check(lib().ti_gemm_tcgen05_decode_plan(n, out_features, in_features, max_splits, SM_COUNT, ctypes.byref(nt),
+        check(lib().ti_gemm_tcgen05_decode_plan(n, out_features, in_features, max_splits, sm_count(), ctypes.byref(nt),
                                                 ctypes.byref(splits)), "gemm_tcgen05_decode_plan")
         plan = _plans[key] = (nt.value, splits.value)
     return plan
@@ -158,8 +167,8 @@ def decode_splits(batch: int, kv_heads: int, max_context: int) -> int:
     """Split count of decode attention: fixed by the batch size alone, so that a captured step
     stays valid whatever the lengths are (the reference fixes it per model:
     src/ops/tile/attention.jl:250-263)."""
-    # Two blocks fit an SM: at most 2 x 148 blocks, so that none has to wait for a second wave.
-    want = (2 * SM_COUNT) // max(1, batch * kv_heads)
+    # Two blocks fit an SM: at most two blocks per SM, so that none has to wait for a second wave.
+    want = (2 * sm_count()) // max(1, batch * kv_heads)
     return max(1, min(want, 32, -(-max_context // 64)))
 
 
@@ -169,7 +178,7 @@ def attention(out, q, cache, meta, step, spec) -> bool:
     if step.is_decode:
         B = step.n_seqs
         # The step's plan may carry the split count and how the work slots are shared out among the sequences.
-        splits = meta.decode_splits or decode_splits(B, spec.num_kv_heads, cache.k.shape[0] * 64)
+        splits = meta.decode_splits or decode_splits(B, spec.num_kv_heads, cache.k.shape[0] * cache.page_size)
         shared = meta.split_work is not None and splits > 1
         rt_buffer = step.runtime.buffer
         ws_o = rt_buffer("attention.ws_o", (B * splits, spec.num_heads, spec.head_dim), torch.float32)

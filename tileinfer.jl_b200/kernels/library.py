@@ -77,7 +77,7 @@ _SIGNATURES = {
     "ti_rmsnorm": [_P, _P, _P, _I, _I, _F, _I, _P],
     "ti_add_rmsnorm": [_P, _P, _P, _I, _L, _P, _P, _I, _I, _F, _I, _P],
     "ti_add": [_P, _P, _L, _I, _P],
-    "ti_attention_inputs": [_P, _L, _P, _I, _L, _P, _P, _P, _P, _P, _F, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ti_attention_inputs": [_P, _L, _P, _I, _L, _P, _P, _P, _P, _P, _F, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_attention_plain": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _I, _I, _I, _I, _I, _I, _I, _P],
     "ti_gemm_plain": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P],
     "ti_argmax": [_P, _L, _I, _I, _P, _P, _P, _P, _P],

@@ -96,10 +96,16 @@ def add(x, delta):
     check(lib().ti_add(x.data_ptr(), delta.data_ptr(), x.numel(), dtype_code(x.dtype), _stream()), "add")
 
 
-def attention_inputs(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, cos_sin, positions, slots,
+def attention_inputs(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, rotation, positions, slots,
                      nq, nkv, head_dim, page_size, write_kv=True):
     """qkv [n, (nq + 2 nkv) D] -> q_out [n, nq, D]; k and v rows into the pools at ``slots``. ``qkv`` may
-    also be the 32-bit partial sums [s, n, features] of a projection that was split over k."""
+    also be the 32-bit partial sums [s, n, features] of a projection that was split over k. ``rotation``:
+    None, or a record with ``cos_sin`` [positions, rotary_dim / 2, 2] float32, ``rotary_dim`` and
+    ``interleaved`` (see ``parts.base.Rotation``)."""
+    cos_sin = rotation.cos_sin if rotation is not None else None
+    rotary, interleaved = (int(rotation.rotary_dim), int(bool(rotation.interleaved))) if rotation is not None else (0, 0)
+    if rotation is not None and (rotary < 2 or rotary % 2 or rotary > head_dim or cos_sin.shape[1] * 2 != rotary):
+        raise KernelError(f"rotation over {rotary} of {head_dim} elements with a table of {tuple(cos_sin.shape)}")
     _need(qkv, "qkv", contiguous=False); _need(q_out, "q_out")
     _need(positions, "positions", torch.int32)
     if qkv.stride(-1) != 1:

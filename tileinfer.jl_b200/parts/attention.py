@@ -29,6 +29,8 @@ class Attention(Mixer):
         else:
             self.qkv = Linear(wq, rt, "q")           # this layer reads another layer's keys and values
         self.o = Linear(rt.param(tensors[p + n["o"]]), rt, "o")
+        # The position encoding's rotation, if it has one: the mixer knows nothing else about it.
+        self.rotation = position.rotation() if position is not None else None
         self.q_norm = rt.param(tensors[p + n["q_norm"]]) if spec.qk_norm else None
         self.k_norm = rt.param(tensors[p + n["k_norm"]]) if spec.qk_norm else None
 
@@ -63,7 +65,7 @@ class Attention(Mixer):
         q = rt.buffer("attention.q", (n, nq, D))
         meta = step.group(cache.group_index)
         ops.attention_inputs(qkv, q, cache.k, cache.v, self.q_norm, self.k_norm, s.qk_norm_eps,
-                             self.position.cos_sin, step.positions, meta.slot_mapping, nq, nkv, D,
+                             self.rotation, step.positions, meta.slot_mapping, nq, nkv, D,
                              cache.page_size, write_kv=own_kv)
         attn = rt.buffer("attention.out", (n, nq * D))
         done = False

@@ -10,7 +10,10 @@ Interfaces (duck-typed; the base classes document them):
 
 * ``Norm(spec, tensors, rt)``: ``forward(x, out)``; ``add_forward(x, delta, out)`` does
   ``x += delta`` then ``out = norm(x)`` in one kernel (``delta`` may be 32-bit partial sums [s, n, size]).
-* ``PositionEncoding(spec, rt, max_positions)``: owns whatever table its kernels read.
+* ``PositionEncoding(spec, rt, max_positions)``: ``rotation()`` returns the :class:`Rotation` that the
+  attention mixer applies to queries and keys (a table of cos/sin per position and pair, how many
+  elements of a head it covers, and which elements are paired), or None for an encoding that rotates
+  nothing; an encoding of another kind offers methods of its own to the mixers written for it.
 * ``Mixer(spec, tensors, rt, position)``: ``cache_request()`` says what per-sequence storage a
   layer of this kind needs; ``forward(h, step, cache) -> delta`` mixes tokens of the same
   sequence, reading and writing ``cache`` (the layer's view of its cache group).
@@ -64,8 +67,26 @@ class Norm(Part):
         raise NotImplementedError
 
 
+@dataclass(frozen=True)
+class Rotation:
+    """A rotation of pairs of a head's elements by angles that depend on the position, as the
+    attention-inputs kernel applies it to queries and keys after their norm.
+
+    ``cos_sin``: float32 ``[max_positions, rotary_dim / 2, 2]`` holding (cos, sin) of every (position,
+    pair), already rounded to the model's element type. ``rotary_dim`` (even, at most the head size): the
+    first so many elements of a head are rotated, the rest pass through. ``interleaved`` False: element i
+    pairs with i + rotary_dim / 2 (rotate-half, what Apertus uses: AntoineBut/TileInfer.jl
+    src/ops/interface.jl:46-52); True: element 2i pairs with 2i + 1.
+    """
+    cos_sin: torch.Tensor
+    rotary_dim: int
+    interleaved: bool = False
+
+
 class PositionEncoding(Part):
-    pass
+    def rotation(self) -> Optional[Rotation]:
+        """What an attention mixer applies to q and k; None: nothing."""
+        return None
 
 
 class Mixer(Part):

@@ -4,8 +4,12 @@ Tables are computed once on the host the way AntoineBut/TileInfer.jl does
 (src/model/rope.jl:15-48): inverse frequencies and angles in 32-bit, cos/sin in 64-bit of
 the 32-bit angle, rounded to 32-bit and then to the model's element type. The scaling is
 static: it does not depend on the running sequence length. The device table is
-``[max_positions, head_dim/2, 2]`` float32 holding (cos, sin) already rounded to the
-element type; both halves of a head share the angles.
+``[max_positions, rotary_dim/2, 2]`` float32 holding (cos, sin) already rounded to the
+element type; both elements of a pair share the angle.
+
+Two options of the record go beyond what Apertus uses: ``rotary_dim`` (rotate only the first so
+many elements of a head; default: all) and ``pairing`` ("half": element i with i + rotary_dim/2,
+the default; "interleaved": 2i with 2i + 1).
 """
 from __future__ import annotations
 
@@ -14,11 +18,18 @@ import math
 import torch
 
 from ..config.spec import PositionSpec
-from .base import PositionEncoding, register_position
+from .base import PositionEncoding, Rotation, register_position
+
+
+def rotary_dim(spec: PositionSpec) -> int:
+    D = int(spec.options.get("rotary_dim", spec.head_dim))
+    if D < 2 or D % 2 or D > spec.head_dim:
+        raise ValueError(f"rotary_dim {D} must be even and between 2 and the head size {spec.head_dim}")
+    return D
 
 
 def inverse_frequencies(spec: PositionSpec) -> torch.Tensor:
-    D = spec.head_dim
+    D = rotary_dim(spec)
     theta = torch.tensor(float(spec.theta), dtype=torch.float32)
     inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float32) / torch.tensor(float(D), dtype=torch.float32)))
     s = spec.scaling
@@ -39,7 +50,12 @@ class RotaryEmbedding(PositionEncoding):
         self.spec = spec
         self.max_positions = int(min(max_positions, spec.max_positions) if spec.max_positions else max_positions)
         inv = inverse_frequencies(spec)
-        table = torch.empty(self.max_positions, spec.head_dim // 2, 2, dtype=torch.float32)
+        self.rotary_dim = rotary_dim(spec)
+        pairing = spec.options.get("pairing", "half")
+        if pairing not in ("half", "interleaved"):
+            raise ValueError(f"rope pairing must be \"half\" or \"interleaved\", not {pairing!r}")
+        self.interleaved = pairing == "interleaved"
+        table = torch.empty(self.max_positions, self.rotary_dim // 2, 2, dtype=torch.float32)
         # In blocks, to bound the 64-bit scratch for long contexts.
         for p0 in range(0, self.max_positions, 1 << 15):
             p1 = min(self.max_positions, p0 + (1 << 15))
@@ -50,10 +66,12 @@ class RotaryEmbedding(PositionEncoding):
             table = table.to(rt.dtype).float()
         self.cos_sin = table.contiguous().to(rt.device)
 
+    def rotation(self) -> Rotation:
+        return Rotation(self.cos_sin, self.rotary_dim, self.interleaved)
+
 
 @register_position("none")
 class NoPosition(PositionEncoding):
     def __init__(self, spec, rt, max_positions):
         self.spec = spec
         self.max_positions = max_positions
-        self.cos_sin = None
