@@ -7,30 +7,38 @@ import os
 import pytest
 
 import helpers
-from tileinfer_b200.cli import ArgumentError, TimedStream, check_options, cli, parse_args, parse_ids, parse_option
+from tileinfer_b200.cli import COMMANDS, OPTIONS, ArgumentError, GenerationStats, cli, token_ids, usage
 
 
 def test_options_and_positionals():
-    pos, opt = parse_args(["model", "1 2 3", "--max-tokens", "7", "--temperature", "0.5"])
-    assert pos == ["model", "1 2 3"] and opt == {"max-tokens": "7", "temperature": "0.5"}
-    pos, opt = parse_args(["--raw", "m", "--seed", "3"], flags=("raw",))
-    assert pos == ["m"] and opt == {"raw": "true", "seed": "3"}
-    with pytest.raises(ArgumentError, match="needs a value"):
-        parse_args(["m", "--seed"])
-    check_options({"seed": "1"}, ("seed", "dtype"))
+    run = COMMANDS["run"]
+    pos, values = run.read(["model", "1 2 3", "--max-tokens", "7", "--temperature", "0.5"])
+    assert pos == ["model", "1 2 3"] and values["max-tokens"] == 7 and values["temperature"] == 0.5
+    assert values["max-context"] == 4096 and values["backend"] == "fast" and values["seed"] is None      # defaults
+    pos, values = run.read(["--seed", "3", "m", "4,5", "--stop-ids", ""])
+    assert pos == ["m", "4,5"] and values["seed"] == 3 and values["stop-ids"] == []
+    with pytest.raises(ArgumentError, match="option --seed needs a value"):
+        run.read(["m", "1", "--seed"])
     with pytest.raises(ArgumentError, match="unknown option --sed"):
-        check_options({"sed": "1"}, ("seed", "dtype"))
-    assert parse_option(int, {"seed": "12"}, "seed", 0) == 12 and parse_option(float, {}, "temperature", 0.25) == 0.25
+        run.read(["m", "1", "--sed", "1"])
+    with pytest.raises(ArgumentError, match="unknown option --max-tokens"):
+        COMMANDS["random"].read(["c.json", "out", "--max-tokens", "3"])
     with pytest.raises(ArgumentError, match="--seed expects an integer, got x"):
-        parse_option(int, {"seed": "x"}, "seed", 0)
+        run.read(["m", "1", "--seed", "x"])
     with pytest.raises(ArgumentError, match="--top-p expects a number"):
-        parse_option(float, {"top-p": "much"}, "top-p", 1.0)
+        run.read(["m", "1", "--top-p", "much"])
+    with pytest.raises(ArgumentError, match="run takes a model and a prompt"):
+        run.read(["m"])
+    # The reference's option names, where it has them (src/cli.jl:14-33).
+    assert {"max-tokens", "max-context", "temperature", "top-k", "top-p", "seed", "backend"} <= set(OPTIONS)
+    text = usage()
+    assert all(f"--{name}" in text for name in OPTIONS) and all(name in text for name in COMMANDS)
 
 
 def test_prompts_are_token_ids():
-    assert parse_ids("5 17 3") == [5, 17, 3] and parse_ids("5,17, 3") == [5, 17, 3] and parse_ids("") == []
+    assert token_ids("5 17 3") == [5, 17, 3] and token_ids("5,17, 3") == [5, 17, 3] and token_ids("") == []
     with pytest.raises(ArgumentError, match="token ids"):
-        parse_ids("hello world")
+        token_ids("hello world")
 
 
 def test_exit_codes_and_messages(capsys, tmp_path):
@@ -63,10 +71,10 @@ def test_random_writes_a_model_folder(tmp_path, capsys):
 
 
 def test_the_statistics_line_counts_from_the_second_token():
-    s = TimedStream()
+    s = GenerationStats()
     for t in range(5):
         s(0, t)
-    assert s.count == 5 and 0 < s.first <= s.second
+    assert s.count == 5 and len(s.arrivals) == 2 and s.started <= s.arrivals[0] <= s.arrivals[1]
     text = s.summary(5)
-    assert text.startswith("first token after ") and text.endswith(" tok/s")
-    assert "nan" in TimedStream().summary(1)                     # no rate from fewer than three tokens
+    assert text.startswith("first token after ") and text.endswith(" tok/s") and "nan" not in text
+    assert "nan" in GenerationStats().summary(1)                 # no rate from fewer than three tokens

@@ -111,9 +111,10 @@ def paged(k, v, page_size, n_pages_total, perm_seed, dtype):
         L = ks.shape[0]
         pages = [order.pop() for _ in range(-(-L // page_size))]
         tables.append(pages)
-        for p in range(L):
-            kp[pages[p // page_size], :, p % page_size] = ks[p]
-            vp[pages[p // page_size], :, p % page_size] = vs[p]
+        pad = len(pages) * page_size - L
+        for pool, src in ((kp, ks), (vp, vs)):
+            whole = torch.cat([src.float(), torch.full((pad, nkv, D), float("nan"))]) if pad else src.float()
+            pool[pages] = whole.view(len(pages), page_size, nkv, D).permute(0, 2, 1, 3)
     kp = torch.nan_to_num(kp, nan=7.0)              # unwritten places hold finite junk, as in a used pool
     vp = torch.nan_to_num(vp, nan=-5.0)
     width = max(len(t) for t in tables) + 2
@@ -543,16 +544,17 @@ def test_attention_window_edge(ops):
     close(out3[0], want[L - 1], dtype, ulps=5.0)
 
 
-def test_attention_decode_with_shared_out_slots(ops):
+@pytest.mark.parametrize("nq,nkv,D,splits,lengths", [(8, 2, 64, 6, [3, 1500, 64, 129, 700]),
+                                                     (32, 8, 128, 9, [5, 32768, 700, 20000])])    # Apertus-8B heads, long contexts
+def test_attention_decode_with_shared_out_slots(ops, nq, nkv, D, splits, lengths):
     """Decode attention over sequences of very unequal lengths with the work slots shared out by length
     (the long sequence read by many blocks, the short ones by one), against exact attention and against
-    the same launch with equal splits."""
+    the same launch with equal splits; up to 32,768 keys, where one sequence gets the most parts there are."""
     import numpy as np
     from tileinfer_b200.engine.step import split_tables
     from tileinfer_b200.kernels.library import check, lib
     torch.manual_seed(21)
-    dtype, nq, nkv, D, splits = torch.bfloat16, 8, 2, 64, 6
-    lengths = [3, 1500, 64, 129, 700]
+    dtype = torch.bfloat16
     B, g = len(lengths), nq // nkv
     ks = [rnd(torch.randn(L, nkv, D), dtype) for L in lengths]
     vs = [rnd(torch.randn(L, nkv, D), dtype) for L in lengths]
@@ -652,4 +654,31 @@ def test_gemm_tcgen05_decode(ops, n, out, k, tile, splits):
                                        status.data_ptr(), st), "tc decode")
     assert torch.equal(guard[:n, :out].float().cpu(), y.float().cpu())
     assert bool((guard[n:] == 7.0).all()) and bool((guard[:, out:] == 7.0).all())
+    fast.check_status()
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_goes_on(ops):
+    """The error path of the bounded waits: a barrier that nothing completes, waited on with a limit of
+    1,024 attempts. The kernel returns, the wait's bit is in the status word, check_status() raises and
+    clears it, and the next tensor-core product runs clean."""
+    from tileinfer_b200.kernels import fast
+    from tileinfer_b200.kernels.library import KernelError, check, lib
+    fast.check_status()
+    status = fast.status_word()
+    result = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    check(lib().ti_wait_probe(status.data_ptr(), 7, 1024, result.data_ptr(), st), "wait_probe")
+    torch.cuda.synchronize()
+    assert int(result.item()) == 2 and int(status.item()) == 1 << 7
+    with pytest.raises(KernelError, match=r"gave up waiting.*\[7\]"):
+        fast.check_status()
+    assert int(status.item()) == 0
+    torch.manual_seed(1)
+    x, w = rnd(torch.randn(40, 256), torch.bfloat16), rnd(torch.randn(128, 256) / 16, torch.bfloat16)
+    y = torch.empty(40, 128, dtype=torch.bfloat16, device="cuda")
+    xd, wd = dev(x, torch.bfloat16), dev(w, torch.bfloat16)
+    rc = lib().ti_gemm_tcgen05(y.data_ptr(), 128, xd.data_ptr(), 256, wd.data_ptr(), 40, 128, 256, 1, 0, 0.0, 0.0, 0.0, 0.0,
+                               status.data_ptr(), st)
+    assert rc == 0
+    close(y, rnd((x.double() @ w.double().t()).float(), torch.bfloat16), torch.bfloat16, ulps=1.0)
     fast.check_status()

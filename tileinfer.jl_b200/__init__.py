@@ -6,7 +6,7 @@ put together from parts (``parts``), a paged cache with a slot per sequence (``c
 step function and a generation loop (``engine``), sampling (``sampling``) and hand-written
 CUDA kernels (``csrc``, loaded by ``kernels``).
 """
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 from .api import generate, generation_defaults, load_model            # noqa: E402
 from .engine import Engine                                            # noqa: E402

@@ -1,7 +1,14 @@
-"""``tileinfer`` command line, in the manner of AntoineBut/TileInfer.jl's (src/cli.jl): commands
-with ``--name value`` options, unknown options refused, exit code 0 or 1, a statistics line on
-stderr. Prompts are token ids (the library has no tokenizer), so ``run`` takes the ids where the
-reference takes text. ``pull/ls/rm/chat`` have no counterpart: a model is a local folder.
+"""``tileinfer`` command line, in the manner of AntoineBut/TileInfer.jl's (src/cli.jl:4-34, 253-277):
+``tileinfer <command> <arguments> [--name value ...]``, unknown options refused, exit code 0 or 1, a
+statistics line on stderr whose decode rate counts from the second token (src/cli.jl:177-187). Its
+option names and meanings are kept where it has them (``--max-tokens``, ``--max-context``,
+``--temperature``, ``--top-k``, ``--top-p``, ``--seed``, ``--backend``). Prompts are token ids (the
+library has no tokenizer), so ``run`` takes ids where the reference takes text; ``pull/ls/rm/chat``
+have no counterpart: a model is a local folder.
+
+Everything the parser knows is in two tables: ``OPTIONS`` (name, type or choices, default, help)
+and ``COMMANDS`` (positional arguments, the options a command takes, its function). The usage text
+is printed from them.
 """
 from __future__ import annotations
 
@@ -9,200 +16,210 @@ import json
 import random
 import sys
 import time
-from typing import Dict, List, Sequence, Tuple
-
-USAGE = """usage: tileinfer <command> [arguments]
-
-commands:
-  run <model> <prompt> [options]       generate a continuation of `prompt`: token ids separated by
-                                       spaces or commas; <model> is a folder with config.json and
-                                       safetensors
-  generate <model> <file> [options]    the same for a batch: one prompt a line in <file>
-                                       ("-" reads standard input); prints one line of ids per prompt
-  random <config.json> <out> [--seed S] [--dtype D]
-                                       write a model folder with random weights for a configuration
-
-run and generate options:
-  --max-tokens N        tokens to generate per prompt at most (default 512)
-  --max-context N       longest sequence in tokens; sizes the KV cache (default 4096)
-  --temperature T       0 for greedy (defaults come from the model's generation_config.json)
-  --top-k K, --top-p P  sampling filters
-  --seed S              random seed
-  --backend fast|plain  tensor-core kernels (default) or the plain reference kernels
-  --dtype bfloat16|float32
-                        element type of weights, activations and cache (default bfloat16)
-  --max-seqs N          sequences per batch at most (default 8)
-  --stop-ids IDS        stop tokens instead of the configuration's EOS ids ("" for none)
-"""
-
-GENERATION_OPTIONS = ("max-tokens", "max-context", "temperature", "top-k", "top-p", "seed", "backend", "dtype",
-                      "max-seqs", "stop-ids")
-FLAGS: Tuple[str, ...] = ()
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 
 class ArgumentError(ValueError):
     pass
 
 
-def parse_args(args: Sequence[str], flags: Sequence[str] = FLAGS):
-    """Positionals and ``--name value`` options; names in ``flags`` take no value (src/cli.jl:40-58)."""
-    positional: List[str] = []
-    options: Dict[str, str] = {}
-    i = 0
-    while i < len(args):
-        a = args[i]
-        if a.startswith("--") and a[2:] in flags:
-            options[a[2:]] = "true"
-            i += 1
-        elif a.startswith("--"):
-            if i + 1 >= len(args):
-                raise ArgumentError(f"option {a} needs a value")
-            options[a[2:]] = args[i + 1]
-            i += 2
-        else:
-            positional.append(a)
-            i += 1
-    return positional, options
-
-
-def check_options(options, allowed):
-    for name in options:
-        if name not in allowed:
-            raise ArgumentError(f"unknown option --{name}")
-
-
-def parse_option(kind, options, name, default):
-    if name not in options:
-        return default
-    try:
-        return kind(options[name])
-    except ValueError:
-        raise ArgumentError(f"--{name} expects {'an integer' if kind is int else 'a number'}, got {options[name]}") from None
-
-
-def parse_ids(text: str) -> List[int]:
+def token_ids(text: str) -> List[int]:
+    """Token ids separated by spaces or commas."""
     try:
         return [int(t) for t in text.replace(",", " ").split()]
     except ValueError:
         raise ArgumentError(f"a prompt is a list of token ids, got \"{text}\"") from None
 
 
-def load_for_generation(model_dir: str, options):
-    from .api import generation_defaults, load_model
-    from .sampling import SamplingParams
-    backend = options.get("backend", "fast")
-    if backend not in ("fast", "plain"):
-        raise ArgumentError("--backend expects fast or plain")
-    dtype = options.get("dtype", "bfloat16")
-    if dtype not in ("bfloat16", "float32"):
-        raise ArgumentError("--dtype expects bfloat16 or float32")
-    max_seqs = parse_option(int, options, "max-seqs", 8)
-    engine = load_model(model_dir, dtype=dtype, backend=backend, max_seqs=max_seqs,
-                        max_context=parse_option(int, options, "max-context", 4096))
-    defaults, stop = generation_defaults(model_dir, engine)
-    sampling = SamplingParams(temperature=parse_option(float, options, "temperature", defaults.temperature),
-                              top_k=parse_option(int, options, "top-k", defaults.top_k),
-                              top_p=parse_option(float, options, "top-p", defaults.top_p))
-    if "stop-ids" in options:
-        stop = parse_ids(options["stop-ids"])
-    seed = parse_option(int, options, "seed", random.getrandbits(32))
-    return engine, sampling, stop, seed
+@dataclass(frozen=True)
+class Option:
+    name: str
+    kind: object                    # int, float, token_ids, or a tuple of allowed words
+    default: object                 # None: decided later (the model's generation defaults, a random seed)
+    help: str
+
+    def read(self, text: str):
+        if isinstance(self.kind, tuple):
+            if text not in self.kind:
+                raise ArgumentError(f"--{self.name} expects {' or '.join(self.kind)}")
+            return text
+        if self.kind is token_ids:
+            return token_ids(text)
+        try:
+            return self.kind(text)
+        except ValueError:
+            what = "an integer" if self.kind is int else "a number"
+            raise ArgumentError(f"--{self.name} expects {what}, got {text}") from None
+
+    def usage(self) -> str:
+        value = "|".join(self.kind) if isinstance(self.kind, tuple) else {int: "N", float: "X", token_ids: "IDS"}[self.kind]
+        default = f" (default {self.default})" if self.default is not None else ""
+        return f"  --{self.name} {value}".ljust(34) + self.help + default
 
 
-class TimedStream:
-    """Records when the first two tokens arrived (src/cli.jl:158-187): decode speed is measured
-    from the second token on, so that it excludes warm-up."""
+OPTIONS: Dict[str, Option] = {o.name: o for o in (
+    Option("max-tokens", int, 512, "tokens to generate per prompt at most"),
+    Option("max-context", int, 4096, "longest sequence in tokens; sizes the KV cache"),
+    Option("temperature", float, None, "0 for greedy (default: the model's generation_config.json, else 0)"),
+    Option("top-k", int, None, "keep the K most likely tokens (0: all)"),
+    Option("top-p", float, None, "keep the smallest set of tokens with this much probability (1: all)"),
+    Option("seed", int, None, "random seed (default: drawn at random)"),
+    Option("backend", ("fast", "plain"), "fast", "tensor-core kernels or the plain reference kernels"),
+    Option("dtype", ("bfloat16", "float32"), "bfloat16", "element type of weights, activations and cache"),
+    Option("max-seqs", int, 8, "sequences per batch at most"),
+    Option("stop-ids", token_ids, None, "stop tokens instead of the configuration's EOS ids (\"\" for none)"),
+)}
+GENERATION = ("max-tokens", "max-context", "temperature", "top-k", "top-p", "seed", "backend", "dtype", "max-seqs", "stop-ids")
+
+
+@dataclass(frozen=True)
+class Command:
+    name: str
+    positionals: Tuple[str, ...]
+    takes: str                      # "run takes a model and a prompt"
+    options: Tuple[str, ...]
+    help: str
+    run: Callable
+
+    def read(self, args: Sequence[str]):
+        """Positionals and typed option values of ``args``; options not given have their defaults."""
+        positional: List[str] = []
+        values = {name: OPTIONS[name].default for name in self.options}
+        words = iter(args)
+        for word in words:
+            if not word.startswith("--"):
+                positional.append(word)
+                continue
+            name = word[2:]
+            if name not in self.options:
+                raise ArgumentError(f"unknown option --{name}")
+            text = next(words, None)
+            if text is None:
+                raise ArgumentError(f"option --{name} needs a value")
+            values[name] = OPTIONS[name].read(text)
+        if len(positional) != len(self.positionals):
+            raise ArgumentError(self.takes)
+        return positional, values
+
+
+class GenerationStats:
+    """An ``on_token`` callback that notes when the first two tokens arrived: the decode rate is counted from
+    the second token on, so that it leaves out the prompt's step and warm-up (src/cli.jl:158-187)."""
 
     def __init__(self, out=None):
-        self.out, self.start, self.first, self.second, self.count = out, time.time(), 0.0, 0.0, 0
+        self.out, self.count = out, 0
+        self.started = time.time()
+        self.arrivals: List[float] = []             # of the first two tokens
 
     def __call__(self, request: int, token: int):
-        now = time.time()
-        if self.first == 0:
-            self.first = now
-        elif self.second == 0:
-            self.second = now
+        if len(self.arrivals) < 2:
+            self.arrivals.append(time.time())
         self.count += 1
         if self.out is not None:
             self.out.write(f"{token} ")
             self.out.flush()
 
     def summary(self, generated: int) -> str:
-        stop = time.time()
-        rate = (generated - 2) / (stop - self.second) if generated > 2 and stop > self.second else float("nan")
-        ttft = (self.first or stop) - self.start
-        return f"first token after {ttft:.2f} s, then {rate:.1f} tok/s"
+        now = time.time()
+        first = self.arrivals[0] if self.arrivals else now
+        rate = float("nan")
+        if generated > 2 and len(self.arrivals) == 2 and now > self.arrivals[1]:
+            rate = (generated - 2) / (now - self.arrivals[1])
+        return f"first token after {first - self.started:.2f} s, then {rate:.1f} tok/s"
 
 
-def cmd_run(positional, options) -> None:
-    check_options(options, GENERATION_OPTIONS)
-    if len(positional) != 2:
-        raise ArgumentError("run takes a model and a prompt")
+def load_for_generation(model_dir: str, values):
+    """The engine and the sampling settings of a ``run`` or ``generate`` call: options given on the command
+    line win over the model's generation_config.json."""
+    from .api import generation_defaults, load_model
+    from .sampling import SamplingParams
+    engine = load_model(model_dir, dtype=values["dtype"], backend=values["backend"], max_seqs=values["max-seqs"],
+                        max_context=values["max-context"])
+    defaults, stop = generation_defaults(model_dir, engine)
+    pick = lambda name, fallback: fallback if values[name] is None else values[name]
+    sampling = SamplingParams(temperature=pick("temperature", defaults.temperature), top_k=pick("top-k", defaults.top_k),
+                              top_p=pick("top-p", defaults.top_p))
+    return engine, sampling, pick("stop-ids", stop), pick("seed", random.getrandbits(32))
+
+
+def cmd_run(positional, values) -> None:
     from .api import generate
     model_dir, prompt = positional
-    ids = parse_ids(prompt)
+    ids = token_ids(prompt)
     if not ids:
         raise ArgumentError("the prompt has no token ids")
-    engine, sampling, stop, seed = load_for_generation(model_dir, options)
-    stream = TimedStream(sys.stdout)
-    out = generate(engine, ids, max_new_tokens=parse_option(int, options, "max-tokens", 512), sampling=sampling,
-                   stop_ids=stop, seed=seed, on_token=stream)
+    engine, sampling, stop, seed = load_for_generation(model_dir, values)
+    stats = GenerationStats(sys.stdout)
+    out = generate(engine, ids, max_new_tokens=values["max-tokens"], sampling=sampling, stop_ids=stop, seed=seed, on_token=stats)
     print(flush=True)
-    print(f"[{len(ids)} prompt tokens, {len(out)} generated; {stream.summary(len(out))}]", file=sys.stderr)
+    print(f"[{len(ids)} prompt tokens, {len(out)} generated; {stats.summary(len(out))}]", file=sys.stderr)
 
 
-def cmd_generate(positional, options) -> None:
-    check_options(options, GENERATION_OPTIONS)
-    if len(positional) != 2:
-        raise ArgumentError("generate takes a model and a file of prompts")
+def cmd_generate(positional, values) -> None:
     from .api import generate
     model_dir, path = positional
     lines = (sys.stdin if path == "-" else open(path)).read().splitlines()
-    prompts = [parse_ids(l) for l in lines if l.strip()]
+    prompts = [token_ids(l) for l in lines if l.strip()]
     if not prompts:
         raise ArgumentError("no prompts")
-    engine, sampling, stop, seed = load_for_generation(model_dir, options)
-    stream = TimedStream()
-    outs = generate(engine, prompts, max_new_tokens=parse_option(int, options, "max-tokens", 512), sampling=sampling,
-                    stop_ids=stop, seed=seed, on_token=stream)
+    engine, sampling, stop, seed = load_for_generation(model_dir, values)
+    stats = GenerationStats()
+    outs = generate(engine, prompts, max_new_tokens=values["max-tokens"], sampling=sampling, stop_ids=stop, seed=seed,
+                    on_token=stats)
     for o in outs:
         print(" ".join(str(t) for t in o))
     total = sum(len(o) for o in outs)
     print(f"[{sum(len(p) for p in prompts)} prompt tokens in {len(prompts)} prompts, {total} generated; "
-          f"{stream.summary(total)}]", file=sys.stderr)
+          f"{stats.summary(total)}]", file=sys.stderr)
 
 
-def cmd_random(positional, options) -> None:
-    check_options(options, ("seed", "dtype"))
-    if len(positional) != 2:
-        raise ArgumentError("random takes a config.json and an output folder")
+def cmd_random(positional, values) -> None:
     import torch
     from .config import config_from_dict
     from .weights import write_model_folder
     with open(positional[0]) as f:
         config = config_from_dict(json.load(f))
-    dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}.get(options.get("dtype", "bfloat16"))
-    if dtype is None:
-        raise ArgumentError("--dtype expects bfloat16 or float32")
-    print("wrote", write_model_folder(config, parse_option(int, options, "seed", 0), positional[1], dtype=dtype))
+    dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[values["dtype"]]
+    print("wrote", write_model_folder(config, values["seed"] or 0, positional[1], dtype=dtype))
 
 
-COMMANDS = {"run": cmd_run, "generate": cmd_generate, "random": cmd_random}
+COMMANDS: Dict[str, Command] = {c.name: c for c in (
+    Command("run", ("model", "prompt"), "run takes a model and a prompt", GENERATION,
+            "generate a continuation of <prompt>: token ids separated by spaces or commas; <model> is a folder with "
+            "config.json and safetensors", cmd_run),
+    Command("generate", ("model", "file"), "generate takes a model and a file of prompts", GENERATION,
+            "the same for a batch: one prompt a line in <file> (\"-\" reads standard input); prints one line of ids per prompt",
+            cmd_generate),
+    Command("random", ("config.json", "out"), "random takes a config.json and an output folder", ("seed", "dtype"),
+            "write a model folder with random weights for a configuration", cmd_random),
+)}
+
+
+def usage() -> str:
+    lines = ["usage: tileinfer <command> [arguments]", "", "commands:"]
+    for c in COMMANDS.values():
+        head = f"  {c.name} " + " ".join(f"<{p}>" for p in c.positionals) + " [options]"
+        lines += [head, f"      {c.help}"]
+    lines += ["", "options of run and generate:"] + [OPTIONS[n].usage() for n in GENERATION]
+    lines += ["", "options of random: --seed N (default 0), --dtype bfloat16|float32"]
+    return "\n".join(lines) + "\n"
 
 
 def cli(args: Sequence[str]) -> int:
-    """Run the command line on ``args``; returns the process exit code (src/cli.jl:258-277)."""
+    """Run the command line on ``args``; returns the process exit code: 0, or 1 after an error message on
+    stderr (src/cli.jl:258-277)."""
     args = list(args)
     if not args or args[0] in ("-h", "--help", "help"):
-        print(USAGE, end="")
-        return 1 if not args else 0
+        print(usage(), end="")
+        return 0 if args else 1
     command = COMMANDS.get(args[0])
     if command is None:
         print(f"unknown command: {args[0]}\n", file=sys.stderr)
-        print(USAGE, end="", file=sys.stderr)
+        print(usage(), end="", file=sys.stderr)
         return 1
     try:
-        command(*parse_args(args[1:]))
+        command.run(*command.read(args[1:]))
     except (ArgumentError, ValueError, FileNotFoundError, RuntimeError) as e:
         print(f"error: {e}", file=sys.stderr)
         return 1

@@ -22,9 +22,9 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
 __device__ __forceinline__ void mbar_arrive(unsigned bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Bounded wait; false (and bit `code` set in *status) when the limit is reached.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code) {
-    for (unsigned it = 0; it < WAIT_LIMIT; ++it) {
+// Bounded wait; false (and bit `code` set in *status) when the limit of attempts is reached.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int* status, int code, unsigned limit = WAIT_LIMIT) {
+    for (unsigned it = 0; it < limit; ++it) {
         unsigned done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"

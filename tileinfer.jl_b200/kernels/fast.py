@@ -102,7 +102,6 @@ def tc_splits(out_features: int, in_features: int, n: int) -> int:
 # their consumer more (residual add + norm of 128 tokens: 8 us with 4 slices, 15 us with 7).
 DECODE_PRODUCT_MIN_TOKENS = 65
 DECODE_PRODUCT_MAX_TOKENS = 128
-DECODE_PRODUCT_SPLITTABLE = False      # the micro-benchmark's switch: send the products that may be cut over k there too
 _plans = {}
 
 
@@ -141,7 +140,7 @@ def _tcgen05(lin, x, out, epilogue, act, allow_partials):
     n, k = x.shape
     w = lin.weight
     may_split = allow_partials and epilogue == ops.EPI_NONE
-    if DECODE_PRODUCT_MIN_TOKENS <= n <= DECODE_PRODUCT_MAX_TOKENS and (DECODE_PRODUCT_SPLITTABLE or not may_split):
+    if DECODE_PRODUCT_MIN_TOKENS <= n <= DECODE_PRODUCT_MAX_TOKENS and not may_split:
         y = _tcgen05_decode(lin, x, out, epilogue, act, allow_partials)
         if y is not None:
             return y

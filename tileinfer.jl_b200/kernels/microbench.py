@@ -3,7 +3,6 @@
     python -m tileinfer_b200.kernels.microbench gemv    --out 21504 --in 4096 --tokens 1 [--splits S]
     python -m tileinfer_b200.kernels.microbench gemm    --out 21504 --in 4096 --tokens 2048 [--epilogue xielu]
     python -m tileinfer_b200.kernels.microbench gemmd   --out 21504 --in 4096 --tokens 64 [--tile 160] [--splits S]
-    python -m tileinfer_b200.kernels.microbench sweep   --tokens 64       (tile widths x k slices of the decode-batch product)
     python -m tileinfer_b200.kernels.microbench decode  --batch 8 --context 1024
     python -m tileinfer_b200.kernels.microbench prefill --tokens 2048 [--kernel mma]
     python -m tileinfer_b200.kernels.microbench timeline --batch 1 --layers 8
@@ -89,33 +88,6 @@ def bench_product(kind, out, k, n, splits, epilogue, once, tile=0, Ws=None, quie
         return ms
     print(f"{kind} out={out} in={k} tokens={n} splits={splits} epilogue={epilogue}: {ms * 1e3:.1f} us, "
           f"{out * k * 2 / ms / 1e6:.0f} GB/s of weights, {2 * n * out * k / ms / 1e9:.1f} TFLOP/s")
-
-
-def sweep_decode_products(n):
-    """Every tile width and k-slice count of the decode-batch product on the Apertus-8B products, against
-    the 128-row kernel with the engine's slice policy: the table the plan's cost model is fitted to."""
-    s = APERTUS_8B_LAYER
-    qkv = (s["heads"] + 2 * s["kv_heads"]) * s["head_dim"]
-    for name, out, k, may_split, epilogue in (("qkv", qkv, s["hidden"], True, "none"), ("o", s["hidden"], s["heads"] * s["head_dim"], True, "none"),
-                                              ("up", s["intermediate"], s["hidden"], False, "xielu"),
-                                              ("down", s["hidden"], s["intermediate"], True, "none"), ("head", s["vocab"], s["hidden"], False, "f32")):
-        Ws = _weights(out, k)
-        old_splits = fast.tc_splits(out, k, n) if may_split else 1
-        old = bench_product("gemm", out, k, n, old_splits, epilogue, False, Ws=Ws, quiet=True)
-        rows = []
-        for splits in ((1, 2, 3, 4, 6, 8) if may_split else (1,)):
-            for tile in range(16, 257, 16):
-                if -(-out // tile) * splits < 64:
-                    continue
-                rows.append((bench_product("gemmd", out, k, n, splits, epilogue, False, tile=tile, Ws=Ws, quiet=True), tile, splits))
-        rows.sort()
-        nt, sp = fast.decode_product_plan(n, out, k, 8 if may_split else 1)
-        planned = [r for r in rows if r[1] == nt and r[2] == sp]
-        print(f"{name} tokens={n}: 128-row kernel ({old_splits} slices) {old * 1e3:.1f} us; plan tile {nt} x {sp} slices "
-              f"{planned[0][0] * 1e3 if planned else float('nan'):.1f} us; best: "
-              + ", ".join(f"{t} x {sp_} {ms * 1e3:.1f}" for ms, t, sp_ in rows[:6]), flush=True)
-        for splits in sorted({r[2] for r in rows}):
-            print(f"   {splits} slices: " + " ".join(f"{t}:{ms * 1e3:.1f}" for ms, t, sp_ in sorted(rows, key=lambda r: r[1]) if sp_ == splits), flush=True)
 
 
 def bench_decode_attention(batch, context, once, splits=0, heads=32, kv_heads=8, head_dim=128):
@@ -246,7 +218,7 @@ def timeline(batch, layers, cached=1023, prefill_tokens=0):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench")
-    ap.add_argument("what", choices=["gemv", "gemm", "gemmd", "sweep", "decode", "prefill", "timeline"])
+    ap.add_argument("what", choices=["gemv", "gemm", "gemmd", "decode", "prefill", "timeline"])
     ap.add_argument("--out", type=int, default=21504)
     ap.add_argument("--in", dest="k", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=1)
@@ -257,19 +229,14 @@ def main(argv=None):
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=8)
     ap.add_argument("--kernel", default="tc", choices=["tc", "mma"], help="prefill attention: tcgen05 or mma.sync kernel")
-    ap.add_argument("--products", default="new", choices=["new", "rows128", "all"],
-                    help="timeline: the engine's choice of product kernels, the 128-row kernel everywhere, or the kernel with the tokens in "
-                         "the tensor-memory lanes for every product of 9 to 128 tokens")
+    ap.add_argument("--products", default="new", choices=["new", "rows128"],
+                    help="timeline: the engine's choice of product kernels, or the 128-row kernel everywhere")
     ap.add_argument("--once", action="store_true", help="a few eager launches and no timing (for ncu)")
     a = ap.parse_args(argv)
     if a.products == "rows128":
         fast.DECODE_PRODUCT_MAX_TOKENS = 0
-    elif a.products == "all":
-        fast.DECODE_PRODUCT_MIN_TOKENS, fast.DECODE_PRODUCT_SPLITTABLE = 9, True
     if a.what in ("gemv", "gemm", "gemmd"):
         bench_product(a.what, a.out, a.k, a.tokens, max(1, a.splits), a.epilogue, a.once, tile=a.tile)
-    elif a.what == "sweep":
-        sweep_decode_products(a.tokens)
     elif a.what == "decode":
         bench_decode_attention(a.batch, a.context, a.once, a.splits)
     elif a.what == "prefill":
