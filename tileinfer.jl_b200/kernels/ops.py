@@ -124,7 +124,7 @@ def attention_inputs(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, rota
         args = (qkv.data_ptr(), qkv.stride(0), None, 0, 0)
         n = qkv.shape[0]
     check(lib().ti_attention_inputs(*args, q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache),
-                                    _ptr(q_norm_w), _ptr(k_norm_w), eps, _ptr(cos_sin), positions.data_ptr(),
+                                    _ptr(q_norm_w), _ptr(k_norm_w), eps, _ptr(cos_sin), rotary, interleaved, positions.data_ptr(),
                                     _ptr(slots), n, nq, nkv, head_dim, page_size, int(write_kv),
                                     dtype_code(q_out.dtype), _stream()), "attention_inputs")
 
