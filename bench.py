@@ -143,7 +143,7 @@ def time_decode(engine, batch, steps, warmup, vocab, count_launches=False):
     decode_batch(engine, sampler, SamplingParams(), list(range(batch)), slots, logits, results, warmup + steps + 2, set(), on_token)
     torch.cuda.synchronize()
     ms = marks[warmup].elapsed_time(marks[warmup + steps])
-    launches = engine.decode_launches(batch) + 2 if count_launches else 0     # the captured step + sampling + id hand-over
+    launches = engine.decode_launches(batch) + 1 if count_launches else 0     # the captured step + sampling (which hands the ids over)
     kv_positions = batch * (CACHED + warmup + 1 + steps / 2)
     assert not slots                                                  # the loop freed every sequence
     return ms / steps, kv_positions, launches

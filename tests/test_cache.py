@@ -141,8 +141,7 @@ def test_a_windowed_group_gives_pages_back_as_they_fall_out_of_the_window():
     assert win.tables[s] == [0, 1, 2, 3] and win.first.get(s, 0) == 0          # key 4 is still seen: page 1, unit 0
     c.reserve([(s, 4)]); c.advance(s, 4)                                      # L = 17: first key 8, page 2
     assert win.tables[s] == [None, None, 2, 3, 4] and win.first[s] == 2 and win.pages.held == 3
-    assert win.pages.take() == 0                                              # page 0 is free again
-    win.pages.give(0)
+    assert not win.pages.is_held(0) and not win.pages.is_held(1)              # pages 0 and 1 are free again
     assert full.tables[s] == [0, 1, 2, 3, 4]                                  # the other group keeps everything
     for _ in range(30):
         c.reserve([(s, 1)]); c.advance(s, 1)
@@ -209,7 +208,7 @@ def test_the_peak_of_a_chunked_step_is_what_running_it_takes():
                 c.reserve([(s, n)]); c.advance(s, n)
         growth = [(s, rng.randint(1, 120)) for s in slots]
         before = win.pages.held
-        predicted = win.peak_pages(growth, c.lengths, chunk)
+        predicted = win.peak_pages(growth, chunk)
         c.reserve(growth, chunk_tokens=chunk)
         peak, room, cur = before, chunk, []
         for s, n in growth:

@@ -61,7 +61,7 @@ def test_decode_work_slots_are_shared_out_by_length():
     all sequences fit the slots; a sequence's slots are consecutive and numbered; equal lengths give
     every sequence the same number of parts; a long sequence among short ones gets most of them."""
     import numpy as np
-    from tileinfer_b200.engine.step import split_tables
+    from tileinfer_b200.kernels.fast import split_tables
     rng = np.random.default_rng(0)
     for B, splits in ((1, 32), (3, 9), (8, 4), (8, 1), (37, 8), (64, 4)):
         for lengths in (np.full(B, 1023), rng.integers(1, 40000, B), np.array([1] * (B - 1) + [30000])):

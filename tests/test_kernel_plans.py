@@ -64,3 +64,13 @@ def test_slices_of_the_other_decode_products():
     assert fast.tc_splits(21504, 4096, 64) == 1 and fast.tc_splits(4096, 21504, 64) == 8
     assert fast.tc_splits(4096, 4096, 2048) == 1                                         # prefill is never cut
     assert fast.decode_splits(1, 8, 4096) == 32 and fast.decode_splits(64, 8, 4096) == 1
+
+
+def test_the_attention_plan_in_the_step_planner_uses_the_same_split_policy():
+    """The C++ plan that fills decode attention's work tables and the Python policy that sizes the kernel's
+    work space when no plan is attached must agree on the split count for every batch size."""
+    from tileinfer_b200.kernels import fast
+    for kv_heads, page, pool in ((8, 64, 64 * 4096), (2, 64, 1024), (1, 16, 640), (8, 64, 128)):
+        plan = fast.SplitKvPlan(kv_heads, page, pool)
+        for batch in (1, 2, 3, 7, 8, 9, 18, 19, 37, 64, 100, 300):
+            assert plan.splits(batch) == fast.decode_splits(batch, kv_heads, pool), (kv_heads, pool, batch)

@@ -551,7 +551,7 @@ def test_attention_decode_with_shared_out_slots(ops, nq, nkv, D, splits, lengths
     (the long sequence read by many blocks, the short ones by one), against exact attention and against
     the same launch with equal splits; up to 32,768 keys, where one sequence gets the most parts there are."""
     import numpy as np
-    from tileinfer_b200.engine.step import split_tables
+    from tileinfer_b200.kernels.fast import split_tables
     from tileinfer_b200.kernels.library import check, lib
     torch.manual_seed(21)
     dtype = torch.bfloat16

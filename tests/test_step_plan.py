@@ -1,4 +1,4 @@
-"""The step's metadata, built on the host (engine/step.py): positions, cache places, sequence ranges and
+"""The step's metadata, built on the host (csrc/host/step_planner.cpp through engine/step.py): positions, cache places, sequence ranges and
 wanted rows of batches of unequal sequences, and the short path for one-token steps, which must write
 exactly what the general one writes. Runs on the CPU (the planner only fills integer buffers)."""
 import random
@@ -8,7 +8,8 @@ import pytest
 import torch
 
 from tileinfer_b200.cache import Cache
-from tileinfer_b200.engine.step import StepPlanner, split_tables
+from tileinfer_b200.engine.step import StepPlanner
+from tileinfer_b200.kernels.fast import SplitKvPlan, split_tables
 from tileinfer_b200.parts import CacheRequest
 
 
@@ -51,7 +52,9 @@ def test_a_batch_of_unequal_sequences():
 def test_the_short_path_for_one_token_steps_writes_what_the_general_one_writes():
     rng = random.Random(3)
     cache, planner = make(max_seqs=6, max_tokens=400)
-    planner.split_policy = lambda batch, group: 4                  # decode attention's work tables too
+    plan = SplitKvPlan(2, 4, 400)                                  # decode attention's work tables too
+    planner.attach_plan(cache.paged_groups[0], plan)
+    assert plan.splits(6) > 1
     slots = [cache.alloc_slot() for _ in range(6)]
     for s in slots:
         n = rng.randrange(1, 40)
@@ -67,7 +70,9 @@ def test_the_short_path_for_one_token_steps_writes_what_the_general_one_writes()
         first = planner.meta[:o["end"]].clone()
         planner.meta.zero_()
         short = planner.plan_decode(live, tokens)
-        assert torch.equal(planner.meta[:o["end"]], first)
+        assert torch.equal(planner.meta[:o["end"]], first) and o["plan_words"][0] > 0
+        work, seq = plan.tables(len(live), short.group(0).plan_table)
+        assert short.group(0).plan is plan and work.numel() == 2 * len(live) * plan.splits(len(live)) and seq.numel() == len(live)
         assert short.is_decode and short.host_starts == general.host_starts and short.max_kv_len == general.max_kv_len
         for s in live:
             cache.advance(s, 1)

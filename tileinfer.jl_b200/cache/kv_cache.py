@@ -21,14 +21,21 @@ chunks, ``prepare`` takes each chunk's pages).
 The reference has one group, one sequence per step and a block table per ``Sequence``
 object (src/kv/block_manager.jl:13-16); slots, groups and the per-sequence state are this
 library's own.
+
+The books (which slots are held, every sequence's length and pages, the pools' free lists) are kept by
+the C++ host runtime (``csrc/host/cache_book.cpp``), which also writes new block-table entries to the
+device and zeroes fresh pages with one kernel; this module allocates the storage and wraps the books.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
+from ..kernels import host
 from ..parts.base import CacheRequest
 from .allocator import NumberPool, OutOfPagesError, OutOfSlotsError
 
@@ -46,63 +53,74 @@ class LayerCache:
     state: Optional[torch.Tensor] = None    # [slots, *shape]
 
 
+def _stream(device) -> Optional[int]:
+    if torch.device(device).type != "cuda":
+        return None
+    from ..kernels import library
+    return library.current_stream()
+
+
+class _Pages:
+    """A paged group's pool of page numbers, as the books see it."""
+
+    def __init__(self, group):
+        self._g = group
+
+    @property
+    def free(self) -> int:
+        return self._g._api.group_pages_free(self._g._book, self._g.book_index)
+
+    @property
+    def held(self) -> int:
+        return self._g._api.group_pages_held(self._g._book, self._g.book_index)
+
+    def is_held(self, page: int) -> bool:
+        return bool(self._g._api.group_page_is_held(self._g._book, self._g.book_index, page))
+
+
 class PagedGroup:
     kind = "paged_kv"
 
-    def __init__(self, index, request: CacheRequest, layers: List[int], num_pages: int, page_size: int, max_seqs: int,
-                 max_pages_per_seq: int, dtype, device, release_granule: int = 1):
+    def __init__(self, index, book, book_index, request: CacheRequest, layers: List[int], num_pages: int, page_size: int,
+                 max_seqs: int, max_pages_per_seq: int, dtype, device, release_granule: int = 1):
         self.index, self.request, self.layers = index, request, layers
         self.page_size, self.num_pages = page_size, num_pages
         self.window = request.window or 0
         self.release_granule = max(1, release_granule)
-        self.first: Dict[int, int] = {}          # logical index of a sequence's first page that is still held
+        self.max_seqs, self.max_pages_per_seq = max_seqs, max_pages_per_seq
+        self._api, self._book, self.book_index = host.api(), book, book_index      # book_index: among the paged groups
         shape = (len(layers), num_pages, request.kv_heads, page_size, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
-        self.pages = NumberPool(num_pages, "page")
-        self.tables: Dict[int, List[int]] = {}
-        self.max_pages_per_seq = max_pages_per_seq
-        self._pin = torch.device(device).type == "cuda"
-        self.host_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32)      # the host's copy, read by the step planner
         self.device_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, device=device)
+        page_bytes = request.kv_heads * page_size * request.head_dim * self.v.element_size()
+        self._api.cache_group_storage(book, book_index, self.device_table.data_ptr(), self.device_table.stride(0), self.v.data_ptr(),
+                                      len(layers), num_pages * page_bytes, page_bytes, int(torch.device(device).type == "cuda"))
+        # The host's copy of the block tables lives in the books; the step planner reads it there.
+        raw = ctypes.cast(self._api.group_host_table(book, book_index), ctypes.POINTER(ctypes.c_int32))
+        self.host_table = torch.from_numpy(np.ctypeslib.as_array(raw, shape=(max_seqs, max_pages_per_seq)))
+        self.pages = _Pages(self)
 
-    def pages_needed(self, slot: int, new_length: int) -> int:
-        have = len(self.tables.get(slot, ()))
-        return max(0, -(-new_length // self.page_size) - have)
+    def table(self, slot: int) -> List[Optional[int]]:
+        """The pages of a sequence by logical index; None where a page was given back behind the window."""
+        buf = (ctypes.c_int * self.max_pages_per_seq)()
+        n = self._api.group_table(self._book, self.book_index, slot, buf, self.max_pages_per_seq)
+        return [None if buf[i] < 0 else buf[i] for i in range(n)]
 
-    def grow_many(self, growth: Sequence[Tuple[int, int]]) -> None:
-        """Pages for each ``(slot, new length)`` (the caller has checked that the pool has them): the block
-        tables' new entries go up in ONE copy and the new pages' values are zeroed by ONE kernel."""
-        rows, cols, numbers = [], [], []
-        for slot, new_length in growth:
-            need = self.pages_needed(slot, new_length)
-            if not need:
-                continue
-            table = self.tables.setdefault(slot, [])
-            if len(table) + need > self.max_pages_per_seq:
-                raise ValueError(f"a sequence of {new_length} positions needs more than {self.max_pages_per_seq} pages")
-            new = self.pages.take_many(need)
-            a = len(table)
-            table.extend(new)
-            self.host_table[slot, a:a + need] = torch.tensor(new, dtype=torch.int32)
-            rows += [slot] * need
-            cols += range(a, a + need)
-            numbers += new
-        if not numbers:
-            return
-        # The upload reads its source when the stream gets there, which may be after a slot has been freed
-        # and handed to another sequence: it has a pinned buffer of its own (the allocator keeps it until the
-        # copy has run), never the host table, which the next owner overwrites at once.
-        packed = torch.tensor([rows, cols, numbers], dtype=torch.int64)
-        packed = (packed.pin_memory() if self._pin else packed).to(self.device_table.device, non_blocking=True)
-        self.device_table[packed[0], packed[1]] = packed[2].to(torch.int32)
-        # A page's last user may have left anything in it. Keys beyond a sequence's length are masked by
-        # selection, but their values take part in P V with weight 0, and 0 times a stale infinity or NaN
-        # is NaN: values are zeroed when a page is taken.
-        self.v.index_fill_(1, packed[2], 0)
+    @property
+    def tables(self) -> Dict[int, List[Optional[int]]]:
+        out = {}
+        for slot in range(self.max_seqs):
+            t = self.table(slot)
+            if t:
+                out[slot] = t
+        return out
 
-    def grow(self, slot: int, new_length: int) -> None:
-        self.grow_many([(slot, new_length)])
+    @property
+    def first(self) -> Dict[int, int]:
+        """Logical index of each sequence's first page that is still held (sequences that gave pages back only)."""
+        firsts = {s: self._api.group_first(self._book, self.book_index, s) for s in range(self.max_seqs)}
+        return {s: f for s, f in firsts.items() if f}
 
     def first_needed_page(self, length: int) -> int:
         """Logical index of the first page that a query at position ``length`` or later can read."""
@@ -111,61 +129,12 @@ class PagedGroup:
         key = max(0, length - self.window + 1)
         return key // self.page_size // self.release_granule * self.release_granule
 
-    def release(self, slot: int, length: int) -> int:
-        """Give back the pages that no query after ``length`` positions can see; returns how many."""
-        table = self.tables.get(slot)
-        if not self.window or not table:
-            return 0
-        a, b = self.first.get(slot, 0), min(self.first_needed_page(length), len(table))
-        for i in range(a, b):
-            self.pages.give(table[i])
-            table[i] = None
-        if b > a:
-            self.first[slot] = b
-        return max(0, b - a)
-
-    def shrink(self, slot: int, new_length: int) -> None:
-        table = self.tables.get(slot, [])
-        keep = -(-new_length // self.page_size)
-        if keep and self.first_needed_page(new_length) < self.first.get(slot, 0):
-            raise ValueError(f"cannot roll back to {new_length} positions: the pages of its window were given back")
-        for p in reversed(table[keep:]):
-            if p is not None:
-                self.pages.give(p)
-        del table[keep:]
-        if not table:
-            self.tables.pop(slot, None)
-            self.first.pop(slot, None)
-
-    def peak_pages(self, growth, lengths: Dict[int, int], chunk_tokens: Optional[int]) -> int:
+    def peak_pages(self, growth: Sequence[Tuple[int, int]], chunk_tokens: Optional[int]) -> int:
         """Most pages beyond those held now that ``growth`` = [(slot, n)] needs at any time when it
         runs in token order in chunks of ``chunk_tokens`` and every chunk's end releases what fell out
         of the window."""
-        logical = {s: len(self.tables.get(s, ())) for s, _ in growth}
-        first = {s: self.first.get(s, 0) for s, _ in growth}
-        length = {s: lengths[s] for s, _ in growth}
-        extra = peak = 0
-        room = chunk_tokens or (1 << 62)
-        touched = []
-        for slot, n in growth:
-            a = 0
-            while a < n:
-                take = min(room, n - a)
-                length[slot] += take
-                need = max(0, -(-length[slot] // self.page_size) - logical[slot])
-                logical[slot] += need
-                extra += need
-                touched.append(slot)
-                a += take
-                room -= take
-                if room == 0:
-                    peak = max(peak, extra)
-                    for s in touched:
-                        b = min(self.first_needed_page(length[s]), logical[s])
-                        extra -= max(0, b - first[s])
-                        first[s] = max(first[s], b)
-                    touched, room = [], chunk_tokens
-        return max(peak, extra)
+        return int(self._api.group_peak_pages(self._book, self.book_index, len(growth), host.ints(s for s, _ in growth),
+                                              host.longs(n for _, n in growth), chunk_tokens or 0))
 
     def bytes_per_position(self) -> int:
         r = self.request
@@ -178,6 +147,22 @@ class StateGroup:
     def __init__(self, index, request: CacheRequest, layers: List[int], max_seqs: int, dtype, device):
         self.index, self.request, self.layers = index, request, layers
         self.state = torch.zeros((len(layers), max_seqs) + tuple(request.shape), dtype=request.dtype or dtype, device=device)
+
+
+class _Slots:
+    def __init__(self, cache):
+        self._c = cache
+
+    @property
+    def held(self) -> int:
+        return self._c._api.cache_slots_held(self._c._book)
+
+    @property
+    def free(self) -> int:
+        return self._c.max_seqs - self.held
+
+    def is_held(self, slot: int) -> bool:
+        return bool(self._c._api.cache_slot_is_held(self._c._book, slot))
 
 
 class Cache:
@@ -199,12 +184,16 @@ class Cache:
         self.max_seq_len = min(max_seq_len or self.max_tokens, self.max_tokens)
         self.max_step_tokens = max_step_tokens
         max_pages_per_seq = -(-self.max_seq_len // page_size)
-        self.slots = NumberPool(max_seqs, "sequence slot")
-        self.lengths: Dict[int, int] = {}
         by_key: Dict[tuple, List[int]] = {}
         for i, r in enumerate(requests):
             if r is not None:
                 by_key.setdefault(r.group_key(), []).append(i)
+        kinds = {requests[layers[0]].kind for layers in by_key.values()}
+        if kinds - {"paged_kv", "state"}:
+            raise ValueError(f"unknown cache kind {sorted(kinds - {'paged_kv', 'state'})[0]}")
+        self._api = host.api()
+        self._book = self._api.cache_create(max_seqs, self.max_seq_len, int("state" in kinds))
+        self.slots = _Slots(self)
         self.groups = []
         self._layer_view: Dict[int, LayerCache] = {}
         for key, layers in by_key.items():
@@ -217,16 +206,15 @@ class Cache:
                     # page that it writes to; plus the tokens of one step.
                     per_seq = -(-(r.window - 1) // page_size) + release_granule + 1
                     pages = min(pages, max_seqs * per_seq + -(-max_step_tokens // page_size))
-                g = PagedGroup(gi, r, layers, pages, page_size, max_seqs, max_pages_per_seq, dtype, device,
+                bi = self._api.cache_add_group(self._book, pages, page_size, r.window or 0, release_granule, max_pages_per_seq)
+                g = PagedGroup(gi, self._book, bi, r, layers, pages, page_size, max_seqs, max_pages_per_seq, dtype, device,
                                release_granule)
                 for j, l in enumerate(layers):
                     self._layer_view[l] = LayerCache(gi, "paged_kv", page_size, g.k[j], g.v[j])
-            elif r.kind == "state":
+            else:
                 g = StateGroup(gi, r, layers, max_seqs, dtype, device)
                 for j, l in enumerate(layers):
                     self._layer_view[l] = LayerCache(gi, "state", state=g.state[j])
-            else:
-                raise ValueError(f"unknown cache kind {r.kind}")
             self.groups.append(g)
         for reader, source in (share or {}).items():
             self._layer_view[reader] = self._layer_view[source]
@@ -234,24 +222,47 @@ class Cache:
         self.state_groups = [g for g in self.groups if g.kind == "state"]
         self.windowed_groups = [g for g in self.paged_groups if g.window]
 
+    def __del__(self):
+        if getattr(self, "_book", None):
+            self._api.cache_destroy(self._book)
+            self._book = None
+
+    @property
+    def book(self):
+        """The C++ books' handle (the step planner and the decode loop work on it directly)."""
+        return self._book
+
+    def _refused(self):
+        raise ValueError(host.last_error())
+
     # ---- slots
     def alloc_slot(self) -> int:
-        slot = self.slots.take()
-        self.lengths[slot] = 0
+        slot = self._api.cache_alloc_slot(self._book)
+        if slot < 0:
+            raise OutOfSlotsError(f"no free sequence slot (all {self.max_seqs} are held)")
         for g in self.state_groups:
             g.state[:, slot].zero_()
         return slot
 
     def free_slot(self, slot: int) -> None:
-        if not self.slots.is_held(slot):
-            raise ValueError(f"sequence slot {slot} is not held (freed twice, or never allocated)")
-        for g in self.paged_groups:
-            g.shrink(slot, 0)
-        del self.lengths[slot]
-        self.slots.give(slot)
+        if self._api.cache_free_slot(self._book, slot):
+            self._refused()
 
     def length(self, slot: int) -> int:
-        return self.lengths[slot]
+        n = self._api.cache_length(self._book, slot)
+        if n < 0:
+            raise KeyError(f"sequence slot {slot} is not held")
+        return int(n)
+
+    @property
+    def lengths(self) -> Dict[int, int]:
+        """Length of every held sequence, by slot."""
+        out = {}
+        for slot in range(self.max_seqs):
+            n = self._api.cache_length(self._book, slot)
+            if n >= 0:
+                out[slot] = int(n)
+        return out
 
     # ---- pages
     def reserve(self, growth: Sequence[Tuple[int, int]], chunk_tokens: Optional[int] = None) -> None:
@@ -259,46 +270,31 @@ class Cache:
         pages or nothing changes (OutOfPagesError), as in src/kv/block_manager.jl:58-65. With
         ``chunk_tokens`` the caller runs the tokens in order in chunks of that many, calling ``prepare``
         before and ``advance`` after each: groups with a window then take their pages chunk by chunk."""
-        for slot, n in growth:
-            if not self.slots.is_held(slot):
-                raise ValueError(f"sequence slot {slot} is not held")
-            if self.lengths[slot] + n > self.max_seq_len:
-                raise ValueError(f"sequence would reach {self.lengths[slot] + n} positions; the cache was sized for "
-                                 f"sequences of at most {self.max_seq_len}")
-        chunked = chunk_tokens is not None and sum(n for _, n in growth) > chunk_tokens
-        for g in self.paged_groups:
-            if g.window and chunked:
-                need = g.peak_pages(growth, self.lengths, chunk_tokens)
-            else:
-                need = sum(g.pages_needed(slot, self.lengths[slot] + n) for slot, n in growth)
-            if need > g.pages.free:
-                raise OutOfPagesError(need, g.pages.free)
-        for g in self.paged_groups:
-            if not (g.window and chunked):
-                g.grow_many([(slot, self.lengths[slot] + n) for slot, n in growth])
+        needed, free = ctypes.c_longlong(), ctypes.c_longlong()
+        rc = self._api.cache_reserve(self._book, len(growth), host.ints(s for s, _ in growth), host.longs(n for _, n in growth),
+                                     chunk_tokens or 0, _stream(self.device), ctypes.byref(needed), ctypes.byref(free))
+        if rc == 1:
+            raise OutOfPagesError(needed.value, free.value)
+        if rc:
+            self._refused()
 
     def prepare(self, growth: Sequence[Tuple[int, int]]) -> None:
         """Before a chunk of a reserved step runs: the pages of this chunk for the groups that take
         them chunk by chunk (``reserve`` has checked that they are there)."""
-        for g in self.windowed_groups:
-            g.grow_many([(slot, self.lengths[slot] + n) for slot, n in growth])
+        if self.windowed_groups and self._api.cache_prepare(self._book, len(growth), host.ints(s for s, _ in growth),
+                                                            host.longs(n for _, n in growth), _stream(self.device)):
+            self._refused()
 
     def advance(self, slot: int, n: int) -> None:
         """The step that wrote ``n`` more positions of ``slot`` has been enqueued."""
-        self.lengths[slot] += n
-        for g in self.windowed_groups:
-            g.release(slot, self.lengths[slot])
+        if self._api.cache_advance(self._book, slot, n):
+            self._refused()
 
     def truncate(self, slot: int, length: int) -> None:
         """Forget the positions after the first ``length`` (src/kv/block_manager.jl:74-81). Only paged
         storage can roll back; a state cannot."""
-        if not 0 <= length <= self.lengths[slot]:
-            raise ValueError(f"cannot truncate a sequence of length {self.lengths[slot]} to {length}")
-        if self.state_groups and length != self.lengths[slot]:
-            raise ValueError("layers with a per-sequence state cannot roll back")
-        for g in self.paged_groups:
-            g.shrink(slot, length)
-        self.lengths[slot] = length
+        if self._api.cache_truncate(self._book, slot, length):
+            self._refused()
 
     def layer(self, index: int) -> LayerCache:
         return self._layer_view[index]

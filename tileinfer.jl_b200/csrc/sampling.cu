@@ -74,8 +74,8 @@ __device__ __forceinline__ void am_block_reduce(float& bv, int& bi, float* sv, i
 }
 
 __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* logits, long long ld, int vocab, int per_chunk,
-                                                            int* __restrict__ out, float* ws_val, int* ws_idx,
-                                                            unsigned* counters) {
+                                                            int* __restrict__ out, int* __restrict__ out2, float* ws_val,
+                                                            int* ws_idx, unsigned* counters) {
     __shared__ float sv[AM_THREADS / 32];
     __shared__ int si[AM_THREADS / 32];
     __shared__ bool last;
@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* logits,
     am_block_reduce(bv, bi, sv, si);
     if (threadIdx.x == 0) {
         out[row_id] = bi == 0x7fffffff ? 0 : bi;
+        if (out2 != nullptr) out2[row_id] = bi == 0x7fffffff ? 0 : bi;     // the next step's token ids, where the caller has them
         counters[row_id] = 0;                              // ready for the next launch
     }
 }
@@ -138,7 +139,7 @@ extern "C" int ti_argmax_chunks(int vocab) {
     return chunks > AM_MAX_CHUNKS ? AM_MAX_CHUNKS : chunks;
 }
 
-extern "C" int ti_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out, float* ws_val, int* ws_idx,
+extern "C" int ti_argmax(const float* logits, long long ld, int n_rows, int vocab, int* out, int* out2, float* ws_val, int* ws_idx,
                          unsigned* counters, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     TI_REQUIRE(vocab > 0, "argmax: vocab %d", vocab);
@@ -147,7 +148,7 @@ extern "C" int ti_argmax(const float* logits, long long ld, int n_rows, int voca
     const int chunks = ti_argmax_chunks(vocab);
     int per_chunk = (vocab + chunks - 1) / chunks;
     per_chunk = (per_chunk + 3) & ~3;
-    ti_launch(argmax_kernel, dim3(chunks, n_rows), dim3(AM_THREADS), 0, stream, logits, ld, vocab, per_chunk, out, ws_val, ws_idx,
+    ti_launch(argmax_kernel, dim3(chunks, n_rows), dim3(AM_THREADS), 0, stream, logits, ld, vocab, per_chunk, out, out2, ws_val, ws_idx,
               counters);
     return ti_check_launch("argmax");
 }
@@ -481,7 +482,7 @@ __device__ int sample_exact(const float* row, int vocab, float inv_t, int top_k,
 __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* logits, long long ld, int vocab,
                                                             float inv_t, int top_k, float top_p,
                                                             const u32* seeds, u32* counters,
-                                                            int* __restrict__ out) {
+                                                            int* __restrict__ out, int* __restrict__ out2) {
     extern __shared__ u64 dyn[];
     __shared__ float scratch[33];
     const float* row = logits + (size_t)blockIdx.x * ld;
@@ -559,12 +560,13 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* logits,
     }
     if (threadIdx.x == 0) {
         out[blockIdx.x] = token;
+        if (out2 != nullptr) out2[blockIdx.x] = token;
         counters[blockIdx.x] = counter + 1;
     }
 }
 
 extern "C" int ti_sample(const float* logits, long long ld, int n_rows, int vocab, float temperature, int top_k,
-                         float top_p, const unsigned* seeds, unsigned* counters, int* out, cudaStream_t stream) {
+                         float top_p, const unsigned* seeds, unsigned* counters, int* out, int* out2, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     TI_REQUIRE(vocab > 0 && vocab <= (1 << SM_ID_BITS), "sample: vocabulary %d exceeds %d", vocab, 1 << SM_ID_BITS);
     TI_REQUIRE(temperature > 0.f, "sample: temperature must be > 0 (use argmax for greedy)");
@@ -580,7 +582,7 @@ extern "C" int ti_sample(const float* logits, long long ld, int n_rows, int voca
         configured = true;
     }
     ti_launch(sample_kernel, dim3(n_rows), dim3(SM_THREADS), smem, stream, logits, ld, vocab, 1.0f / temperature, top_k, top_p, seeds,
-                                                        counters, out);
+                                                        counters, out, out2);
     return ti_check_launch("sample");
 }
 

@@ -25,6 +25,7 @@ from ..config import load_config, resolve_architecture
 from ..parts import Runtime
 from ..weights import load_tensors, random_tensors
 from .model import DecoderModel, ignorable_tensors, tensor_declarations
+from ..kernels.host import nvtx_range
 from .step import StepPlanner
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -58,10 +59,18 @@ class Engine:
         self.max_step_tokens = int(max_step_tokens)
         self.planner = StepPlanner(self.cache, self.max_step_tokens, self.device)
         self.planner.runtime = self.rt
-        if self.rt.fast and self.rt.dtype == torch.bfloat16:
-            from ..kernels import fast
-            self.planner.split_policy = lambda batch, group: fast.decode_splits(batch, group.request.kv_heads,
-                                                                              group.num_pages * group.page_size)
+        # A mixer may want tables of its own in the metadata of one-token steps: the first mixer of each paged
+        # group is asked for its plan.
+        asked = set()
+        for occ, li in enumerate(self.spec.order):
+            view = self.cache.layer(occ) if occ in self.cache._layer_view else None
+            if view is None or view.kind != "paged_kv" or view.group_index in asked:
+                continue
+            asked.add(view.group_index)
+            mixer = self.model.blocks[li].mixer
+            plan = mixer.decode_plan(self.cache.groups[view.group_index]) if hasattr(mixer, "decode_plan") else None
+            if plan is not None:
+                self.planner.attach_plan(self.cache.groups[view.group_index], plan)
         self.use_graphs = graphs
         self._graphs: Dict[int, object] = {}
         self._logits: Dict[int, torch.Tensor] = {}
@@ -143,6 +152,10 @@ class Engine:
         if decode and out is None:
             return self._decode_step(entries, want)
         logits = out if out is not None else torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device)
+        with nvtx_range("prefill" if not decode else "step"):
+            return self._general_step(entries, want, logits, n_total)
+
+    def _general_step(self, entries, want, logits, n_total):
         if n_total <= self.max_step_tokens:
             ctx = self.planner.plan(entries, want)
             self.model.forward(ctx, self.cache, logits)
@@ -236,6 +249,16 @@ class Engine:
         for s in slots:
             self.cache.advance(s, 1)
         return logits
+
+    def graph_ready(self, batch: int) -> bool:
+        """Whether a decode step of ``batch`` sequences can be replayed from its captured graph as it is."""
+        held = self._graphs.get(batch) if self.use_graphs else None
+        return held is not None and held[1] == self.rt.generation
+
+    def decode_loop(self, sampler):
+        """The C++ side of the generation loop for ``sampler``'s rows (``csrc/decode_loop.cu``)."""
+        from .decode_loop import DecodeLoop
+        return DecodeLoop(self, sampler)
 
     def decode_launches(self, batch: int) -> int:
         """Kernels in one captured decode step of ``batch`` sequences (0 before its first capture)."""

@@ -102,24 +102,30 @@ def decode_batch(engine, sampler, sampling, live, slots, logits, results, max_ne
     changes nothing for the others. AntoineBut/TileInfer.jl pipelines its decode loop the same way
     for one sequence (src/engine/runner.jl:157-191)."""
     import torch
+    loop = engine.decode_loop(sampler) if engine.use_graphs else None
     dead = set()                                       # requests known to have ended, possibly still a row of `logits`
     while live:
-        tokens_dev = sampler.sample(logits, sampling)
-        host, ready = sampler.fetch_async(tokens_dev)
         rows = [row for row, r in enumerate(live) if r not in dead and len(results[r]) + 1 < max_new_tokens]
         nxt = [live[row] for row in rows]
-        next_logits = None
-        if nxt:
-            ids = engine.decode_token_buffer(len(nxt))
-            if len(rows) == len(live):
-                ids.copy_(tokens_dev)
-            else:
-                keep = torch.tensor(rows, dtype=torch.long, device=engine.device)
-                ids.copy_(tokens_dev[keep])
-                sampler.keep_rows(rows)
-            next_logits = engine.decode([slots[r] for r in nxt], None)
-        ready.synchronize()
-        tokens = host.tolist()
+        if loop is not None and (not nxt or engine.graph_ready(len(nxt))):
+            # One call: sample, start the tokens' copy, hand them to the next step, reserve, upload, launch its graph.
+            next_logits = loop.enqueue(logits, sampling, rows, [slots[r] for r in nxt])
+            tokens = loop.wait()
+        else:
+            # The first step of a batch size (which captures its graph), or an engine without graphs: the same, step by step.
+            whole = len(rows) == len(live)
+            ids = engine.decode_token_buffer(len(nxt)) if nxt else None
+            tokens_dev = sampler.sample(logits, sampling, also=ids if whole else None)
+            host, ready = sampler.fetch_async(tokens_dev)
+            next_logits = None
+            if nxt:
+                if not whole:
+                    keep = torch.tensor(rows, dtype=torch.long, device=engine.device)
+                    ids.copy_(tokens_dev[keep])
+                    sampler.keep_rows(rows)
+                next_logits = engine.decode([slots[r] for r in nxt], None)
+            ready.synchronize()
+            tokens = host.tolist()
         for row, r in enumerate(live):
             if r in dead:
                 continue

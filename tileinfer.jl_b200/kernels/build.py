@@ -1,4 +1,6 @@
-"""Compiles the CUDA sources of ``csrc/`` for sm_100a into one shared library.
+"""Compiles the CUDA sources of ``csrc/`` (kernels and their launchers) and the C++ sources of
+``csrc/host/`` (the host runtime: the cache's books, the step planner, the decode loop) for sm_100a
+into one shared library.
 
 ``nvcc`` is run once per source file, in parallel, and the objects are linked with the
 static CUDA runtime, so the library depends on nothing but the driver. Objects and the
@@ -37,14 +39,22 @@ def find_nvcc() -> str:
                      "tileinfer_b200 cannot be built, and there is no fallback without them")
 
 
+HOST = "host"          # the sub-folder of the host runtime's C++ files
+
+
 def sources() -> list:
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    """Paths relative to ``csrc/``: every ``.cu`` there and every ``.cpp`` of ``csrc/host/``."""
+    host = os.path.join(CSRC, HOST)
+    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu")) + \
+        sorted(os.path.join(HOST, f) for f in (os.listdir(host) if os.path.isdir(host) else []) if f.endswith(".cpp"))
 
 
 def _stamp() -> str:
     h = hashlib.sha256()
-    for f in sorted(os.listdir(CSRC)):
-        if f.endswith((".cu", ".cuh", ".h")):
+    host = os.path.join(CSRC, HOST)
+    files = [f for f in os.listdir(CSRC)] + [os.path.join(HOST, f) for f in (os.listdir(host) if os.path.isdir(host) else [])]
+    for f in sorted(files):
+        if f.endswith((".cu", ".cuh", ".h", ".cpp")):
             h.update(f.encode())
             with open(os.path.join(CSRC, f), "rb") as fh:
                 h.update(fh.read())
@@ -101,7 +111,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
     reporter.start()
 
     def compile_one(src: str) -> str:
-        obj = os.path.join(d, src[:-3] + ".o")
+        obj = os.path.join(d, os.path.splitext(src)[0].replace(os.sep, "_") + ".o")
         cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")

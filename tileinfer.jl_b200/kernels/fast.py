@@ -162,6 +162,57 @@ def _tcgen05(lin, x, out, epilogue, act, allow_partials):
     return out
 
 
+MAX_PARTS = 32              # parts of one sequence in decode attention (the combine kernel's limit)
+
+
+def _align32(n: int) -> int:
+    return -(-n // 32) * 32
+
+
+class SplitKvPlan:
+    """How decode attention's B x splits work slots are shared out among the sequences of a step: the
+    attention mixer's ``decode_plan``. The tables are computed by C++ (``csrc/host/split_kv_plan.cpp``) while
+    the step's metadata is filled; this object carries the native plan to the step planner and tells the
+    kernel's caller where the two tables lie in the words the plan was given."""
+
+    def __init__(self, kv_heads: int, page_size: int, pool_tokens: int):
+        from . import host
+        self._api = host.api()
+        self.native = self._api.split_kv_plan_create(kv_heads, page_size, pool_tokens, sm_count(), MAX_PARTS)
+        if not self.native:
+            raise KernelError(host.last_error())
+        self._splits = {}
+
+    def splits(self, batch: int) -> int:
+        s = self._splits.get(batch)
+        if s is None:
+            s = self._splits[batch] = int(self._api.split_kv_plan_splits(self.native, batch))
+        return s
+
+    def tables(self, batch: int, words: torch.Tensor):
+        """(work [2 * batch * splits], seq [batch]) inside ``words``, the plan's part of the step's metadata."""
+        n = 2 * batch * self.splits(batch)
+        return words[:n], words[_align32(n):_align32(n) + batch]
+
+
+def split_tables(lengths, splits: int, page_size: int):
+    """The plan's tables for explicit sizes, as numpy arrays work [batch * splits, 2] and seq [batch] (tests and
+    micro-benchmarks): work[slot] = (sequence << 16 | part << 8 | parts, or -1: no work; the sequence's length),
+    seq[sequence] = first slot << 8 | parts."""
+    import ctypes
+
+    import numpy as np
+    from . import host
+    B = len(lengths)
+    work = np.zeros((B * splits, 2), dtype=np.int32)
+    seq = np.zeros(B, dtype=np.int32)
+    rc = host.api().split_kv_tables(B, splits, page_size, MAX_PARTS, host.longs(int(x) for x in lengths),
+                                    work.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), seq.ctypes.data_as(ctypes.POINTER(ctypes.c_int)))
+    if rc:
+        raise KernelError(host.last_error())
+    return work, seq
+
+
 def decode_splits(batch: int, kv_heads: int, max_context: int) -> int:
     """Split count of decode attention: fixed by the batch size alone, so that a captured step
     stays valid whatever the lengths are (the reference fixes it per model:
@@ -176,17 +227,19 @@ def attention(out, q, cache, meta, step, spec) -> bool:
         return False
     if step.is_decode:
         B = step.n_seqs
-        # The step's plan may carry the split count and how the work slots are shared out among the sequences.
-        splits = meta.decode_splits or decode_splits(B, spec.num_kv_heads, cache.k.shape[0] * cache.page_size)
-        shared = meta.split_work is not None and splits > 1
+        # The step's plan carries the split count and how the work slots are shared out among the sequences.
+        plan = meta.plan if isinstance(meta.plan, SplitKvPlan) else None
+        splits = plan.splits(B) if plan is not None else decode_splits(B, spec.num_kv_heads, cache.k.shape[0] * cache.page_size)
+        shared = plan is not None and meta.plan_table is not None and splits > 1
+        work, seq = plan.tables(B, meta.plan_table) if shared else (None, None)
         rt_buffer = step.runtime.buffer
         ws_o = rt_buffer("attention.ws_o", (B * splits, spec.num_heads, spec.head_dim), torch.float32)
         ws_ml = rt_buffer("attention.ws_ml", (B * splits, spec.num_heads, 2), torch.float32)
         rc = lib().ti_attention_decode_shared(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                                               meta.block_table.data_ptr(), meta.block_table.stride(0),
                                               step.seq_slots.data_ptr(), step.kv_lens.data_ptr(),
-                                              meta.split_work.data_ptr() if shared else None,
-                                              meta.split_seq.data_ptr() if shared else None, ws_o.data_ptr(),
+                                              work.data_ptr() if shared else None,
+                                              seq.data_ptr() if shared else None, ws_o.data_ptr(),
                                               ws_ml.data_ptr(), spec.scale, B, spec.num_heads, spec.num_kv_heads,
                                               spec.head_dim, cache.page_size, splits, spec.window or 0, _stream())
         if rc == 2:

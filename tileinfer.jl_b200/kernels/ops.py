@@ -171,15 +171,17 @@ def argmax_workspace(rows: int, vocab: int, device):
     return ws
 
 
-def argmax(logits, out, workspace=None):
+def argmax(logits, out, workspace=None, also=None):
+    """out[row] = the largest logit's id, ties to the smaller id; ``also``: a second int32 vector that gets the same
+    tokens (the next step's token ids)."""
     _need(logits, "logits", torch.float32, contiguous=False); _need(out, "out", torch.int32)
     val, idx, cnt = workspace or argmax_workspace(logits.shape[0], logits.shape[1], logits.device)
-    check(lib().ti_argmax(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], out.data_ptr(),
+    check(lib().ti_argmax(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], out.data_ptr(), _ptr(also),
                           val.data_ptr(), idx.data_ptr(), cnt.data_ptr(), _stream()), "argmax")
 
 
-def sample(logits, out, temperature, top_k, top_p, seeds, counters):
+def sample(logits, out, temperature, top_k, top_p, seeds, counters, also=None):
     _need(logits, "logits", torch.float32, contiguous=False); _need(out, "out", torch.int32)
     _need(seeds, "seeds", torch.int32); _need(counters, "counters", torch.int32)
     check(lib().ti_sample(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], temperature, top_k,
-                          top_p, seeds.data_ptr(), counters.data_ptr(), out.data_ptr(), _stream()), "sample")
+                          top_p, seeds.data_ptr(), counters.data_ptr(), out.data_ptr(), _ptr(also), _stream()), "sample")

@@ -55,6 +55,14 @@ class Attention(Mixer):
         return CacheRequest("paged_kv", kv_heads=self.spec.num_kv_heads, head_dim=self.spec.head_dim,
                             window=self.spec.window)
 
+    def decode_plan(self, group):
+        """The fast decode kernel reads the keys of a step's sequences in B x splits work slots; how they are
+        shared out among sequences of unequal lengths is a table in the step's metadata."""
+        if not (self.rt.fast and self.rt.dtype == torch.bfloat16) or self.spec.kv_source is not None:
+            return None
+        from ..kernels import fast
+        return fast.SplitKvPlan(self.spec.num_kv_heads, group.page_size, group.num_pages * group.page_size)
+
     def forward(self, h, step, cache):
         s, rt = self.spec, self.rt
         n = h.shape[0]

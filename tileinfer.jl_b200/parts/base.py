@@ -16,7 +16,8 @@ Interfaces (duck-typed; the base classes document them):
   nothing; an encoding of another kind offers methods of its own to the mixers written for it.
 * ``Mixer(spec, tensors, rt, position)``: ``cache_request()`` says what per-sequence storage a
   layer of this kind needs; ``forward(h, step, cache) -> delta`` mixes tokens of the same
-  sequence, reading and writing ``cache`` (the layer's view of its cache group).
+  sequence, reading and writing ``cache`` (the layer's view of its cache group);
+  ``decode_plan(group)`` may ask for tables of its own in the metadata of one-token steps.
 * ``FeedForward(spec, tensors, rt)``: ``forward(h, step) -> delta``, token by token.
 * ``Block(layer_spec, mixer, feed_forward, mixer_norm, feed_forward_norm)``:
   ``forward(x, h, step, cache, next_norm, h_out)``.
@@ -91,6 +92,15 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     def cache_request(self) -> Optional[CacheRequest]:
+        return None
+
+    def decode_plan(self, group) -> Optional[Any]:
+        """Tables that this mixer's kernels want in the metadata of one-token steps, beside what every step
+        carries, or None. ``group`` is the cache group of the mixer's layers (the first mixer of a group is
+        asked, once). The returned object's ``native`` field is a C++ ``ti::GroupPlan`` (``csrc/host/host_common.h``:
+        how many words a step of a given batch size needs, and how to fill them from the sequences' lengths);
+        the step planner reserves and fills those words every step and hands them to the mixer as
+        ``step.group(i).plan_table``, with the object itself as ``step.group(i).plan``."""
         return None
 
     def forward(self, h: torch.Tensor, step, cache) -> torch.Tensor:

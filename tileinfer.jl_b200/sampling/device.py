@@ -54,13 +54,14 @@ class DeviceSampler:
         ev.record()
         return host, ev
 
-    def sample(self, logits: torch.Tensor, params: SamplingParams) -> torch.Tensor:
-        """Tokens [rows] (int32, on the device) for float32 logits [rows, vocab]."""
+    def sample(self, logits: torch.Tensor, params: SamplingParams, also: torch.Tensor = None) -> torch.Tensor:
+        """Tokens [rows] (int32, on the device) for float32 logits [rows, vocab]; ``also``: a second int32
+        vector that receives the same tokens (the next step's token ids)."""
         n = logits.shape[0]
         out = self.tokens[:n]
         if params.greedy:
-            ops.argmax(logits, out)
+            ops.argmax(logits, out, also=also)
         else:
             ops.sample(logits, out, float(params.temperature), int(params.top_k), float(params.top_p),
-                       self.seeds[:n], self.counters[:n])
+                       self.seeds[:n], self.counters[:n], also=also)
         return out
