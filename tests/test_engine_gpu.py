@@ -147,6 +147,39 @@ def test_sampled_generation_and_stop_tokens(models):
     assert len(seen) == 6 and {r for r, _ in seen} == {0, 1}
 
 
+@pytest.mark.parametrize("params", [dict(temperature=0.0), dict(temperature=0.9, top_k=40, top_p=0.95)])
+def test_the_one_call_decode_loop_gives_what_the_step_by_step_loop_gives(models, params):
+    """With graphs the generation loop enqueues a step by ONE C++ call (sample, hand the ids over, reserve,
+    upload, launch the graph); without graphs it does the same step by step from Python. 48 tokens for nine
+    requests with stop tokens that several of them hit at different times (rows drop out, the sampler's
+    seeds and counters are compacted on the device, pages are crossed): the same tokens, in 32-bit exactly."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.sampling import SamplingParams
+    folder, pc, pw = models["B"]
+    prompts = helpers.random_prompts(pc.vocab, [1, 4, 17, 33, 70, 9, 50, 2, 63], 31)
+    sampling = SamplingParams(**params)
+    outs = []
+    for graphs in (True, False):
+        eng = ti.Engine.load(folder, dtype="float32", max_context=128, max_seqs=9, max_tokens=9 * 128, graphs=graphs)
+        free = ti.generate(eng, prompts, max_new_tokens=48, sampling=sampling, stop_ids=[], seed=77)
+        if graphs:
+            counts = {}
+            for g in free:
+                for t in set(g[3:]):
+                    counts[t] = counts.get(t, 0) + 1
+            stops = sorted(counts, key=lambda t: (-counts[t], t))[:4]
+        cut = ti.generate(eng, prompts, max_new_tokens=48, sampling=sampling, stop_ids=stops, seed=77)
+        again = ti.generate(eng, prompts, max_new_tokens=48, sampling=sampling, stop_ids=stops, seed=77)     # every graph captured by now
+        assert again == cut and eng.cache.slots.held == 0 and eng.cache.free_pages() == eng.cache.num_pages
+        outs.append((free, cut))
+    assert outs[0] == outs[1]
+    free, cut = outs[0]
+    assert len({len(c) for c in cut}) > 2                                    # requests ended at different times
+    for f, c in zip(free, cut):
+        hit = [j for j, t in enumerate(f) if t in stops]
+        assert c == (f[:hit[0]] if hit else f)
+
+
 def test_errors_leave_the_cache_untouched(models):
     import tileinfer_b200 as ti
     from tileinfer_b200.cache import OutOfPagesError

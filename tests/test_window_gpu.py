@@ -46,7 +46,7 @@ def poison_free_pages(engine, value=float("nan")):
     (or one that was never taken) shows at once, and so does a page whose last user's values reach the
     next one."""
     for g in engine.cache.paged_groups:
-        free = torch.tensor(sorted(g.pages._free), dtype=torch.long, device=g.k.device)
+        free = torch.tensor([p for p in range(g.num_pages) if not g.pages.is_held(p)], dtype=torch.long, device=g.k.device)
         if len(free):
             g.k[:, free] = value
             g.v[:, free] = -value
