@@ -264,8 +264,12 @@ def test_attention_inputs_with_a_partial_or_interleaved_rotation(ops, dtype, D, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n,out,k", [(1, 100, 72), (37, 301, 120), (130, 96, 200), (5, 4099, 33)])
+@pytest.mark.parametrize("n,out,k", [(1, 100, 72), (37, 301, 120), (130, 96, 200), (5, 4099, 33), (70, 130, 37), (300, 260, 264),
+                                     (64, 40, 1000), (65, 40, 1000)])
 def test_gemm_plain_and_epilogues(ops, dtype, n, out, k):
+    """The 32-bit product's three kernels (weight streaming up to 64 tokens, 128 x 128 tiles for rows that can be read
+    16 bytes at a time, 64 x 64 tiles for the rest) against a 64-bit product, their epilogues, and that a row's
+    bits do not depend on which kernel ran or how many rows shared the launch."""
     torch.manual_seed(4)
     x, w = rnd(torch.randn(n, k), dtype), rnd(torch.randn(out, k) * k ** -0.5, dtype)
     want = rnd((x.double() @ w.double().t()).float(), dtype)

@@ -33,7 +33,7 @@ def case(seed, B, nq, nkv, D, lens):
     k = torch.randn(pages, nkv, 64, D, generator=g).to(torch.bfloat16).cuda()
     v = torch.randn(pages, nkv, 64, D, generator=g).to(torch.bfloat16).cuda()
     q = torch.randn(B, nq, D, generator=g).to(torch.bfloat16).cuda()
-    table = torch.zeros(B, max(-(-n // 64) for n in lens), dtype=torch.int32)
+    table = torch.zeros(B, max(1, max(-(-n // 64) for n in lens)), dtype=torch.int32)
     order = torch.randperm(pages, generator=g).tolist()
     for b, n in enumerate(lens):
         for i in range(-(-n // 64)):
@@ -67,6 +67,29 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         # results are in fact identical.
         assert float((got.float() - want.float()).abs().max()) <= 5 * 2.0 ** -8 * float(want.float().abs().max())
         assert torch.equal(got, want)
+        # And against exact attention over each sequence's own keys (gathered from its pages), so that the check does
+        # not rest on the ordinary entry point alone: softmax(q k / sqrt(D)) v in 64-bit, the new token last.
+        for b, n in enumerate(lens):
+            pages = table[b, :-(-n // 64)].long()
+            keys = k[pages].permute(0, 2, 1, 3).reshape(-1, nkv, D)[:n].double().repeat_interleave(nq // nkv, 1)
+            vals = v[pages].permute(0, 2, 1, 3).reshape(-1, nkv, D)[:n].double().repeat_interleave(nq // nkv, 1)
+            p = torch.softmax(torch.einsum("hd,khd->hk", q[b].double(), keys) * scale, -1)
+            exact = torch.einsum("hk,khd->hd", p, vals)
+            assert float((got[b].double() - exact).abs().max()) <= 5 * 2.0 ** -8 * float(exact.abs().max()), (call, b)
+
+
+def test_a_sequence_without_keys_gives_zeros_not_nan():
+    """kv_lens[b] == 0 (an empty request in a batch): zeros, with and without splits, from both entry points' kernels."""
+    lib = entry_points()
+    stream = torch.cuda.current_stream().cuda_stream
+    q, k, v, table, slots, kv_lens = case(5, 2, 4, 2, 64, [0, 70])
+    for splits in (1, 3):
+        out = torch.full((2, 4, 64), float("nan"), dtype=torch.bfloat16, device="cuda")
+        rc = lib.ti_attention_decode_noalloc(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), table.data_ptr(), table.stride(0),
+                                             slots.data_ptr(), kv_lens.data_ptr(), 0.125, 2, 4, 2, 64, 64, splits, 0, stream)
+        assert rc == 0, lib.ti_last_error()
+        torch.cuda.synchronize()
+        assert float(out[0].float().abs().sum()) == 0.0 and bool(torch.isfinite(out[1].float()).all()) and float(out[1].float().abs().max()) > 0
 
 
 def test_no_alloc_entry_point_refuses_what_its_array_cannot_hold():

@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
         }
         const int head = kvh * group + row;
         if (splits == 1) {
-            out[((size_t)b * nq + head) * D + d] = __float2bfloat16_rn(O / L);
+            out[((size_t)b * nq + head) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);   // a sequence without keys: zeros
         } else {
             const size_t idx = (size_t)(slot - split) * nq + (size_t)head * parts + split;   // a head's parts lie together
             ws_o[idx * D + d] = O;
@@ -206,10 +206,10 @@ __global__ void attention_combine_kernel(bf16* __restrict__ out, const float* ws
         for (int s = 0; s < parts; ++s) M = fmaxf(M, sm[s]);
         float L = 0.f;
         for (int s = 0; s < parts; ++s) {
-            sw[s] = exp2f(sm[s] - M);
+            sw[s] = M == -INFINITY ? 0.f : exp2f(sm[s] - M);     // no part saw a key (a sequence of length 0): zeros, not 0/0
             L += sl[s] * sw[s];
         }
-        s_inv = 1.0f / L;
+        s_inv = L > 0.f ? 1.0f / L : 0.f;
     }
     __syncthreads();
     const float inv = s_inv;

@@ -18,6 +18,11 @@
 //    every element they later read, so nothing has to be cleared between calls; but two calls whose
 //    kernels overlap on the GPU (different streams, no ordering between them) race on it. Keep the
 //    calls of one device on one stream, or order them with events.
+//  * The array that is used is the CURRENT device's (cudaGetDevice at the time of the call): make the
+//    device of `stream` current before calling, or the kernels are handed another GPU's array.
+//  * The per-device table of looked-up addresses is not guarded by a lock: do the first call on each
+//    device from one thread before other threads use that device (later calls only read the table).
+//  * A sequence whose kv_lens entry is 0 gets an output of zeros.
 //  * It calls no cudaMalloc, cudaFree or any routine that allocates.
 //
 // Arguments and results are those of ti_attention_decode() without the two work-space pointers:
