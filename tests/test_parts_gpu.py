@@ -1,6 +1,6 @@
 """Each part of a layer alone against the plain implementation, at sizes that are not the tiny models',
-and a toy mixer with a state of its own, a toy feed-forward with routing and another position encoding,
-all defined HERE: they are registered, built into a model by a toy architecture and stepped through the
+and a toy mixer with a state of its own, a toy feed-forward with routing, another position encoding, a scaled
+embedding and a capped head, all defined HERE: they are registered, built into a model by a toy architecture and stepped through the
 engine without any change to the library's files."""
 import math
 import os
@@ -252,8 +252,40 @@ def test_block_part(dtype):
 def build_toy_architecture():
     from tileinfer_b200.config import (FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec,
                                        TensorDecl, register_architecture)
-    from tileinfer_b200.parts import (CacheRequest, FeedForward, Mixer, PositionEncoding, register_feed_forward,
-                                      register_mixer, register_position)
+    from tileinfer_b200.parts import (CacheRequest, Embedding, FeedForward, Head, Mixer, PositionEncoding, register_embedding,
+                                      register_feed_forward, register_head, register_mixer, register_position)
+
+    @register_embedding("toy_scaled")
+    class ScaledEmbedding(Embedding):
+        """Rows of the table times a multiplier from the model's options: an end of the model that is not Apertus's."""
+
+        def __init__(self, spec, tensors, rt):
+            self.table = rt.param(tensors[spec.embed_name])
+            self.scale = float(spec.options["embed_scale"])
+
+        @classmethod
+        def tensors(cls, spec):
+            return [TensorDecl(spec.embed_name, (spec.vocab_size, spec.hidden_size), ("normal", 0.5))]
+
+        def forward(self, token_ids, out, status):
+            out.copy_((self.table[token_ids.long()].float() * self.scale).to(out.dtype))
+            return out
+
+    @register_head("toy_capped")
+    class CappedHead(Head):
+        """logits = cap * tanh(W h / cap), with a head matrix of its own."""
+
+        def __init__(self, spec, tensors, rt, embedding):
+            self.weight = tensors[spec.lm_head_name].to(rt.device).float()
+            self.cap = float(spec.options["logit_cap"])
+
+        @classmethod
+        def tensors(cls, spec):
+            return [TensorDecl(spec.lm_head_name, (spec.vocab_size, spec.hidden_size), ("normal", 0.3))]
+
+        def forward(self, h, logits):
+            logits.copy_(self.cap * torch.tanh(h.float() @ self.weight.t() / self.cap))
+            return logits
 
     @register_position("toy_learned")
     class LearnedOffsets(PositionEncoding):
@@ -349,7 +381,8 @@ def build_toy_architecture():
                              norm("l1.n2"))
             # The order names the toy layer twice: its second run has a state of its own.
             return ModelSpec("ToyForCausalLM", self.vocab_size, H, (toy, attn), (0, 1, 0), norm("final"),
-                             "embed", "head", self.max_position_embeddings)
+                             "embed", "head", self.max_position_embeddings, embedding_kind="toy_scaled", head_kind="toy_capped",
+                             options={"embed_scale": 3.0, "logit_cap": 2.5})
 
     register_architecture("ToyForCausalLM", ToyConfig)
     return ToyConfig
@@ -393,4 +426,5 @@ def test_toy_parts_are_registered_built_and_stepped(dtype):
         assert again.shape == whole.shape and bool(torch.isfinite(whole).all())
         limit = 1e-4 if dtype == "float32" else 4 * 2.0 ** -8 * float(whole.abs().max())
         assert float((again - whole).abs().max()) <= limit
-        assert float(whole.abs().max()) > 1e-3
+        assert 1.0 < float(whole.abs().max()) <= 2.5                     # the toy head's cap is in effect
+        assert type(eng.model.embedding).__name__ == "ScaledEmbedding" and type(eng.model.head).__name__ == "CappedHead"

@@ -123,3 +123,9 @@ class ModelSpec:
     bos_token_id: Optional[int] = None
     # Standard deviation of the random-weights mode for matrices.
     init_std: float = 0.02
+    # The two ends of the model are parts too, looked up by kind like the layers' parts: how token ids become
+    # the residual stream ("lookup": rows of the table, unscaled) and how the final norm's output becomes
+    # logits ("linear": a product with the head matrix, 32-bit out). ``options`` is theirs to read.
+    embedding_kind: str = "lookup"
+    head_kind: str = "linear"
+    options: Mapping[str, Any] = field(default_factory=dict)

@@ -1,4 +1,4 @@
-"""The decoder: embedding, the layers in their order, final norm, LM head.
+"""The decoder: embedding part, the layers in their order, final norm, head part.
 
 Built from a :class:`ModelSpec` alone: every layer's parts are looked up by kind, and the
 order in which layers run is the spec's ``order`` list (an entry may repeat a layer; a
@@ -20,10 +20,7 @@ from ..parts import Linear, Runtime, lookup
 
 def tensor_declarations(spec: ModelSpec) -> List[TensorDecl]:
     """Every checkpoint tensor a model of this spec reads."""
-    decls = [TensorDecl(spec.embed_name, (spec.vocab_size, spec.hidden_size), ("normal", spec.init_std),
-                        allow_extra_rows=True)]
-    if spec.lm_head_name is not None:
-        decls.append(TensorDecl(spec.lm_head_name, (spec.vocab_size, spec.hidden_size), ("normal", spec.init_std)))
+    decls = list(lookup("embedding", spec.embedding_kind).tensors(spec)) + list(lookup("head", spec.head_kind).tensors(spec))
     decls += lookup("norm", spec.final_norm.kind).tensors(spec.final_norm)
     for layer in spec.layers:
         decls += lookup("norm", layer.mixer_norm.kind).tensors(layer.mixer_norm)
@@ -47,9 +44,8 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], rt: Runtime, max_positions: int):
         self.spec, self.rt = spec, rt
         self.max_positions = int(min(max_positions, spec.max_positions))
-        self.embed = rt.param(tensors[spec.embed_name])
-        head = self.embed if spec.lm_head_name is None else rt.param(tensors[spec.lm_head_name])
-        self.lm_head = Linear(head, rt, "lm_head")
+        self.embedding = lookup("embedding", spec.embedding_kind)(spec, tensors, rt)
+        self.head = lookup("head", spec.head_kind)(spec, tensors, rt, self.embedding)
         self.final_norm = lookup("norm", spec.final_norm.kind)(spec.final_norm, tensors, rt)
         self._positions: Dict[tuple, object] = {}
         self.blocks = []
@@ -111,7 +107,7 @@ class DecoderModel:
 
         for b in self.blocks:
             visit([b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm])
-        visit([self.final_norm, self.lm_head])
+        visit([self.final_norm, self.head])
         return total
 
     def forward(self, step, cache, logits: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -125,7 +121,7 @@ class DecoderModel:
         n = step.n_tokens
         x = rt.buffer("model.x", (n, spec.hidden_size))
         h = rt.buffer("model.h", (n, spec.hidden_size))
-        ops.embed(x, self.embed, step.token_ids, self.status)
+        self.embedding.forward(step.token_ids, x, self.status)
         order = spec.order
         self.blocks[order[0]].input_norm.forward(x, h) if order else self.final_norm.forward(x, h)
         for occ, li in enumerate(order):
@@ -135,5 +131,5 @@ class DecoderModel:
             return None
         hw = rt.buffer("model.h_wanted", (step.n_want, spec.hidden_size))
         ops.gather_rows(hw, h, step.want_idx)
-        self.lm_head.forward(hw, logits, ops.EPI_F32_OUT)
+        self.head.forward(hw, logits)
         return logits

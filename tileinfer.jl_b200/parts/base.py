@@ -21,6 +21,9 @@ Interfaces (duck-typed; the base classes document them):
 * ``FeedForward(spec, tensors, rt)``: ``forward(h, step) -> delta``, token by token.
 * ``Block(layer_spec, mixer, feed_forward, mixer_norm, feed_forward_norm)``:
   ``forward(x, h, step, cache, next_norm, h_out)``.
+* ``Embedding(model_spec, tensors, rt)`` and ``Head(model_spec, tensors, rt, embedding)``: the two ends of the
+  model (``ModelSpec.embedding_kind`` / ``head_kind``), so that an embedding multiplier or a scaled or capped
+  logit is a registered part, not an edit of the decoder.
 
 Every class also has ``tensors(spec) -> [TensorDecl]``: the checkpoint tensors it reads,
 with shapes, used by the loader's checks and by the random-weights mode.
@@ -112,7 +115,25 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-_REGISTRIES: Dict[str, Dict[str, Any]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}
+class Embedding(Part):
+    """Token ids to the residual stream. ``__init__(spec: ModelSpec, tensors, rt)``; ``table`` is the matrix a tied
+    head shares; ``forward(token_ids, out, status)`` writes ``out`` [n, hidden] (``status``: a device word that
+    receives 1 + the index of a token whose id is outside the vocabulary)."""
+
+    def forward(self, token_ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """The final norm's output at the wanted rows to 32-bit logits. ``__init__(spec: ModelSpec, tensors, rt,
+    embedding)`` (the embedding part, whose table a tied head uses); ``forward(h, logits)``."""
+
+    def forward(self, h: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+_REGISTRIES: Dict[str, Dict[str, Any]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+                                          "embedding": {}, "head": {}}
 
 
 def _register(family: str, kind: str, cls):
@@ -138,6 +159,14 @@ def register_position(kind: str, cls=None):
 
 def register_block(kind: str, cls=None):
     return _register("block", kind, cls) if cls is not None else (lambda c: _register("block", kind, c))
+
+
+def register_embedding(kind: str, cls=None):
+    return _register("embedding", kind, cls) if cls is not None else (lambda c: _register("embedding", kind, c))
+
+
+def register_head(kind: str, cls=None):
+    return _register("head", kind, cls) if cls is not None else (lambda c: _register("head", kind, c))
 
 
 def lookup(family: str, kind: str):
