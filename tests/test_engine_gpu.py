@@ -278,6 +278,44 @@ def test_a_long_prompt_in_chunks_through_the_tensor_core_attention(dtype):
         eng.check_health()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_context_beyond_8192_positions_next_to_a_short_one(dtype):
+    """9,000 positions (past the 8,192 of Apertus-8B's rope scaling record, 141 pages) next to a sequence of 300:
+    the prompts go through in chunks of 2,048 tokens that attend to the earlier chunks' pages, then both
+    sequences decode together, where the fast path shares the decode attention's work slots out by length (the
+    long sequence is read by many blocks, the short one by one). In 32-bit a page that was skipped or read
+    twice would move the logits by far more than the bound; bfloat16 checks the fast kernels on the same data."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.weights import write_model_folder
+    cfg_dict = dict(helpers.TINY_D, max_position_embeddings=16384, num_hidden_layers=1,
+                    rope_scaling={"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 8192,
+                                  "low_freq_factor": 1.0, "high_freq_factor": 4.0})
+    with tempfile.TemporaryDirectory() as d:
+        folder = write_model_folder(ApertusConfig.from_dict(cfg_dict), 17, os.path.join(d, "m"))
+        pc, pw = plain.load_folder(folder)
+        long_, short = helpers.random_prompts(pc.vocab, [9020, 320], 19)
+        pdt = torch.float32 if dtype == "float32" else torch.bfloat16
+        want_long = [0, 2047, 2048, 8191, 8192, 8999]
+        ref_long, ref_short = plain.forward(pc, pw, long_, pdt), plain.forward(pc, pw, short, pdt)
+        eng = ti.Engine.load(folder, dtype=dtype, max_context=9088, max_seqs=2, max_tokens=9088 + 384, max_step_tokens=2048)
+        a, b = eng.new_sequence(), eng.new_sequence()
+        got = eng.step([(a, long_[:9000]), (b, short[:300])], [want_long, [0, 299]]).cpu()
+        tol_long, tol_short = tolerance(dtype, ref_long), tolerance(dtype, ref_short)
+        assert float((got[:6] - ref_long[want_long]).abs().max()) <= tol_long
+        assert float((got[6:] - ref_short[[0, 299]]).abs().max()) <= tol_short
+        for t in range(20):
+            row = eng.step([(a, [long_[9000 + t]]), (b, [short[300 + t]])]).cpu()
+            assert float((row[0] - ref_long[9000 + t]).abs().max()) <= tol_long, t
+            assert float((row[1] - ref_short[300 + t]).abs().max()) <= tol_short, t
+        if dtype == "bfloat16":
+            plan = eng.planner._layout(2, 2, 2)[1]["groups"][0].plan
+            work, seq = plan.tables(2, eng.planner._layout(2, 2, 2)[1]["groups"][0].plan_table)
+            parts = (seq.cpu() & 255).tolist()
+            assert parts[0] > parts[1] >= 1                     # the long sequence got most of the work slots
+        eng.check_health()
+
+
 def test_command_line(models, capsys):
     from tileinfer_b200.cli import cli
     folder, pc, pw = models["A"]

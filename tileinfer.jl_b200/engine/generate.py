@@ -129,12 +129,12 @@ def decode_batch(engine, sampler, sampling, live, slots, logits, results, max_ne
         for row, r in enumerate(live):
             if r in dead:
                 continue
-            verdict = finished(tokens[row], len(results[r]), max_new_tokens, stop)
-            if verdict != "stop":
+            outcome = finished(tokens[row], len(results[r]), max_new_tokens, stop)
+            if outcome != "stop":
                 results[r].append(tokens[row])
                 if on_token is not None:
                     on_token(r, tokens[row])
-            if verdict != "go":
+            if outcome != "go":
                 dead.add(r)
                 engine.free_sequence(slots.pop(r))
         live, logits = nxt, next_logits
