@@ -9,6 +9,7 @@
 // accumulation and one rounding (src/ops/reference.jl:23-26, src/ops/tile/linear.jl:12-13);
 // the logits leave in 32-bit after that rounding (src/ops/tile/linear.jl:26).
 #include "common.cuh"
+#include "mma_util.cuh"
 
 #define GP_BM 64      // tokens per tile
 #define GP_BN 64      // output features per tile
@@ -250,6 +251,93 @@ __global__ void __launch_bounds__(GV_ROWS * GV_SLOTS) gemv_plain_kernel(void* __
     }
 }
 
+// The weight-streaming kernel with its k blocks in flight: the same block shape and the same sums, but the
+// weight rows' and the tokens' k blocks are copied to shared memory with 16-byte cp.async several stages ahead
+// (raw, widened when they are read), so that a block has tens of kilobytes in flight instead of one k block.
+// It needs rows that can be read 16 bytes at a time; the kernel above serves the rest.
+template <typename T, int TPT, int STAGES>
+__global__ void __launch_bounds__(GV_ROWS * GV_SLOTS) gemv_plain_pipe_kernel(void* __restrict__ y, long long ldy, const T* x, long long ldx,
+                                                                              const T* __restrict__ W, int n, int out, int in, int epilogue,
+                                                                              XieluParams act) {
+    extern __shared__ __align__(16) unsigned char pipe_smem[];
+    constexpr int VEC = 16 / sizeof(T);                    // elements per 16-byte chunk
+    constexpr int CHUNKS = GV_BK / VEC;                    // chunks per row of a k block
+    constexpr int ROW = GV_BK + VEC;                       // elements between rows in shared memory (16 bytes of padding)
+    const int stage_elems = (GV_ROWS + n) * ROW;
+    T* stages = reinterpret_cast<T*>(pipe_smem);
+    const int tid = threadIdx.x;
+    const int row = tid % GV_ROWS, slot = tid / GV_ROWS;
+    const int m0 = blockIdx.x * GV_ROWS;
+    float acc[TPT];
+#pragma unroll
+    for (int j = 0; j < TPT; ++j) acc[j] = 0.f;
+    const int tiles = (in + GV_BK - 1) / GV_BK;
+    auto issue = [&](int tile) {
+        if (tile < tiles) {
+            T* ws = stages + (size_t)(tile % STAGES) * stage_elems;
+            T* xs = ws + GV_ROWS * ROW;
+            const int k0 = tile * GV_BK;
+            for (int i = tid; i < (GV_ROWS + n) * CHUNKS; i += GV_ROWS * GV_SLOTS) {
+                const int r = i / CHUNKS, k = k0 + (i % CHUNKS) * VEC;
+                T* dst = (r < GV_ROWS ? ws + r * ROW : xs + (r - GV_ROWS) * ROW) + (i % CHUNKS) * VEC;
+                const bool inside = k < in && (r >= GV_ROWS || m0 + r < out);      // in % VEC == 0: a chunk is inside the row or outside it
+                if (inside) cp_async16(smem_u32(dst), r < GV_ROWS ? W + (size_t)(m0 + r) * in + k : x + (size_t)(r - GV_ROWS) * ldx + k);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        cp_async_commit();
+    };
+    pdl_wait();
+    pdl_launch_dependents();
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    for (int tile = 0; tile < tiles; ++tile) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();                                   // this tile has landed, and the stage refilled below is no longer read
+        issue(tile + STAGES - 1);
+        const T* ws = stages + (size_t)(tile % STAGES) * stage_elems + row * ROW;
+        const T* xs = stages + (size_t)(tile % STAGES) * stage_elems + GV_ROWS * ROW;
+        const int kmax = min(GV_BK, in - tile * GV_BK);
+#pragma unroll 4
+        for (int kk = 0; kk < kmax; ++kk) {
+            const float w = to_f32(ws[kk]);
+#pragma unroll
+            for (int j = 0; j < TPT; ++j) {
+                const int t = slot + j * GV_SLOTS;
+                if (t < n) acc[j] = fmaf(to_f32(xs[t * ROW + kk]), w, acc[j]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    const int c = m0 + row;
+    if (c >= out) return;
+#pragma unroll
+    for (int j = 0; j < TPT; ++j) {
+        const int t = slot + j * GV_SLOTS;
+        if (t >= n) continue;
+        float v = rnd<T>(acc[j]);
+        if (epilogue == TI_EPI_XIELU) v = xielu_value<T>(v, act);
+        if (epilogue == TI_EPI_F32_OUT) ((float*)y)[(size_t)t * ldy + c] = v;
+        else ((T*)y)[(size_t)t * ldy + c] = from_f32<T>(v);
+    }
+}
+
+template <typename T, int TPT, int STAGES>
+static int launch_gemv_pipe(void* y, long long ldy, const T* x, long long ldx, const T* W, int n, int out, int in, int epilogue,
+                            const XieluParams& act, cudaStream_t stream) {
+    constexpr int VEC = 16 / sizeof(T);
+    const size_t smem = (size_t)STAGES * (GV_ROWS + n) * (GV_BK + VEC) * sizeof(T);
+    static size_t configured = 0;
+    if (smem > configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemv_plain_pipe_kernel<T, TPT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(STAGES * (GV_ROWS + TPT * GV_SLOTS) * (GV_BK + VEC) * sizeof(T)));
+        if (e != cudaSuccess) return ti_fail("gemv_plain: %s", cudaGetErrorString(e));
+        configured = STAGES * (GV_ROWS + TPT * GV_SLOTS) * (GV_BK + VEC) * sizeof(T);
+    }
+    ti_launch(gemv_plain_pipe_kernel<T, TPT, STAGES>, dim3((out + GV_ROWS - 1) / GV_ROWS), dim3(GV_ROWS * GV_SLOTS), smem, stream, y, ldy, x, ldx, W, n,
+              out, in, epilogue, act);
+    return ti_check_launch("gemv_plain");
+}
+
 extern "C" int ti_gemm_plain(void* y, long long ldy, const void* x, long long ldx, const void* W, int n, int out, int in,
                              int epilogue, float alpha_p, float alpha_n, float beta, float eps, int dtype,
                              cudaStream_t stream) {
@@ -260,6 +348,15 @@ extern "C" int ti_gemm_plain(void* y, long long ldy, const void* x, long long ld
     TI_REQUIRE(grid.y <= 65535, "gemm: too many rows (%d) for one launch", n);
     XieluParams act{alpha_p, alpha_n, beta, eps};
     if (n <= GV_MAX_TOKENS) {                              // few tokens: the weight-streaming form (same sums, bit for bit)
+        const int vec = dtype == TI_F32 ? 4 : 8;           // elements of a 16-byte chunk
+        if (in % vec == 0 && ldx % vec == 0 && aligned16(x) && aligned16(W)) {
+            TI_DISPATCH_DTYPE(dtype, {
+                if (n <= GV_SLOTS) return launch_gemv_pipe<T, 1, 8>(y, ldy, (const T*)x, ldx, (const T*)W, n, out, in, epilogue, act, stream);
+                if (n <= 2 * GV_SLOTS) return launch_gemv_pipe<T, 2, 6>(y, ldy, (const T*)x, ldx, (const T*)W, n, out, in, epilogue, act, stream);
+                if (n <= 4 * GV_SLOTS) return launch_gemv_pipe<T, 4, 4>(y, ldy, (const T*)x, ldx, (const T*)W, n, out, in, epilogue, act, stream);
+                return launch_gemv_pipe<T, 8, 3>(y, ldy, (const T*)x, ldx, (const T*)W, n, out, in, epilogue, act, stream);
+            });
+        }
         const size_t smem = (size_t)n * (GV_BK + 1) * sizeof(float);
         const dim3 blocks((out + GV_ROWS - 1) / GV_ROWS), threads(GV_ROWS * GV_SLOTS);
 #define GV_LAUNCH(TPT) ti_launch(gemv_plain_kernel<T, TPT>, blocks, threads, smem, stream, y, ldy, (const T*)x, ldx, (const T*)W, n, out, in, epilogue, act)
