@@ -297,14 +297,22 @@ __global__ void __launch_bounds__(GV_ROWS * GV_SLOTS) gemv_plain_pipe_kernel(voi
         issue(tile + STAGES - 1);
         const T* ws = stages + (size_t)(tile % STAGES) * stage_elems + row * ROW;
         const T* xs = stages + (size_t)(tile % STAGES) * stage_elems + GV_ROWS * ROW;
-        const int kmax = min(GV_BK, in - tile * GV_BK);
-#pragma unroll 4
-        for (int kk = 0; kk < kmax; ++kk) {
-            const float w = to_f32(ws[kk]);
+        const int chunks = min(GV_BK, in - tile * GV_BK) / VEC;      // in % VEC == 0
+        // 16 bytes of the row and of each token at a time (shared-memory reads, not arithmetic, bound this loop);
+        // the k terms are still added one by one in ascending order.
+#pragma unroll 2
+        for (int c = 0; c < chunks; ++c) {
+            Vec16<T> w;
+            w.load(ws + c * VEC);
 #pragma unroll
             for (int j = 0; j < TPT; ++j) {
                 const int t = slot + j * GV_SLOTS;
-                if (t < n) acc[j] = fmaf(to_f32(xs[t * ROW + kk]), w, acc[j]);
+                if (t < n) {
+                    Vec16<T> xv;
+                    xv.load(xs + t * ROW + c * VEC);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) acc[j] = fmaf(xv.v[e], w.v[e], acc[j]);
+                }
             }
         }
     }
