@@ -686,3 +686,39 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_goes_on(ops):
     assert rc == 0
     close(y, rnd((x.double() @ w.double().t()).float(), torch.bfloat16), torch.bfloat16, ulps=1.0)
     fast.check_status()
+
+
+def test_new_pages_reach_the_device_table_and_their_values_are_zeroed(ops):
+    """The cache's books (C++) write a fresh page's block-table entry to the device and zero its VALUES in every
+    layer of the group with one kernel; keys and pages that were not taken are left alone. Many pages at once
+    (more than one launch's worth of writes), two groups, slots given back and taken again."""
+    from tileinfer_b200.cache import Cache
+    from tileinfer_b200.parts import CacheRequest
+    reqs = [CacheRequest("paged_kv", kv_heads=2, head_dim=16), CacheRequest("paged_kv", kv_heads=2, head_dim=16),
+            CacheRequest("paged_kv", kv_heads=1, head_dim=48), CacheRequest("paged_kv", kv_heads=2, head_dim=16)]
+    cache = Cache(reqs, torch.bfloat16, "cuda", max_tokens=64 * 200, max_seqs=4, page_size=64)
+    assert [g.layers for g in cache.paged_groups] == [[0, 1, 3], [2]]
+    for g in cache.paged_groups:
+        g.k.fill_(float("nan")); g.v.fill_(float("nan"))
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    cache.reserve([(a, 64 * 150 + 1), (b, 70)])                 # 151 + 2 pages: three launches of writes per group
+    torch.cuda.synchronize()
+    for g in cache.paged_groups:
+        assert torch.equal(g.device_table.cpu(), g.host_table)
+        taken = torch.tensor(sorted(p for t in g.tables.values() for p in t))
+        assert len(taken) == 153 and g.pages.held == 153
+        free = torch.tensor([p for p in range(g.num_pages) if not g.pages.is_held(p)])
+        assert float(g.v[:, taken].float().abs().sum()) == 0.0                      # zeroed in every layer of the group
+        assert bool(torch.isnan(g.v[:, free].float()).all()) and bool(torch.isnan(g.k.float()).all())
+    cache.advance(a, 64 * 150 + 1); cache.advance(b, 70)
+    cache.free_slot(a)
+    for g in cache.paged_groups:
+        g.v.fill_(float("nan"))
+    c = cache.alloc_slot()
+    assert c == a
+    cache.reserve([(c, 65)])                                    # the lowest free pages again: they were a's
+    torch.cuda.synchronize()
+    for g in cache.paged_groups:
+        pages = torch.tensor(g.tables[c])
+        assert g.tables[c] == [0, 1] and torch.equal(g.device_table[c, :2].cpu(), pages.int())
+        assert float(g.v[:, pages].float().abs().sum()) == 0.0 and bool(torch.isnan(g.v[:, torch.tensor(g.tables[b])].float()).all())
