@@ -104,8 +104,12 @@ __global__ void attention_inputs_kernel(const T* qkv, long long qkv_stride, cons
 // The same for head sizes 64 and 128 in bfloat16: a lane owns VPL = D/32
 // consecutive elements (one 4- or 8-byte access), the rotation partner i +- D/2 lives in lane +- 16 and
 // comes by shuffle, so no shared memory and no strided loops are needed.
+//
+// With several heads per warp (a prompt's step) the kernel is bound by how many loads are in flight, so it is held to
+// 64 registers for eight blocks per SM (21.5 against 24.8 us for 2,048 tokens of 32 + 8 + 8 heads of 128).
 template <int VPL, int HPW>
-__global__ void attention_inputs_vec_kernel(const bf16* qkv, long long qkv_stride, const float* partials, int n_partials,
+__global__ void __launch_bounds__(AI_WARPS * 32, HPW >= 4 ? 8 : 1)
+attention_inputs_vec_kernel(const bf16* qkv, long long qkv_stride, const float* partials, int n_partials,
                                             long long partial_stride, bf16* __restrict__ q_out,
                                             bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                             const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float eps,

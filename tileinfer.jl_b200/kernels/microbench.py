@@ -5,6 +5,8 @@
     python -m tileinfer_b200.kernels.microbench gemmd   --out 21504 --in 4096 --tokens 64 [--tile 160] [--splits S]
     python -m tileinfer_b200.kernels.microbench decode  --batch 8 --context 1024
     python -m tileinfer_b200.kernels.microbench prefill --tokens 2048 [--kernel mma]
+    python -m tileinfer_b200.kernels.microbench inputs  --tokens 2048     (q/k norm + rotation + cache write)
+    python -m tileinfer_b200.kernels.microbench addnorm --tokens 2048     (residual add + RMSNorm)
     python -m tileinfer_b200.kernels.microbench timeline --batch 1 --layers 8
     python -m tileinfer_b200.kernels.microbench timeline --tokens 2048 --layers 4      (a prefill step)
 
@@ -158,6 +160,53 @@ def bench_prefill_attention(tokens, once, kernel="tc", heads=32, kv_heads=8, hea
     print(f"prefill attention ({kernel}) tokens={tokens}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s (causal)")
 
 
+def bench_attention_inputs(tokens, once, heads=32, kv_heads=8, head_dim=128):
+    """Per-head q/k norm + rotation + cache write of ``tokens`` tokens of one sequence (a prefill step's kernel)."""
+    from types import SimpleNamespace
+
+    from . import ops
+    F = (heads + 2 * kv_heads) * head_dim
+    pages = -(-tokens // 64)
+    # Rotating inputs, as the step's activations are new every layer (they come from L2 or HBM, not from L1).
+    qkvs = [torch.randn(tokens, F, device="cuda").to(torch.bfloat16) for _ in range(4)]
+    q = torch.empty(tokens, heads, head_dim, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(pages, kv_heads, 64, head_dim, dtype=torch.bfloat16, device="cuda")
+    v = torch.zeros_like(k)
+    qn = torch.ones(head_dim, dtype=torch.bfloat16, device="cuda")
+    kn = torch.ones(head_dim, dtype=torch.bfloat16, device="cuda")
+    table = torch.randn(tokens, head_dim // 2, 2, device="cuda")
+    rotation = SimpleNamespace(cos_sin=table, rotary_dim=head_dim, interleaved=False)
+    pos = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    calls = [(lambda x=x: ops.attention_inputs(x, q, k, v, qn, kn, 1e-5, rotation, pos, pos, heads, kv_heads, head_dim, 64)) for x in qkvs]
+    if once:
+        for c in calls[:3]:
+            c()
+        torch.cuda.synchronize()
+        print("launched 3 attention-inputs kernels")
+        return
+    ms = _graph_time(calls)
+    nbytes = tokens * F * 2 * 2
+    print(f"attention inputs tokens={tokens}: {ms * 1e3:.1f} us, {nbytes / ms / 1e6:.0f} GB/s read + written")
+
+
+def bench_add_norm(tokens, once, hidden=4096):
+    """Residual add + RMSNorm of ``tokens`` rows (a prefill step's kernel): reads x and delta, writes x and h."""
+    from . import ops
+    xs = [torch.randn(tokens, hidden, device="cuda").to(torch.bfloat16) for _ in range(4)]
+    ds = [torch.randn(tokens, hidden, device="cuda").to(torch.bfloat16) for _ in range(4)]
+    h = torch.empty(tokens, hidden, dtype=torch.bfloat16, device="cuda")
+    w = torch.ones(hidden, dtype=torch.bfloat16, device="cuda")
+    calls = [(lambda x=x, d=d: ops.add_rmsnorm(x, d, w, h, 1e-5)) for x, d in zip(xs, ds)]
+    if once:
+        for c in calls[:3]:
+            c()
+        torch.cuda.synchronize()
+        print("launched 3 add + norm kernels")
+        return
+    ms = _graph_time(calls)
+    print(f"add + norm tokens={tokens}: {ms * 1e3:.1f} us, {tokens * hidden * 2 * 4 / ms / 1e6:.0f} GB/s read + written")
+
+
 def timeline(batch, layers, cached=1023, prefill_tokens=0):
     from torch.profiler import ProfilerActivity, profile
 
@@ -218,7 +267,7 @@ def timeline(batch, layers, cached=1023, prefill_tokens=0):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench")
-    ap.add_argument("what", choices=["gemv", "gemm", "gemmd", "decode", "prefill", "timeline"])
+    ap.add_argument("what", choices=["gemv", "gemm", "gemmd", "decode", "prefill", "inputs", "addnorm", "timeline"])
     ap.add_argument("--out", type=int, default=21504)
     ap.add_argument("--in", dest="k", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=1)
@@ -241,6 +290,10 @@ def main(argv=None):
         bench_decode_attention(a.batch, a.context, a.once, a.splits)
     elif a.what == "prefill":
         bench_prefill_attention(a.tokens if a.tokens > 1 else 2048, a.once, a.kernel)
+    elif a.what == "inputs":
+        bench_attention_inputs(a.tokens if a.tokens > 1 else 2048, a.once)
+    elif a.what == "addnorm":
+        bench_add_norm(a.tokens if a.tokens > 1 else 2048, a.once)
     else:
         timeline(a.batch, a.layers, prefill_tokens=a.tokens if a.tokens > 1 else 0)
     return 0
