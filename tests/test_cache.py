@@ -107,6 +107,50 @@ def test_groups_by_need_have_their_own_storage():
         c.reserve([(s, 4)]); c.advance(s, 4); c.truncate(s, 2)
 
 
+def test_a_third_kind_of_storage_is_registered_not_edited_in():
+    """A kind of per-sequence storage defined HERE (a pair of tensors per layer and slot, marked as started with -1,
+    able to roll back) is registered, built next to a paged group, started with every new sequence and handed to
+    its layers; an unregistered kind is refused by name."""
+    from tileinfer_b200.cache import LayerCache, register_cache_kind
+
+    @register_cache_kind("toy_pair")
+    class PairGroup:
+        paged, rolls_back = False, True
+
+        @classmethod
+        def create(cls, cache, index, request, layers):
+            g = cls()
+            g.index, g.request, g.layers = index, request, layers
+            g.a = torch.zeros((len(layers), cache.max_seqs) + tuple(request.shape))
+            g.b = torch.zeros((len(layers), cache.max_seqs), dtype=torch.int64)
+            g.started = []
+            return g
+
+        def views(self):
+            return [LayerCache(self.index, self.kind, extra=(self.a[j], self.b[j])) for j in range(len(self.layers))]
+
+        def start(self, slot):
+            self.a[:, slot] = -1.0
+            self.b[:, slot] = 0
+            self.started.append(slot)
+
+    reqs = [kv(), CacheRequest("toy_pair", shape=(3,)), kv(), CacheRequest("toy_pair", shape=(3,))]
+    c = Cache(reqs, torch.float32, "cpu", max_tokens=32, max_seqs=2, page_size=4)
+    paged, pair = c.groups
+    assert paged.layers == [0, 2] and pair.layers == [1, 3] and pair.kind == "toy_pair"
+    assert c.paged_groups == [paged] and c.layer(3).kind == "toy_pair"
+    a, b = c.layer(3).extra
+    assert a.data_ptr() == pair.a[1].data_ptr() and b.shape == (2,)
+    s = c.alloc_slot()
+    assert pair.started == [s] and float(a[s].sum()) == -3.0
+    c.reserve([(s, 6)]); c.advance(s, 6); c.truncate(s, 2)                 # this kind rolls back: the books allow it
+    assert c.length(s) == 2
+    c.free_slot(s)
+    assert c.alloc_slot() == s and pair.started == [s, s]
+    with pytest.raises(ValueError, match="unknown cache kind 'ring'.*toy_pair"):
+        Cache([kv(), CacheRequest("ring")], torch.float32, "cpu", max_tokens=32, max_seqs=2, page_size=4)
+
+
 def test_random_traffic_keeps_the_books_straight():
     rng = random.Random(0)
     c = make(max_tokens=64 * 4, max_seqs=6)

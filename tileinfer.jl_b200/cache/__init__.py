@@ -1,2 +1,2 @@
 from .allocator import NumberPool, OutOfPagesError, OutOfSlotsError
-from .kv_cache import DEFAULT_PAGE_SIZE, Cache, LayerCache, PagedGroup, StateGroup
+from .kv_cache import DEFAULT_PAGE_SIZE, Cache, LayerCache, PagedGroup, StateGroup, register_cache_kind

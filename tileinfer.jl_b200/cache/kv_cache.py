@@ -51,6 +51,24 @@ class LayerCache:
     k: Optional[torch.Tensor] = None        # [pages, kv_heads, page_size, head_dim]
     v: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None    # [slots, *shape]
+    extra: object = None                    # whatever a registered kind of its own hands to its mixer
+
+
+# The kinds of storage a CacheRequest can name. A group class has
+#   create(cache, index, request, layers) -> group   (classmethod; `layers` are the layers with this request)
+#   views() -> [LayerCache]                           one per layer, in the order of `layers`
+#   start(slot)                                       a sequence begins in `slot` (clear what the last one left)
+#   paged                                             True only for storage in pages, which the books and the step planner handle
+#   rolls_back                                        False if a sequence cannot be cut back to an earlier length
+_GROUP_KINDS: Dict[str, type] = {}
+
+
+def register_cache_kind(name: str):
+    def deco(cls):
+        cls.kind = name
+        _GROUP_KINDS[name] = cls
+        return cls
+    return deco
 
 
 def _stream(device) -> Optional[int]:
@@ -78,8 +96,29 @@ class _Pages:
         return bool(self._g._api.group_page_is_held(self._g._book, self._g.book_index, page))
 
 
+@register_cache_kind("paged_kv")
 class PagedGroup:
-    kind = "paged_kv"
+    paged, rolls_back = True, True
+
+    @classmethod
+    def create(cls, cache, index, request, layers):
+        pages = cache.num_pages
+        if request.window and cache.max_step_tokens:
+            # Each sequence: the pages that its window touches, the release unit's slack and the
+            # page that it writes to; plus the tokens of one step.
+            per_seq = -(-(request.window - 1) // cache.page_size) + cache.release_granule + 1
+            pages = min(pages, cache.max_seqs * per_seq + -(-cache.max_step_tokens // cache.page_size))
+        max_pages_per_seq = -(-cache.max_seq_len // cache.page_size)
+        bi = cache._api.cache_add_group(cache._book, pages, cache.page_size, request.window or 0, cache.release_granule,
+                                        max_pages_per_seq)
+        return cls(index, cache._book, bi, request, layers, pages, cache.page_size, cache.max_seqs, max_pages_per_seq,
+                   cache.dtype, cache.device, cache.release_granule)
+
+    def views(self):
+        return [LayerCache(self.index, self.kind, self.page_size, self.k[j], self.v[j]) for j in range(len(self.layers))]
+
+    def start(self, slot: int) -> None:
+        pass                                   # fresh pages are zeroed as they are handed out
 
     def __init__(self, index, book, book_index, request: CacheRequest, layers: List[int], num_pages: int, page_size: int,
                  max_seqs: int, max_pages_per_seq: int, dtype, device, release_granule: int = 1):
@@ -141,12 +180,23 @@ class PagedGroup:
         return 2 * len(self.layers) * r.kv_heads * r.head_dim * self.k.element_size()
 
 
+@register_cache_kind("state")
 class StateGroup:
-    kind = "state"
+    paged, rolls_back = False, False
+
+    @classmethod
+    def create(cls, cache, index, request, layers):
+        return cls(index, request, layers, cache.max_seqs, cache.dtype, cache.device)
 
     def __init__(self, index, request: CacheRequest, layers: List[int], max_seqs: int, dtype, device):
         self.index, self.request, self.layers = index, request, layers
         self.state = torch.zeros((len(layers), max_seqs) + tuple(request.shape), dtype=request.dtype or dtype, device=device)
+
+    def views(self):
+        return [LayerCache(self.index, self.kind, state=self.state[j]) for j in range(len(self.layers))]
+
+    def start(self, slot: int) -> None:
+        self.state[:, slot].zero_()
 
 
 class _Slots:
@@ -183,43 +233,30 @@ class Cache:
         self.max_tokens = self.num_pages * page_size
         self.max_seq_len = min(max_seq_len or self.max_tokens, self.max_tokens)
         self.max_step_tokens = max_step_tokens
-        max_pages_per_seq = -(-self.max_seq_len // page_size)
+        self.release_granule = release_granule
         by_key: Dict[tuple, List[int]] = {}
         for i, r in enumerate(requests):
             if r is not None:
                 by_key.setdefault(r.group_key(), []).append(i)
         kinds = {requests[layers[0]].kind for layers in by_key.values()}
-        if kinds - {"paged_kv", "state"}:
-            raise ValueError(f"unknown cache kind {sorted(kinds - {'paged_kv', 'state'})[0]}")
+        for kind in sorted(kinds):
+            if kind not in _GROUP_KINDS:
+                raise ValueError(f"unknown cache kind {kind!r} (registered: {', '.join(sorted(_GROUP_KINDS))})")
         self._api = host.api()
-        self._book = self._api.cache_create(max_seqs, self.max_seq_len, int("state" in kinds))
+        self._book = self._api.cache_create(max_seqs, self.max_seq_len, int(any(not _GROUP_KINDS[k].rolls_back for k in kinds)))
         self.slots = _Slots(self)
         self.groups = []
         self._layer_view: Dict[int, LayerCache] = {}
         for key, layers in by_key.items():
             r = requests[layers[0]]
-            gi = len(self.groups)
-            if r.kind == "paged_kv":
-                pages = self.num_pages
-                if r.window and max_step_tokens:
-                    # Each sequence: the pages that its window touches, the release unit's slack and the
-                    # page that it writes to; plus the tokens of one step.
-                    per_seq = -(-(r.window - 1) // page_size) + release_granule + 1
-                    pages = min(pages, max_seqs * per_seq + -(-max_step_tokens // page_size))
-                bi = self._api.cache_add_group(self._book, pages, page_size, r.window or 0, release_granule, max_pages_per_seq)
-                g = PagedGroup(gi, self._book, bi, r, layers, pages, page_size, max_seqs, max_pages_per_seq, dtype, device,
-                               release_granule)
-                for j, l in enumerate(layers):
-                    self._layer_view[l] = LayerCache(gi, "paged_kv", page_size, g.k[j], g.v[j])
-            else:
-                g = StateGroup(gi, r, layers, max_seqs, dtype, device)
-                for j, l in enumerate(layers):
-                    self._layer_view[l] = LayerCache(gi, "state", state=g.state[j])
+            g = _GROUP_KINDS[r.kind].create(self, len(self.groups), r, layers)
+            for l, view in zip(layers, g.views()):
+                self._layer_view[l] = view
             self.groups.append(g)
         for reader, source in (share or {}).items():
             self._layer_view[reader] = self._layer_view[source]
-        self.paged_groups = [g for g in self.groups if g.kind == "paged_kv"]
-        self.state_groups = [g for g in self.groups if g.kind == "state"]
+        self.paged_groups = [g for g in self.groups if g.paged]
+        self.state_groups = [g for g in self.groups if not g.paged]
         self.windowed_groups = [g for g in self.paged_groups if g.window]
 
     def __del__(self):
@@ -240,8 +277,8 @@ class Cache:
         slot = self._api.cache_alloc_slot(self._book)
         if slot < 0:
             raise OutOfSlotsError(f"no free sequence slot (all {self.max_seqs} are held)")
-        for g in self.state_groups:
-            g.state[:, slot].zero_()
+        for g in self.groups:
+            g.start(slot)
         return slot
 
     def free_slot(self, slot: int) -> None:

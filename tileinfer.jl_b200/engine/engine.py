@@ -64,7 +64,7 @@ class Engine:
         asked = set()
         for occ, li in enumerate(self.spec.order):
             view = self.cache.layer(occ) if occ in self.cache._layer_view else None
-            if view is None or view.kind != "paged_kv" or view.group_index in asked:
+            if view is None or not self.cache.groups[view.group_index].paged or view.group_index in asked:
                 continue
             asked.add(view.group_index)
             mixer = self.model.blocks[li].mixer

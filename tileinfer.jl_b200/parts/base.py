@@ -44,7 +44,8 @@ class CacheRequest:
 
     ``kind == "paged_kv"``: keys and values of every position (or of the last ``window``),
     ``kv_heads × head_dim`` each, in pages. ``kind == "state"``: a tensor of fixed ``shape``
-    and ``dtype`` per sequence, zeroed when a sequence starts.
+    and ``dtype`` per sequence, zeroed when a sequence starts. Any other kind is one that was
+    registered with ``cache.register_cache_kind``; its group class reads what it needs from these fields.
     """
     kind: str
     kv_heads: int = 0
