@@ -433,3 +433,13 @@ def test_every_size_is_taken_or_handed_to_a_kernel_that_takes_it(case, dtype):
             for i, (ref, h) in enumerate(zip(refs, head)):
                 assert float((out[i] - ref[h + t]).abs().max()) <= tolerance(dtype, ref), (t, i)
         eng.check_health()
+
+
+def test_a_head_size_the_kernels_do_not_take_is_refused_when_the_model_is_built():
+    """No kernel takes heads above 512 or of odd size: building the model says so, before any step runs."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.config import ApertusConfig
+    for head_dim in (528, 1024):
+        cfg = ApertusConfig.from_dict(_odd(hidden_size=64, num_attention_heads=2, num_key_value_heads=1, head_dim=head_dim))
+        with pytest.raises(ValueError, match=f"head size {head_dim}"):
+            ti.Engine.random(cfg, 0, dtype="float32", max_context=64, max_seqs=1, max_tokens=64)

@@ -16,6 +16,7 @@ from .library import KernelError, check, lib
 
 F32, BF16 = 0, 1
 EPI_NONE, EPI_XIELU, EPI_F32_OUT = 0, 1, 2
+MAX_HEAD_DIM = 512      # the largest head the attention kernels take (csrc/attention_inputs.cu, csrc/attention_plain.cu)
 
 
 def dtype_code(dtype: torch.dtype) -> int:

@@ -21,6 +21,10 @@ from .linear import Linear
 class Attention(Mixer):
     def __init__(self, spec: MixerSpec, tensors, rt, position):
         self.spec, self.rt, self.position = spec, rt, position
+        if spec.head_dim < 2 or spec.head_dim % 2 or spec.head_dim > ops.MAX_HEAD_DIM:
+            raise ValueError(f"attention: head size {spec.head_dim} is not one the kernels take (even, at most {ops.MAX_HEAD_DIM})")
+        if spec.num_kv_heads < 1 or spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"attention: {spec.num_heads} query heads do not divide into {spec.num_kv_heads} KV heads")
         n = spec.tensor_names
         p = spec.prefix
         wq, wk, wv = (rt.param(tensors[p + n[k]]) for k in ("q", "k", "v"))
