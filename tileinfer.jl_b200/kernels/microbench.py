@@ -7,6 +7,7 @@
     python -m tileinfer_b200.kernels.microbench prefill --tokens 2048 [--kernel mma]
     python -m tileinfer_b200.kernels.microbench inputs  --tokens 2048     (q/k norm + rotation + cache write)
     python -m tileinfer_b200.kernels.microbench addnorm --tokens 2048     (residual add + RMSNorm)
+    python -m tileinfer_b200.kernels.microbench sampling --batch 8 [--out VOCAB]   (greedy and sampled choice of a token)
     python -m tileinfer_b200.kernels.microbench timeline --batch 1 --layers 8
     python -m tileinfer_b200.kernels.microbench timeline --tokens 2048 --layers 4      (a prefill step)
 
@@ -207,6 +208,31 @@ def bench_add_norm(tokens, once, hidden=4096):
     print(f"add + norm tokens={tokens}: {ms * 1e3:.1f} us, {tokens * hidden * 2 * 4 / ms / 1e6:.0f} GB/s read + written")
 
 
+def bench_sampling(batch, vocab, once):
+    """The choice of a token from 32-bit logits of ``batch`` rows: greedy, and by temperature with and without
+    top-k / top-p (logits of a spread that a model's have: normal, scaled by 3)."""
+    from . import ops
+    logits = [(3 * torch.randn(batch, vocab, device="cuda")).contiguous() for _ in range(4)]
+    out = torch.empty(batch, dtype=torch.int32, device="cuda")
+    seeds = torch.arange(batch, dtype=torch.int32, device="cuda")
+    counters = torch.zeros(batch, dtype=torch.int32, device="cuda")
+    ws = ops.argmax_workspace(batch, vocab, "cuda")
+    kinds = {"greedy": lambda l: ops.argmax(l, out, ws),
+             "temperature 0.8": lambda l: ops.sample(l, out, 0.8, 0, 1.0, seeds, counters),
+             "temperature 1.0, top-k 40, top-p 0.9": lambda l: ops.sample(l, out, 1.0, 40, 0.9, seeds, counters)}
+    for name, f in kinds.items():
+        calls = [(lambda l=l: f(l)) for l in logits]
+        if once:
+            for c in calls[:3]:
+                c()
+            torch.cuda.synchronize()
+            continue
+        ms = _graph_time(calls)
+        print(f"{name}: batch {batch}, vocabulary {vocab}: {ms * 1e3:.1f} us ({batch * vocab * 4 / ms / 1e6:.0f} GB/s of logits)")
+    if once:
+        print("launched 3 kernels of each kind")
+
+
 def timeline(batch, layers, cached=1023, prefill_tokens=0):
     from torch.profiler import ProfilerActivity, profile
 
@@ -267,7 +293,7 @@ def timeline(batch, layers, cached=1023, prefill_tokens=0):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="microbench")
-    ap.add_argument("what", choices=["gemv", "gemm", "gemmd", "decode", "prefill", "inputs", "addnorm", "timeline"])
+    ap.add_argument("what", choices=["gemv", "gemm", "gemmd", "decode", "prefill", "inputs", "addnorm", "sampling", "timeline"])
     ap.add_argument("--out", type=int, default=21504)
     ap.add_argument("--in", dest="k", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=1)
@@ -294,6 +320,8 @@ def main(argv=None):
         bench_attention_inputs(a.tokens if a.tokens > 1 else 2048, a.once)
     elif a.what == "addnorm":
         bench_add_norm(a.tokens if a.tokens > 1 else 2048, a.once)
+    elif a.what == "sampling":
+        bench_sampling(a.batch, a.out if a.out != 21504 else 131072, a.once)
     else:
         timeline(a.batch, a.layers, prefill_tokens=a.tokens if a.tokens > 1 else 0)
     return 0
