@@ -213,64 +213,58 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer (TMA)
-        // The whole warp walks the loop (so that it reaches the final barrier converged); lane 0 issues.
+        // ONE thread walks the loop: a wait that the whole warp executes costs 32 barrier tests and a vote
+        // per k block, which at 64 of k per stage is more than the copy it guards.
         int stage = 0;
         unsigned phase = 0;
         bool ok = true;
         int issued = 0;                                     // k blocks of this block so far
-        while (ok && it.next(p)) {
+        while (lane == 0 && ok && it.next(p)) {
             for (int kb = it.kb_lo; kb < it.kb_hi; ++kb, ++issued) {
-                ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1));
+                ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1);
                 if (!ok) break;
-                if (lane == 0) {
-                    const unsigned bar = full0 + 8 * stage;
-                    const unsigned a_dst = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
-                    if (issued >= ahead) {                  // else the weights of this stage are already on their way
-                        mbar_expect_tx(bar, C::STAGE_BYTES);
+                const unsigned bar = full0 + 8 * stage;
+                const unsigned a_dst = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
+                if (issued >= ahead) {                      // else the weights of this stage are already on their way
+                    mbar_expect_tx(bar, C::STAGE_BYTES);
 #pragma unroll
-                        for (int h = 0; h < MT; ++h)
-                            tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, kb * BK, (it.m * MT + h) * BM, bar);
-                    }
-                    tma_load_2d(a_dst + C::A_BYTES, &map_x, kb * BK, it.n * BN, bar);
+                    for (int h = 0; h < MT; ++h)
+                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, kb * BK, (it.m * MT + h) * BM, bar);
                 }
-                __syncwarp();
+                tma_load_2d(a_dst + C::A_BYTES, &map_x, kb * BK, it.n * BN, bar);
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
         }
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer (lane 0 issues)
+        // ---------------------------------------------------------------- MMA issuer (one thread)
         int stage = 0;
         unsigned phase = 0;
         int local = 0;
         bool ok = true;
-        while (ok && it.next(p)) {
+        while (lane == 0 && ok && it.next(p)) {
             const int acc = C::ACC_BUFS == 2 ? (local & 1) : 0;
             const unsigned acc_phase = C::ACC_BUFS == 2 ? ((local >> 1) & 1) : (local & 1);
-            ok = __all_sync(0xffffffffu, mbar_wait(acce0 + 8 * acc, acc_phase ^ 1, p.status, 2));
+            ok = mbar_wait(acce0 + 8 * acc, acc_phase ^ 1, p.status, 2);
             if (!ok) break;
             tc_fence_after();
             const unsigned d_tmem = tmem_base + (unsigned)(acc * MT * BN);
             for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
-                ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, p.status, 3));
+                ok = mbar_wait(full0 + 8 * stage, phase, p.status, 3);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
-                    const unsigned a_addr = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
-                    const unsigned long long db = smem_desc_sw128(a_addr + C::A_BYTES);
+                const unsigned a_addr = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
+                const unsigned long long db = smem_desc_sw128(a_addr + C::A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)      // 16 k = 32 bytes further along the swizzled row
+                for (int k = 0; k < BK / 16; ++k)          // 16 k = 32 bytes further along the swizzled row
 #pragma unroll
-                        for (int h = 0; h < MT; ++h)       // the sub-tiles share the token operand
-                            umma_bf16(d_tmem + (unsigned)(h * BN), smem_desc_sw128(a_addr + h * (BM * BK * 2)) + (unsigned long long)(2 * k),
-                                      db + (unsigned long long)(2 * k), instr_desc<BN>(), (kb > it.kb_lo || k > 0) ? 1u : 0u);
-                    umma_commit(empty0 + 8 * stage);       // the stage is free once these MMAs have read it
-                }
-                __syncwarp();
+                    for (int h = 0; h < MT; ++h)           // the sub-tiles share the token operand
+                        umma_bf16(d_tmem + (unsigned)(h * BN), smem_desc_sw128(a_addr + h * (BM * BK * 2)) + (unsigned long long)(2 * k),
+                                  db + (unsigned long long)(2 * k), instr_desc<BN>(), (kb > it.kb_lo || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * stage);           // the stage is free once these MMAs have read it
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
-            if (lane == 0) umma_commit(accf0 + 8 * acc);   // the accumulator is complete
-            __syncwarp();
+            umma_commit(accf0 + 8 * acc);                  // the accumulator is complete
             ++local;
         }
     } else {
@@ -418,22 +412,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         int stage = 0;
         unsigned phase = 0;
         bool ok = true;
-        while (ok && it.next(p)) {
+        while (lane == 0 && ok && it.next(p)) {             // one thread: see the producer of the kernel above
             for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
-                ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1));
+                ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1);
                 if (!ok) break;
-                if (lane == 0) {
-                    if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * C::STAGE_BYTES);
-                    const unsigned bar = map_to_block(full0 + 8 * stage, 0);
-                    const unsigned a_dst = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
+                if (rank == 0) mbar_expect_tx(full0 + 8 * stage, 2 * C::STAGE_BYTES);
+                const unsigned bar = map_to_block(full0 + 8 * stage, 0);
+                const unsigned a_dst = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
 #pragma unroll
-                    for (int a = 0; a < C::KB; ++a) {
-                        tma_load_2d_pair(a_dst + a * C::ATOM_BYTES, &map_w, (kb * C::KB + a) * BK, (it.m * 2 + (int)rank) * BM, bar);
-                        tma_load_2d_pair(a_dst + C::A_BYTES + a * C::ATOM_BYTES, &map_x, (kb * C::KB + a) * BK,
-                                         it.n * BN + (int)rank * (BN / 2), bar);
-                    }
+                for (int a = 0; a < C::KB; ++a) {
+                    tma_load_2d_pair(a_dst + a * C::ATOM_BYTES, &map_w, (kb * C::KB + a) * BK, (it.m * 2 + (int)rank) * BM, bar);
+                    tma_load_2d_pair(a_dst + C::A_BYTES + a * C::ATOM_BYTES, &map_x, (kb * C::KB + a) * BK,
+                                     it.n * BN + (int)rank * (BN / 2), bar);
                 }
-                __syncwarp();
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
         }
@@ -444,33 +435,29 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
         int local = 0;
         bool ok = true;
         constexpr unsigned IDESC = instr_desc_bf16(2 * BM, BN, false);
-        while (rank == 0 && ok && it.next(p)) {
+        while (rank == 0 && lane == 0 && ok && it.next(p)) {
             const int acc = local & 1;
             const unsigned acc_phase = (local >> 1) & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(acce0 + 8 * acc, acc_phase ^ 1, p.status, 2));
+            ok = mbar_wait(acce0 + 8 * acc, acc_phase ^ 1, p.status, 2);
             if (!ok) break;
             tc_fence_after();
             const unsigned d_tmem = tmem_base + (unsigned)(acc * BN);
             for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
-                ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, p.status, 3));
+                ok = mbar_wait(full0 + 8 * stage, phase, p.status, 3);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
-                    const unsigned a_addr = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
+                const unsigned a_addr = smem_addr(tiles + (size_t)stage * C::STAGE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < C::KB * BK / 16; ++k) {        // 16 k = 32 bytes along the swizzled row; 64 k = the next block of rows
-                        const unsigned off = (k / 4) * C::ATOM_BYTES + (k % 4) * 32;
-                        umma_bf16_pair(d_tmem, smem_desc_sw128(a_addr + off), smem_desc_sw128(a_addr + C::A_BYTES + off), IDESC,
-                                       (kb > it.kb_lo || k > 0) ? 1u : 0u);
-                    }
-                    umma_commit_pair(empty0 + 8 * stage);  // the stage is free in both blocks once these MMAs have read it
+                for (int k = 0; k < C::KB * BK / 16; ++k) {            // 16 k = 32 bytes along the swizzled row; 64 k = the next block of rows
+                    const unsigned off = (k / 4) * C::ATOM_BYTES + (k % 4) * 32;
+                    umma_bf16_pair(d_tmem, smem_desc_sw128(a_addr + off), smem_desc_sw128(a_addr + C::A_BYTES + off), IDESC,
+                                   (kb > it.kb_lo || k > 0) ? 1u : 0u);
                 }
-                __syncwarp();
+                umma_commit_pair(empty0 + 8 * stage);      // the stage is free in both blocks once these MMAs have read it
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
-            if (lane == 0) umma_commit_pair(accf0 + 8 * acc);
-            __syncwarp();
+            umma_commit_pair(accf0 + 8 * acc);
             ++local;
         }
     } else {

@@ -140,56 +140,49 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
     const unsigned tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------------------------------------------------------- producer (TMA); lane 0 issues
+        // ---------------------------------------------------------------- producer (TMA), one thread
         int stage = 0, issued = 0;
         unsigned phase = 0;
         bool ok = true;
-        while (ok && it.next(p)) {
+        while (lane == 0 && ok && it.next(p)) {
             for (int kb = it.kb_lo; kb < it.kb_hi; ++kb, ++issued) {
-                ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 11));
+                ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 11);
                 if (!ok) break;
-                if (lane == 0) {
-                    const unsigned bar = full0 + 8 * stage;
-                    const unsigned dst = smem_addr(tiles + (size_t)stage * p.stage_bytes);
-                    if (issued >= ahead) {                  // else this stage's weights are already on their way
-                        mbar_expect_tx(bar, (unsigned)(A_BYTES + b_bytes));
-                        tma_load_2d(dst + A_BYTES, &map_w, kb * BK, it.m * p.nt, bar);
-                    }
-                    tma_load_2d(dst, &map_x, kb * BK, 0, bar);
+                const unsigned bar = full0 + 8 * stage;
+                const unsigned dst = smem_addr(tiles + (size_t)stage * p.stage_bytes);
+                if (issued >= ahead) {                      // else this stage's weights are already on their way
+                    mbar_expect_tx(bar, (unsigned)(A_BYTES + b_bytes));
+                    tma_load_2d(dst + A_BYTES, &map_w, kb * BK, it.m * p.nt, bar);
                 }
-                __syncwarp();
+                tma_load_2d(dst, &map_x, kb * BK, 0, bar);
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
         }
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer (lane 0 issues)
+        // ---------------------------------------------------------------- MMA issuer, one thread
         int stage = 0, local = 0;
         unsigned phase = 0;
         bool ok = true;
         const unsigned idesc = instr_desc_rt(p.nt);
-        while (ok && it.next(p)) {
-            ok = __all_sync(0xffffffffu, mbar_wait(acce, (unsigned)((local & 1) ^ 1), p.status, 12));   // the epilogue has read the last tile
+        while (lane == 0 && ok && it.next(p)) {
+            ok = mbar_wait(acce, (unsigned)((local & 1) ^ 1), p.status, 12);   // the epilogue has read the last tile
             if (!ok) break;
             tc_fence_after();
             for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
-                ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * stage, phase, p.status, 13));
+                ok = mbar_wait(full0 + 8 * stage, phase, p.status, 13);
                 if (!ok) break;
                 tc_fence_after();
-                if (lane == 0) {
-                    const unsigned a_addr = smem_addr(tiles + (size_t)stage * p.stage_bytes);
-                    const unsigned long long da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + A_BYTES);
+                const unsigned a_addr = smem_addr(tiles + (size_t)stage * p.stage_bytes);
+                const unsigned long long da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)      // 16 of k = 32 bytes further along the swizzled row
-                        umma_bf16(tmem_base, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), idesc,
-                                  (kb > it.kb_lo || k > 0) ? 1u : 0u);
-                    umma_commit(empty0 + 8 * stage);       // the stage is free once these MMAs have read it
-                }
-                __syncwarp();
+                for (int k = 0; k < BK / 16; ++k)          // 16 of k = 32 bytes further along the swizzled row
+                    umma_bf16(tmem_base, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), idesc,
+                              (kb > it.kb_lo || k > 0) ? 1u : 0u);
+                umma_commit(empty0 + 8 * stage);           // the stage is free once these MMAs have read it
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
             if (!ok) break;
-            if (lane == 0) umma_commit(accf);              // the accumulator is complete
-            __syncwarp();
+            umma_commit(accf);                             // the accumulator is complete
             ++local;
         }
     } else {
