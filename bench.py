@@ -390,13 +390,15 @@ def main(argv=None) -> int:
     batches = sorted({1, args.batch, 64} if not (args.skip_points or fp32) else {args.batch})
     max_batch = max(batches)
 
+    e2e_steps = max(min(args.steps, 16), 8) if fp32 else max(args.steps, 128)
+    per_seq = -(-(CACHED + max(e2e_steps, args.steps + args.warmup) + 8) // 64) * 64      # positions a sequence may reach, in whole pages
+
     def make_engine(dtype):
         return Engine.random(cfg, seed=0, dtype=dtype, max_context=CONTEXT, max_seqs=max_batch,
-                             max_tokens=max(max_batch * 1280, PREFILL_TOKENS + 64), max_step_tokens=PREFILL_TOKENS)
+                             max_tokens=max(max_batch * per_seq, PREFILL_TOKENS + 64), max_step_tokens=PREFILL_TOKENS)
 
     engine = make_engine(args.dtype)
     prefill_ms = time_prefill(engine, PREFILL_TOKENS, vocab, reps=1 if fp32 else 3)
-    e2e_steps = max(min(args.steps, 16), 8) if fp32 else max(args.steps, 128)
     points = {}
     for b in batches:
         if b == args.batch:
