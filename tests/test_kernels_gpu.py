@@ -422,6 +422,55 @@ def test_device_sampler_follows_the_host_rule(ops, temperature, top_k, top_p, V)
     assert checked > rows * 2
 
 
+@pytest.mark.parametrize("V", [131072, 40009, 1531])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 40, 0.9), (1.3, 0, 0.5), (0.6, 3, 1.0)])
+def test_a_row_shared_by_a_cluster_gives_the_one_block_token(ops, temperature, top_k, top_p, V):
+    """The sampler with 2, 4 or 8 blocks per row (their histograms added up and their candidates collected through
+    distributed shared memory) chooses what one block per row chooses, on every row: ordinary rows, a flat row and a
+    crowd of equals (more tokens in a bin than the fast path gathers: the exact path), everything in the last token,
+    ties at the top; and the library's own choice of the sharing agrees with the plain rule away from borders."""
+    torch.manual_seed(21)
+    rows = 9
+    logits = torch.randn(rows, V) * 3.0
+    logits[0] = 0.0
+    logits[1, 100] = logits[1, V - 7] = logits[1].max() + 1
+    logits[2, :] = -30.0; logits[2, V - 1] = 5.0
+    logits[3, 5:] = logits[3, 5]
+    logits[4, ::3] = logits[4, 0]
+    seeds = [(7654321 * (r + 3)) & 0xFFFFFFFF for r in range(rows)]
+    from tileinfer_b200.sampling.device import _as_i32
+    sd = _as_i32(seeds).cuda()
+    lg = dev(logits)
+    for counter in (0, 5):
+        got = {}
+        for share in (1, 2, 4, 8, 0):
+            ct = torch.full((rows,), counter, dtype=torch.int32, device="cuda")
+            out = torch.full((rows,), -7, dtype=torch.int32, device="cuda")
+            ops.sample(lg, out, temperature, top_k, top_p, sd, ct, cluster_blocks=share)
+            assert ct.tolist() == [counter + 1] * rows
+            got[share] = out.tolist()
+        for share in (2, 4, 8, 0):
+            assert got[share] == got[1], f"{share} blocks per row, counter {counter}"
+        checked = 0
+        for r in range(5, rows):                       # the ordinary rows against the plain rule, as in the test above
+            u = plain.sampling_uniform(seeds[r], counter)
+            ids, probs = plain.filtered_dist(logits[r], temperature, top_k, top_p)
+            cum, near = 0.0, False
+            for p in probs:
+                cum += p
+                near = near or abs(cum - u) < 1e-5
+            if top_p < 1:
+                _, full = plain.filtered_dist(logits[r], temperature, top_k, 1.0)
+                c = 0.0
+                for p in full:
+                    c += p
+                    near = near or abs(c - top_p) < 1e-5
+            if not near:
+                assert got[0][r] == ids[plain.pick(probs, u)], f"row {r} counter {counter}"
+                checked += 1
+        assert checked >= 2
+
+
 @pytest.mark.parametrize("nq,nkv,D", [(32, 8, 128), (6, 3, 32), (5, 1, 48), (4, 2, 16), (8, 8, 64), (16, 1, 64)])
 def test_attention_prefill(ops, nq, nkv, D):
     """Sequences of unequal lengths in one launch, some continuing from cached positions (start > 0),

@@ -237,11 +237,11 @@ __device__ Selected select_key(const float* row, int vocab, int mode, u64 bound,
 // ------------------------------------------------------------------------------ the binned fast path
 // f(index, logit) for every token of the row, the block's threads sharing them out; sixteen values per
 // thread are in flight at a time (one L2 round trip per value would otherwise bound a pass).
-template <typename F> __device__ __forceinline__ void for_each_logit(const float* row, int vocab, F f) {
-    int done = 0;
-    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
-        const int n4 = vocab >> 2;
-        const float4* row4 = reinterpret_cast<const float4*>(row);
+template <typename F> __device__ __forceinline__ void for_each_logit(const float* row, int lo, int hi, F f) {
+    int done = lo;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0 && (lo & 3) == 0) {
+        const int first4 = lo >> 2, n4 = hi > lo ? (hi - lo) >> 2 : 0;
+        const float4* row4 = reinterpret_cast<const float4*>(row) + first4;
         for (int i = threadIdx.x; i < n4; i += 4 * SM_THREADS) {
             float4 v[4];
 #pragma unroll
@@ -250,21 +250,22 @@ template <typename F> __device__ __forceinline__ void for_each_logit(const float
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int j = i + u * SM_THREADS;
-                if (j < n4) { f(4 * j, v[u].x); f(4 * j + 1, v[u].y); f(4 * j + 2, v[u].z); f(4 * j + 3, v[u].w); }
+                if (j < n4) { const int t = lo + 4 * j; f(t, v[u].x); f(t + 1, v[u].y); f(t + 2, v[u].z); f(t + 3, v[u].w); }
             }
         }
-        done = n4 * 4;
+        done = lo + n4 * 4;
     }
-    for (int i = done + threadIdx.x; i < vocab; i += 4 * SM_THREADS) {
+    for (int i = done + threadIdx.x; i < hi; i += 4 * SM_THREADS) {
         float v[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-            if (i + u * SM_THREADS < vocab) v[u] = __ldcg(row + i + u * SM_THREADS);
+            if (i + u * SM_THREADS < hi) v[u] = __ldcg(row + i + u * SM_THREADS);
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-            if (i + u * SM_THREADS < vocab) f(i + u * SM_THREADS, v[u]);
+            if (i + u * SM_THREADS < hi) f(i + u * SM_THREADS, v[u]);
     }
 }
+template <typename F> __device__ __forceinline__ void for_each_logit(const float* row, int vocab, F f) { for_each_logit(row, 0, vocab, f); }
 
 #define SB_BINS 4096
 #define SB_PER_NAT 128.0f
@@ -318,12 +319,17 @@ struct BinSelected {
 };
 
 // The first key (ascending) among keys <= bound whose cumulative weight (mode: counts or masses) reaches
-// target, from the histogram of the set and one gathering pass over the row. All threads get it.
-__device__ BinSelected select_binned(const float* row, int vocab, int mode, u64 bound, u64 target, float maxl, float inv_t,
-                                     const Binned& h) {
-    BinSelected r;
+// target, from the histogram of the set and one gathering pass over the row, in three steps that the kernels
+// below put together: the bin that holds the target (find_bin), that bin's tokens out of a stretch of the row
+// (gather_bin; several blocks may each gather a stretch), and the choice among them in key order (pick_in_bin).
+struct BinChoice {
+    int bin;
+    u64 base;         // weight of the bins before it
+};
+
+__device__ BinChoice find_bin(int mode, u64 target, const Binned& h) {
     if (target == 0) target = 1;
-    // 1. The bin: four bins per thread, block scan.
+    // Four bins per thread, block scan.
     u64 local[4], sum = 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -354,14 +360,21 @@ __device__ BinSelected select_binned(const float* row, int vocab, int mode, u64 
         if (threadIdx.x == last / 4) { res[0] = (u64)last; res[1] = incl - sum; for (int e = 0; e < last % 4; ++e) res[1] += local[e]; }
         __syncthreads();
     }
-    const int bin = (int)res[0];
-    const u64 base = res[1];
+    BinChoice c;
+    c.bin = (int)res[0];
+    c.base = res[1];
     __syncthreads();
-    // 2. Its tokens.
-    u32* n_cand = reinterpret_cast<u32*>(h.scan + SM_WARPS + 6);
-    if (threadIdx.x == 0) *n_cand = 0;
-    __syncthreads();
-    for_each_logit(row, vocab, [&](int i, float l) {
+    return c;
+}
+
+// The counter of gathered tokens (a 32-bit word in the scan scratch).
+__device__ __forceinline__ u32* gathered_count(const Binned& h) { return reinterpret_cast<u32*>(h.scan + SM_WARPS + 6); }
+
+// Appends the tokens of row[lo, hi) that fall into `bin` (keys <= bound) to the candidates; the counter keeps
+// counting beyond SB_CAP, which the caller reads as an overflow.
+__device__ void gather_bin(const float* row, int lo, int hi, int mode, u64 bound, int bin, float maxl, float inv_t, const Binned& h) {
+    u32* n_cand = gathered_count(h);
+    for_each_logit(row, lo, hi, [&](int i, float l) {
         if (token_bin(l, maxl, inv_t) != bin) return;
         const u64 key = ((u64)desc_key(l) << SM_ID_BITS) | (u64)i;
         if (key > bound) return;
@@ -370,12 +383,18 @@ __device__ BinSelected select_binned(const float* row, int vocab, int mode, u64 
         const u32 at = atomicAdd(n_cand, 1u);
         if (at < SB_CAP) { h.cand_key[at] = key; h.cand_w[at] = w; }
     });
-    __syncthreads();
-    const int n = (int)*n_cand;
+}
+
+// Among the n gathered tokens of `bin`, in key order, the first whose cumulative weight reaches what is left of the target.
+__device__ BinSelected pick_in_bin(int mode, u64 target, const BinChoice& at, int n, const Binned& h) {
+    BinSelected r;
+    if (target == 0) target = 1;
+    const int bin = at.bin;
+    const u64 base = at.base;
     r.bin = bin;
     r.overflow = n > SB_CAP || n == 0;
     if (r.overflow) { __syncthreads(); return r; }
-    // 3. In key order: bitonic sort of the next power of two, then scans of counts and masses.
+    // Bitonic sort of the next power of two, then scans of counts and masses.
     int n2 = 1;
     while (n2 < n) n2 <<= 1;
     for (int i = n + threadIdx.x; i < n2; i += SM_THREADS) { h.cand_key[i] = ~0ull; h.cand_w[i] = 0; }
@@ -433,6 +452,17 @@ __device__ BinSelected select_binned(const float* row, int vocab, int mode, u64 
     r.count_in_bin = (u32)(place + 1);
     __syncthreads();
     return r;
+}
+
+
+__device__ BinSelected select_binned(const float* row, int vocab, int mode, u64 bound, u64 target, float maxl, float inv_t,
+                                     const Binned& h) {
+    const BinChoice at = find_bin(mode, target, h);
+    if (threadIdx.x == 0) *gathered_count(h) = 0;
+    __syncthreads();
+    gather_bin(row, 0, vocab, mode, bound, at.bin, maxl, inv_t, h);
+    __syncthreads();
+    return pick_in_bin(mode, target, at, (int)*gathered_count(h), h);
 }
 
 // The set shrinks to the keys up to a selected one: its bin keeps what lies before and at it, later bins empty.
@@ -565,9 +595,234 @@ __global__ void __launch_bounds__(SM_THREADS) sample_kernel(const float* logits,
     }
 }
 
-extern "C" int ti_sample(const float* logits, long long ld, int n_rows, int vocab, float temperature, int top_k,
-                         float top_p, const unsigned* seeds, unsigned* counters, int* out, int* out2, cudaStream_t stream) {
+// ------------------------------------------------------------------------------ a row shared by a cluster
+// The same rule with the row shared out among the C blocks of a cluster, for steps of a few rows, where one block
+// per row leaves most of the GPU idle and is bound by one SM's instruction rate (a pass over 131,072 logits takes a
+// block about 15 us). Every block makes the passes over its own stretch of the row (maximum, histogram, the
+// gathering of a bin's tokens) into its own shared memory; the histograms are added up, and the gathered tokens
+// collected, through distributed shared memory; the scans, the sort and the choices run in block 0 alone, on the
+// same integers as in the one-block kernel, so the token is the same. Block 0 tells the others what to gather
+// through a few words of its shared memory; a barrier of the cluster stands before and after every such order.
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ unsigned remote_addr(const void* p, unsigned rank) {
+    unsigned a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"((unsigned)__cvta_generic_to_shared(p)), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ u32 ld_remote(const u32* p, unsigned rank) {
+    u32 v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote_addr(p, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ u64 ld_remote(const u64* p, unsigned rank) {
+    u64 v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote_addr(p, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_remote(const float* p, unsigned rank) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote_addr(p, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_remote(u32* p, unsigned rank, u32 v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote_addr(p, rank)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_remote(u64* p, unsigned rank, u64 v) {
+    asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(remote_addr(p, rank)), "l"(v) : "memory");
+}
+
+template <int C>
+__global__ void __launch_bounds__(SM_THREADS) sample_cluster_kernel(const float* logits, long long ld, int vocab,
+                                                                    float inv_t, int top_k, float top_p,
+                                                                    const u32* seeds, u32* counters,
+                                                                    int* __restrict__ out, int* __restrict__ out2) {
+    extern __shared__ u64 dyn[];
+    __shared__ float scratch[33];
+    __shared__ float my_max;
+    __shared__ u64 order[4];                               // block 0's: [0] 0 gather / 1 finished, [1] bin, [2] bound, [3] mode
+    const unsigned rank = cluster_rank();
+    const int row_id = blockIdx.x / C;
+    const float* row = logits + (size_t)row_id * ld;
+    const int per = ((vocab + C - 1) / C + 3) & ~3;        // stretches begin at multiples of 4 (16-byte loads)
+    const int lo = min(vocab, (int)rank * per), hi = min(vocab, lo + per);
+    pdl_wait();
+    pdl_launch_dependents();
+
+    float maxl = -INFINITY;
+    for_each_logit(row, lo, hi, [&](int, float l) { maxl = fmaxf(maxl, l); });
+    maxl = block_max(maxl, scratch);
+    if (threadIdx.x == 0) my_max = maxl;
+    cluster_sync_all();
+#pragma unroll
+    for (int r = 0; r < C; ++r) maxl = fmaxf(maxl, ld_remote(&my_max, (unsigned)r));
+
+    Binned h;
+    h.mass = dyn;
+    h.cand_key = dyn + SB_BINS;
+    h.cand_w = h.cand_key + SB_CAP;
+    h.scan = h.cand_w + SB_CAP;
+    h.count = reinterpret_cast<u32*>(h.scan + SM_WARPS + 8);
+    u32* mass_lo = reinterpret_cast<u32*>(h.cand_key);      // as in the one-block kernel: masses as two 32-bit halves
+    u32* mass_hi = mass_lo + SB_BINS;
+    for (int b = threadIdx.x; b < SB_BINS; b += SM_THREADS) { mass_lo[b] = 0; mass_hi[b] = 0; h.count[b] = 0; }
+    __syncthreads();
+    const bool need_counts = top_k > 0 && top_k < vocab;
+    for_each_logit(row, lo, hi, [&](int, float l) {
+        const int b = token_bin(l, maxl, inv_t);
+        const u64 w = token_weight(W_MASS, l, maxl, inv_t);
+        if (w) {
+            const u32 wl = (u32)w;
+            u32 wh = (u32)(w >> 32);
+            if (wl) {
+                const u32 old = atomicAdd(&mass_lo[b], wl);
+                wh += (old + wl < old) ? 1u : 0u;
+            }
+            if (wh) atomicAdd(&mass_hi[b], wh);
+        }
+        if (need_counts) atomicAdd(&h.count[b], 1u);
+    });
+    __syncthreads();
+    cluster_sync_all();                                    // every block's histogram stands
+    // Each block adds up its share of the bins over all blocks and hands the sums to block 0.
+    for (int b = (int)rank * (SB_BINS / C) + threadIdx.x; b < ((int)rank + 1) * (SB_BINS / C); b += SM_THREADS) {
+        u64 m = 0;
+        u32 c = 0;
+#pragma unroll
+        for (int r = 0; r < C; ++r) {
+            m += ((u64)ld_remote(&mass_hi[b], (unsigned)r) << 32) + (u64)ld_remote(&mass_lo[b], (unsigned)r);
+            c += ld_remote(&h.count[b], (unsigned)r);
+        }
+        st_remote(&h.mass[b], 0u, m);
+        st_remote(&h.count[b], 0u, c);
+    }
+    cluster_sync_all();                                    // block 0 holds the row's histogram
+
+    if (rank != 0) {
+        // Gather what block 0 orders, until it says that it has finished.
+        while (true) {
+            cluster_sync_all();                            // an order stands
+            if (ld_remote(&order[0], 0u) != 0) break;
+            const int bin = (int)ld_remote(&order[1], 0u), mode = (int)ld_remote(&order[3], 0u);
+            const u64 bound = ld_remote(&order[2], 0u);
+            if (threadIdx.x == 0) *gathered_count(h) = 0;
+            __syncthreads();
+            gather_bin(row, lo, hi, mode, bound, bin, maxl, inv_t, h);
+            __syncthreads();
+            cluster_sync_all();                            // gathered; block 0 now reads the candidates
+        }
+        cluster_sync_all();                                // nobody reads block 0's order any more
+        return;
+    }
+
+    const u32 counter = counters[row_id];
+    const u32 r24 = mix32(mix32(seeds[row_id]) ^ counter) >> 8;
+    auto select = [&](int mode, u64 bound, u64 target) -> BinSelected {
+        const BinChoice at = find_bin(mode, target, h);
+        if (threadIdx.x == 0) {
+            order[0] = 0; order[1] = (u64)at.bin; order[2] = bound; order[3] = (u64)mode;
+            *gathered_count(h) = 0;
+        }
+        __syncthreads();
+        cluster_sync_all();
+        gather_bin(row, lo, hi, mode, bound, at.bin, maxl, inv_t, h);
+        __syncthreads();
+        cluster_sync_all();
+        // The other blocks' candidates behind this block's own; the sort puts them in key order.
+        long long n = (long long)*gathered_count(h);
+        __syncthreads();
+        for (int r = 1; r < C; ++r) {
+            const u32 nr = ld_remote(gathered_count(h), (unsigned)r);
+            if (n + (long long)nr <= SB_CAP)
+                for (int i = threadIdx.x; i < (int)nr; i += SM_THREADS) {
+                    h.cand_key[n + i] = ld_remote(&h.cand_key[i], (unsigned)r);
+                    h.cand_w[n + i] = ld_remote(&h.cand_w[i], (unsigned)r);
+                }
+            n += (long long)nr;
+        }
+        __syncthreads();
+        return pick_in_bin(mode, target, at, n > SB_CAP ? SB_CAP + 1 : (int)n, h);
+    };
+    int token = -1;
+    do {
+        u64 bound = ~0ull;
+        if (need_counts) {
+            const BinSelected k = select(W_COUNT, bound, (u64)top_k);
+            if (k.overflow) break;
+            bound = k.sel.key;
+            cut_histogram(h, k);
+        }
+        u64 part = 0, total;
+        for (int b = threadIdx.x; b < SB_BINS; b += SM_THREADS) part += h.mass[b];
+        block_scan(part, h.scan, total);
+        if (top_p < 1.0f) {
+            const u64 target = (u64)ceil((double)top_p * (double)total);
+            const BinSelected p = select(W_MASS, bound, target);
+            if (p.overflow) break;
+            bound = p.sel.key;
+            total = p.sel.through;
+            cut_histogram(h, p);
+        }
+        const BinSelected d = select(W_MASS, bound, draw_target(total, r24));
+        if (d.overflow) break;
+        token = (int)(d.sel.key & ((1ull << SM_ID_BITS) - 1));
+    } while (false);
+    __syncthreads();
+    if (threadIdx.x == 0) order[0] = 1;
+    __syncthreads();
+    cluster_sync_all();                                    // the others see that nothing more is ordered
+    cluster_sync_all();                                    // and have read it: from here on this block is alone
+    if (token < 0) {                                       // a crowded bin: the exact path, by this block over the whole row
+        u64* hist = dyn;
+        u64* totals = dyn + SM_WARPS * 256;
+        u64* shared = totals + 256;
+        token = sample_exact(row, vocab, inv_t, top_k, top_p, r24, maxl, hist, totals, shared);
+    }
+    if (threadIdx.x == 0) {
+        out[row_id] = token;
+        if (out2 != nullptr) out2[row_id] = token;
+        counters[row_id] = counter + 1;
+    }
+}
+
+template <int C>
+static int launch_sample_cluster(const float* logits, long long ld, int n_rows, int vocab, float inv_t, int top_k, float top_p,
+                                 const unsigned* seeds, unsigned* counters, int* out, int* out2, size_t smem, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return ti_fail("sample: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_rows * C);
+    cfg.blockDim = dim3(SM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = C; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ti_pdl_enabled ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, sample_cluster_kernel<C>, logits, ld, vocab, inv_t, top_k, top_p, seeds, counters, out, out2);
+    return ti_check_launch("sample");
+}
+
+// `cluster_blocks`: blocks that share a row (1, 2, 4 or 8; 0: chosen here from the number of rows and the vocabulary).
+extern "C" int ti_sample_shared(const float* logits, long long ld, int n_rows, int vocab, float temperature, int top_k,
+                                float top_p, const unsigned* seeds, unsigned* counters, int* out, int* out2, int cluster_blocks,
+                                cudaStream_t stream) {
     if (n_rows == 0) return 0;
+    TI_REQUIRE(cluster_blocks == 0 || cluster_blocks == 1 || cluster_blocks == 2 || cluster_blocks == 4 || cluster_blocks == 8,
+               "sample: %d blocks per row (0, 1, 2, 4 or 8)", cluster_blocks);
     TI_REQUIRE(vocab > 0 && vocab <= (1 << SM_ID_BITS), "sample: vocabulary %d exceeds %d", vocab, 1 << SM_ID_BITS);
     TI_REQUIRE(temperature > 0.f, "sample: temperature must be > 0 (use argmax for greedy)");
     TI_REQUIRE(top_k >= 0, "sample: top_k must be >= 0");
@@ -581,9 +836,32 @@ extern "C" int ti_sample(const float* logits, long long ld, int n_rows, int voca
         if (e != cudaSuccess) return ti_fail("sample: %s", cudaGetErrorString(e));
         configured = true;
     }
+    // A few rows of a large vocabulary: a cluster of blocks per row, as many as keep the launch within one round of the SMs.
+    int sm_count = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    // Measured at a vocabulary of 131,072 on 148 SMs (us, temperature only, for 1 / 2 / 4 / 8 blocks per row): 12 rows 47 / 35 /
+    // 28 / 26, 16 rows 47 / 35 / 28 / 44, 32 rows 48 / 36 / 30 / 65, 37 rows 49 / 37 / 50, 74 rows 53 / 43 / 80, 96 rows 54 / 74:
+    // clusters that do not all find room at once wait for one another, the larger the earlier.
+    int share = cluster_blocks;
+    if (share == 0) {
+        if (vocab < 32768) share = 1;                          // a pass of one block is short already
+        else if (n_rows * 8 * 3 <= sm_count * 2) share = 8;
+        else if (n_rows * 4 * 8 <= sm_count * 7) share = 4;
+        else if (n_rows * 2 <= sm_count) share = 2;
+        else share = 1;
+    }
+    if (share == 8) return launch_sample_cluster<8>(logits, ld, n_rows, vocab, 1.0f / temperature, top_k, top_p, seeds, counters, out, out2, smem, stream);
+    if (share == 4) return launch_sample_cluster<4>(logits, ld, n_rows, vocab, 1.0f / temperature, top_k, top_p, seeds, counters, out, out2, smem, stream);
+    if (share == 2) return launch_sample_cluster<2>(logits, ld, n_rows, vocab, 1.0f / temperature, top_k, top_p, seeds, counters, out, out2, smem, stream);
     ti_launch(sample_kernel, dim3(n_rows), dim3(SM_THREADS), smem, stream, logits, ld, vocab, 1.0f / temperature, top_k, top_p, seeds,
                                                         counters, out, out2);
     return ti_check_launch("sample");
+}
+
+extern "C" int ti_sample(const float* logits, long long ld, int n_rows, int vocab, float temperature, int top_k,
+                         float top_p, const unsigned* seeds, unsigned* counters, int* out, int* out2, cudaStream_t stream) {
+    return ti_sample_shared(logits, ld, n_rows, vocab, temperature, top_k, top_p, seeds, counters, out, out2, 0, stream);
 }
 
 // The uniform number of (seed, counter), for tests of the generator itself.

@@ -82,6 +82,7 @@ _SIGNATURES = {
     "ti_gemm_plain": [_P, _L, _P, _L, _P, _I, _I, _I, _I, _F, _F, _F, _F, _I, _P],
     "ti_argmax": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "ti_sample": [_P, _L, _I, _I, _F, _I, _F, _P, _P, _P, _P, _P],
+    "ti_sample_shared": [_P, _L, _I, _I, _F, _I, _F, _P, _P, _P, _P, _I, _P],
     "ti_random_normal": [_P, _I, _L, _L, _U, _U, _F, _F, _P],
     "ti_wait_probe": [_P, _I, _I, _P, _P],
 }

@@ -181,8 +181,11 @@ def argmax(logits, out, workspace=None, also=None):
                           val.data_ptr(), idx.data_ptr(), cnt.data_ptr(), _stream()), "argmax")
 
 
-def sample(logits, out, temperature, top_k, top_p, seeds, counters, also=None):
+def sample(logits, out, temperature, top_k, top_p, seeds, counters, also=None, cluster_blocks=0):
+    """``cluster_blocks``: how many blocks share a row (1, 2, 4 or 8); 0 lets the library choose from the number of
+    rows and the vocabulary. The token does not depend on it."""
     _need(logits, "logits", torch.float32, contiguous=False); _need(out, "out", torch.int32)
     _need(seeds, "seeds", torch.int32); _need(counters, "counters", torch.int32)
-    check(lib().ti_sample(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], temperature, top_k,
-                          top_p, seeds.data_ptr(), counters.data_ptr(), out.data_ptr(), _ptr(also), _stream()), "sample")
+    check(lib().ti_sample_shared(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], temperature, top_k,
+                                 top_p, seeds.data_ptr(), counters.data_ptr(), out.data_ptr(), _ptr(also), cluster_blocks,
+                                 _stream()), "sample")
