@@ -145,7 +145,10 @@ extern "C" int ti_argmax(const float* logits, long long ld, int n_rows, int voca
     TI_REQUIRE(vocab > 0, "argmax: vocab %d", vocab);
     TI_REQUIRE(n_rows <= 65535, "argmax: %d rows in one launch", n_rows);
     TI_REQUIRE(ws_val != nullptr && ws_idx != nullptr && counters != nullptr, "argmax: work space missing");
-    const int chunks = ti_argmax_chunks(vocab);
+    // Many rows: fewer, longer chunks (about 2,048 blocks in all), so that the launch is not a long queue of tiny blocks.
+    int chunks = ti_argmax_chunks(vocab);
+    const int fewer = 2048 / n_rows < 8 ? 8 : 2048 / n_rows;
+    if (fewer < chunks) chunks = fewer;
     int per_chunk = (vocab + chunks - 1) / chunks;
     per_chunk = (per_chunk + 3) & ~3;
     ti_launch(argmax_kernel, dim3(chunks, n_rows), dim3(AM_THREADS), 0, stream, logits, ld, vocab, per_chunk, out, out2, ws_val, ws_idx,
