@@ -710,6 +710,57 @@ def test_gemm_tcgen05_decode(ops, n, out, k, tile, splits):
     fast.check_status()
 
 
+@pytest.mark.parametrize("raw", [(18.125, 10.5), (0.3, -0.4)])
+def test_xielu_over_every_bfloat16_value(ops, raw):
+    """The activation has 65,280 possible finite inputs in bfloat16: every one of them through the element-wise
+    kernel and through the epilogue of every product kernel (the products have one-hot weight rows, so that
+    the sums ARE the inputs), bit for bit against the step-wise formula. An approximation of expm1 that rounds
+    one input differently shows here."""
+    from tileinfer_b200.kernels import fast
+    from tileinfer_b200.kernels.library import check, lib
+    dtype = torch.bfloat16
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    vals = bits[torch.isfinite(bits.float())]
+    assert vals.numel() == 65280
+    a = plain.xielu_scalars(torch.tensor(raw[0]), torch.tensor(raw[1]), torch.tensor(0.5), torch.tensor(-1e-6), dtype)
+    act = (float(a.alpha_p), float(a.alpha_n), float(a.beta), float(a.eps))
+    want = plain.xielu(vals.float(), a, dtype)
+    y = torch.empty(vals.numel(), dtype=dtype, device="cuda")
+    ops.xielu(y, vals.cuda(), *act)
+    assert torch.equal(y.float().cpu(), want)
+    # As products: x [1020 tokens, 64] holds the values, W [128, 64] has row j = unit vector j mod 64.
+    k, out = 64, 128
+    x = vals.view(-1, k)
+    w = torch.zeros(out, k)
+    w[torch.arange(out), torch.arange(out) % k] = 1.0
+    wd = dev(w, dtype)
+    want2 = want.view(-1, k).repeat(1, 2)
+    st = torch.cuda.current_stream().cuda_stream
+    status = fast.status_word()
+    for lo, hi in ((0, 1020), (0, 128), (128, 192), (192, 200)):      # 1,020 tokens at once, then steps of 128, 64 and 8
+        xd = x[lo:hi].contiguous().cuda()
+        n = hi - lo
+        got = {}
+        y2 = torch.full((n, out), float("nan"), dtype=dtype, device="cuda")
+        check(lib().ti_gemm_tcgen05(y2.data_ptr(), out, xd.data_ptr(), k, wd.data_ptr(), n, out, k, 1, 1, *act, status.data_ptr(), st), "tc")
+        got["tcgen05"] = y2
+        if n <= 128:
+            y3 = torch.full((n, out), float("nan"), dtype=dtype, device="cuda")
+            check(lib().ti_gemm_tcgen05_decode(y3.data_ptr(), out, xd.data_ptr(), k, wd.data_ptr(), n, out, k, 0, 1, 1, *act,
+                                               status.data_ptr(), st), "tc decode")
+            got["tcgen05 decode"] = y3
+        if n <= 16:
+            y4 = torch.full((n, out), float("nan"), dtype=dtype, device="cuda")
+            check(lib().ti_gemv_bf16(y4.data_ptr(), out, xd.data_ptr(), k, wd.data_ptr(), n, out, k, 1, 1, *act, st), "gemv")
+            got["weight streaming"] = y4
+        y5 = torch.full((n, out), float("nan"), dtype=dtype, device="cuda")
+        ops.gemm_plain(y5, xd, wd, ops.EPI_XIELU, act)
+        got["plain"] = y5
+        for name, yy in got.items():
+            assert torch.equal(yy.float().cpu(), want2[lo:hi]), f"{name}, tokens {lo} to {hi}"
+    fast.check_status()
+
+
 def test_a_wait_that_runs_out_is_reported_and_the_device_goes_on(ops):
     """The error path of the bounded waits: a barrier that nothing completes, waited on with a limit of
     1,024 attempts. The kernel returns, the wait's bit is in the status word, check_status() raises and
