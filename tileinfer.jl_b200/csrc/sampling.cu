@@ -840,9 +840,12 @@ extern "C" int ti_sample_shared(const float* logits, long long ld, int n_rows, i
         configured = true;
     }
     // A few rows of a large vocabulary: a cluster of blocks per row, as many as keep the launch within one round of the SMs.
-    int sm_count = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    static int sm_count = 0;                                   // asked once: the answer does not change
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 1;
+    }
     // Measured at a vocabulary of 131,072 on 148 SMs (us, temperature only, for 1 / 2 / 4 / 8 blocks per row): 12 rows 47 / 35 /
     // 28 / 26, 16 rows 47 / 35 / 28 / 44, 32 rows 48 / 36 / 30 / 65, 37 rows 49 / 37 / 50, 74 rows 53 / 43 / 80, 96 rows 54 / 74:
     // clusters that do not all find room at once wait for one another, the larger the earlier.
