@@ -118,7 +118,7 @@ def release(engine, slots):
         engine.free_sequence(s)
 
 
-def time_decode(engine, batch, steps, warmup, vocab, count_launches=False):
+def time_decode(engine, batch, steps, warmup, vocab, count_launches=False, cached=None):
     """Device time of ``steps`` decode steps of ``batch`` sequences through the library's own decode
     loop (greedy sampling on the device, the host one step behind): CUDA events are recorded when the
     tokens of step W and of step W + K reach the host, which brackets exactly K steps on the stream."""
@@ -126,11 +126,12 @@ def time_decode(engine, batch, steps, warmup, vocab, count_launches=False):
     from tileinfer_b200.engine.generate import decode_batch
     from tileinfer_b200.sampling import DeviceSampler, SamplingParams
     warmup = max(warmup, 3)
-    slots_list = fill_cache(engine, batch, CACHED - 1)
+    cached = CACHED if cached is None else cached
+    slots_list = fill_cache(engine, batch, cached - 1)
     sampler = DeviceSampler(batch, engine.device)
     gen = torch.Generator().manual_seed(1)
     tokens = torch.randint(0, vocab, (batch,), generator=gen).tolist()
-    logits = engine.decode(slots_list, tokens)                       # position CACHED - 1: now CACHED positions are held
+    logits = engine.decode(slots_list, tokens)                       # position cached - 1: now `cached` positions are held
     slots = dict(enumerate(slots_list))
     results = [[] for _ in range(batch)]
     marks = {}
@@ -144,7 +145,7 @@ def time_decode(engine, batch, steps, warmup, vocab, count_launches=False):
     torch.cuda.synchronize()
     ms = marks[warmup].elapsed_time(marks[warmup + steps])
     launches = engine.decode_launches(batch) + 1 if count_launches else 0     # the captured step + sampling (which hands the ids over)
-    kv_positions = batch * (CACHED + warmup + 1 + steps / 2)
+    kv_positions = batch * (cached + warmup + 1 + steps / 2)
     assert not slots                                                  # the loop freed every sequence
     return ms / steps, kv_positions, launches
 
@@ -330,6 +331,44 @@ def run_70b(args, pk, pk_source):
     return 0
 
 
+def run_sweep(args, pk, pk_source):
+    """Apertus-8B sizes at further batch sizes, context lengths and prompt lengths than the headline line: decode steps
+    of 1 to 128 sequences after 1,023 to 32,767 cached positions, and prompts of 128 to 8,192 tokens, each with its
+    fraction of the measured peak. One line of JSON with two lists."""
+    import torch
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.engine import Engine
+    cfg_dict = dict(APERTUS_8B, max_position_embeddings=32768 + 256)
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    cfg = ApertusConfig.from_dict(cfg_dict)
+    points = [(1, 1023), (1, 8191), (1, 32767), (4, 1023), (8, 1023), (8, 8191), (8, 32767), (16, 1023), (16, 8191), (32, 1023),
+              (32, 8191), (64, 1023), (64, 8191), (128, 1023), (128, 4095)]
+    steps, warmup = max(8, min(args.steps, 32)), max(args.warmup, 3)
+    room = max(b * (-(-(c + steps + warmup + 8) // 64) * 64) for b, c in points)
+    engine = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=32768 + 256, max_seqs=128, max_tokens=room, max_step_tokens=8192)
+    clocks = ClockSampler()
+    clocks.start()
+    decode = []
+    for b, c in points:
+        pt = decode_point(engine, b, steps, warmup, cfg.vocab_size, pk, cached=c)
+        decode.append({"batch": b, "cached": c, "ms": round(pt["ms"], 4), "tok_s": round(pt["value"], 1), "frac": round(pt["frac"], 4)})
+    prefill = []
+    for tokens in (128, 512, 2048, 8192):
+        ms = time_prefill(engine, tokens, cfg.vocab_size, reps=2)
+        flops = flops_prefill(cfg_dict, cfg.num_hidden_layers, tokens)
+        prefill.append({"tokens": tokens, "ms": round(ms, 3), "tok_s": round(tokens * 1000.0 / ms, 1),
+                        "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                        "weights_frac": round(engine.weight_bytes() / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)})
+    clock_info = clocks.stop()
+    engine.check_health()
+    print(json.dumps({"metric": "decode and prefill at further sizes (Apertus-8B bf16)", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "dtype": "bf16", "data": "synthetic: random weights, uniform random token ids",
+                      "config": {"model": "Apertus-8B shapes", "layers": cfg.num_hidden_layers, "layers_full": 32, "peaks": pk_source},
+                      "clocks": clock_info, "decode": decode, "prefill": prefill}))
+    return 0
+
+
 def flops_prefill(cfg, n_layers, tokens):
     H, I, D = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
     nq, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
@@ -337,10 +376,10 @@ def flops_prefill(cfg, n_layers, tokens):
     return n_layers * per_layer + 2 * H * cfg["vocab_size"]
 
 
-def decode_point(engine, batch, steps, warmup, vocab, pk, count_launches=False):
+def decode_point(engine, batch, steps, warmup, vocab, pk, count_launches=False, cached=None):
     """One decode measurement: tokens per second, ms per step, the bytes the step has to read (every
     weight once, and the cache of the live sequences) and their rate as a fraction of the HBM peak."""
-    ms, kv_positions, launches = time_decode(engine, batch, steps, warmup, vocab, count_launches=count_launches)
+    ms, kv_positions, launches = time_decode(engine, batch, steps, warmup, vocab, count_launches=count_launches, cached=cached)
     step_bytes = engine.weight_bytes() + kv_positions * engine.kv_bytes_per_position()
     gbs = step_bytes / (ms * 1e-3) / 1e9
     return {"value": batch * 1000.0 / ms, "ms": ms, "bytes": step_bytes, "gbs": gbs, "frac": gbs / pk["hbm_gbs"], "launches": launches}
@@ -357,7 +396,7 @@ def main(argv=None) -> int:
                     help="float32: the true 32-bit path (strict 32-bit FMA products) as the headline")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick checks)")
-    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b"],
+    ap.add_argument("--preset", default="8b", choices=["8b", "8b-long", "70b", "sweep"],
                     help="8b: the headline line (default); 8b-long: 8 unequal sequences of up to 32,768 positions; "
                          "70b: Apertus-70B sizes, 141 GB of weights")
     args = ap.parse_args(argv)
@@ -379,6 +418,8 @@ def main(argv=None) -> int:
         return run_long_context(args, *peaks())
     if args.preset == "70b":
         return run_70b(args, *peaks())
+    if args.preset == "sweep":
+        return run_sweep(args, *peaks())
     cfg_dict = dict(APERTUS_8B)
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:

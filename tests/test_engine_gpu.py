@@ -350,9 +350,9 @@ def test_one_layer_at_apertus_8b_sizes(dtype):
         folder = write_model_folder(ApertusConfig.from_dict(cfg_dict), 5, os.path.join(d, "m"))
         pc, pw = plain.load_folder(folder)
         pdt = torch.float32 if dtype == "float32" else torch.bfloat16
-        prompts = helpers.random_prompts(16384, [150, 37], 6)
+        prompts = helpers.random_prompts(16384, [150, 37, 330], 6)
         refs = [plain.forward(pc, pw, p, pdt) for p in prompts]
-        eng = ti.load_model(folder, dtype=dtype, max_context=256, max_seqs=2)
+        eng = ti.load_model(folder, dtype=dtype, max_context=512, max_seqs=2)
         tol = tolerance(dtype, refs[0])
         from tileinfer_b200.kernels import library
         before = dict(library.call_counts)
@@ -380,6 +380,18 @@ def test_one_layer_at_apertus_8b_sizes(dtype):
         assert float((got - refs[0][:100]).abs().max()) <= tol
         if dtype == "bfloat16":
             assert library.call_counts.get("ti_gemm_tcgen05_decode", 0) - before.get("ti_gemm_tcgen05_decode", 0) == 2   # up projection and head
+        eng.free_sequence(a)
+        eng.free_sequence(b)
+        # 330 + 37 tokens in one step: the o and down products have fewer tiles of 256 x 256 than there are SM pairs and
+        # come in k slices that the norms add up.
+        a, b = eng.new_sequence(), eng.new_sequence()
+        wanted = [0, 100, 255, 256, 329]
+        got = eng.step([(a, prompts[2]), (b, prompts[1])], [wanted, [0, 36]]).cpu()
+        want = torch.stack([refs[2][i] for i in wanted] + [refs[1][0], refs[1][36]])
+        assert float((got - want).abs().max()) <= tolerance(dtype, refs[2])
+        if dtype == "bfloat16":
+            from tileinfer_b200.kernels import fast
+            assert fast.tc_splits(4096, 21504, 367) > 1 and fast.tc_splits(4096, 4096, 367) > 1
         eng.check_health()
 
 

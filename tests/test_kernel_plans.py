@@ -62,7 +62,11 @@ def test_slices_of_the_other_decode_products():
     assert fast.gemv_splits(21504, 4096) == 1 and fast.gemv_splits(4096, 21504) == 1     # 16-row blocks already fill the SMs
     assert fast.gemv_splits(1024, 8192) > 1
     assert fast.tc_splits(21504, 4096, 64) == 1 and fast.tc_splits(4096, 21504, 64) == 8
-    assert fast.tc_splits(4096, 4096, 2048) == 1                                         # prefill is never cut
+    assert fast.tc_splits(4096, 4096, 2048) == 1 and fast.tc_splits(4096, 21504, 1024) == 1    # enough tiles for every SM pair: not cut
+    # A prompt of a few hundred tokens: products with few output rows have fewer tiles of 256 x 256 than the 74 SM pairs.
+    assert fast.tc_splits(4096, 21504, 512) == 2 and fast.tc_splits(4096, 4096, 367) == 2     # 32 tiles -> 64
+    assert fast.tc_splits(4096, 21504, 768) == 3                                         # 48 tiles -> 144 in two rounds of a third
+    assert fast.tc_splits(4096, 1024, 512) == 1                                          # a slice keeps at least 1,024 of k
     assert fast.decode_splits(1, 8, 4096) == 32 and fast.decode_splits(64, 8, 4096) == 1
 
 

@@ -637,6 +637,7 @@ def test_attention_decode_with_shared_out_slots(ops, nq, nkv, D, splits, lengths
 
 @pytest.mark.parametrize("n,out,k,splits", [(17, 100, 72, 1), (37, 301, 120, 1), (130, 384, 512, 1), (300, 256, 4160, 1),
                                              (64, 512, 1024, 4), (2048, 256, 192, 1), (40, 4099, 264, 3),
+                                             (300, 512, 2048, 2), (700, 777, 4160, 3),      # k slices on SM pairs
                                              (1024, 4900, 8200, 1)])      # the last one takes 256-row blocks
 def test_gemm_tcgen05(ops, n, out, k, splits):
     from tileinfer_b200.kernels import fast

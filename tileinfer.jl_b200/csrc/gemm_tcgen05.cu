@@ -405,7 +405,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     const unsigned tmem_base = *tmem_slot;
 
     TileIter it;
-    it.id = blockIdx.x >> 1; it.step = gridDim.x >> 1; it.total = p.m_tiles * p.n_tiles;
+    it.id = blockIdx.x >> 1; it.step = gridDim.x >> 1; it.total = p.m_tiles * p.n_tiles * p.splits;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer (TMA), in both blocks
@@ -477,7 +477,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
             const int n_valid = min(BN, p.N - n0);
             const int m_first = (it.m * 2 + (int)rank) * BM + quarter * 32;
             const unsigned t_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * BN);
-            epilogue_rows<BN, C::EPI_WARPS, C::OUT_BYTES>(t_row, m_first, lane, n0, n_valid, col_group, warp - 2, 0, out_buf, out_tiles,
+            epilogue_rows<BN, C::EPI_WARPS, C::OUT_BYTES>(t_row, m_first, lane, n0, n_valid, col_group, warp - 2, it.split, out_buf, out_tiles,
                                                           &map_y, y, p, act);
             tc_fence_before();
             __syncwarp();
@@ -540,7 +540,7 @@ int pair_clusters(int sm_count) {
 
 int launch_pair(void* y, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& my, const Params& p, cudaStream_t stream) {
     const int clusters = pair_clusters(0);
-    const int tiles = p.m_tiles * p.n_tiles;
+    const int tiles = p.m_tiles * p.n_tiles * p.splits;
     const int pairs = tiles < clusters ? tiles : clusters;
     ti_launch(gemm_tcgen05_pair_kernel, dim3(2 * pairs), dim3(PairCfg::THREADS), PairCfg::SMEM, stream, mw, mx, my, y, p);
     return ti_check_launch("gemm_tcgen05 (pairs)");
@@ -568,7 +568,9 @@ int gemm_dispatch(void* y, long long ldy, const void* x, long long ldx, const vo
         const long long waves2 = (((out + 2 * BM - 1) / (2 * BM)) * n_t + sm_count - 1) / sm_count;
         if (3 * waves2 < 2 * waves1) mt = 2;
     }
-    const bool pair = mt == 1 && bn == 256 && splits <= 1 && out >= 2 * BM && pair_clusters(sm_count) > 0;
+    // (A product of a few hundred tokens with few output rows has fewer tiles than there are SM pairs: it may come cut
+    // over k, each slice a tile of its own, leaving 32-bit partial sums.)
+    const bool pair = mt == 1 && bn == 256 && (splits <= 1 || (epilogue == EPI_PARTIAL && n > 256)) && out >= 2 * BM && pair_clusters(sm_count) > 0;
     if (pair) mt = 2;
     p.M = out;
     p.m_tiles = (out + mt * BM - 1) / (mt * BM);

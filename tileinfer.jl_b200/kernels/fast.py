@@ -85,9 +85,23 @@ def tc_splits(out_features: int, in_features: int, n: int) -> int:
     add partial sums: as many as fill the device's block slots (two per SM for token tiles of up to 64), at
     most 8, each at least 512 of k. Measured at 64 tokens: down projection 46 us in 3 slices, 35 us in 8;
     o 17 us in 2, 11 us in 8."""
+    if n > 256:
+        # A prompt of a few hundred tokens: tiles of 256 weight rows x 256 tokens on SM pairs. A product with few output
+        # rows has fewer of them than there are pairs (the down projection of 512 tokens: 32 tiles for 74 pairs) and is
+        # cut over k into the number of slices (up to 4, each at least 1,024 of k) that takes the fewest rounds of the pairs.
+        tiles = -(-out_features // 256) * -(-n // 256)
+        pairs = max(1, sm_count() // 2)
+        tile_us = in_features * 0.00585                  # 256 x 256 x k on two SMs at 11.2 TFLOP/s each
+        best, best_time = 1, -(-tiles // pairs) * tile_us
+        for s in range(2, min(4, in_features // 1024) + 1):
+            # rounds of the pairs, each 1/s as long; the slices' 32-bit sums are written, and read again by the consumer
+            time = -(-tiles * s // pairs) * tile_us / s + s * n * out_features * 8 / 5e6
+            if time < best_time - 1e-9:
+                best, best_time = s, time
+        return best
     tiles = -(-out_features // 128) * -(-n // (256 if n > 128 else 128 if n > 64 else 64 if n > 32 else 32))
     slots = sm_count() * (2 if n <= 64 else 1)
-    if n > 256 or tiles >= slots:
+    if tiles >= slots:
         return 1
     return max(1, min(8, slots // tiles, (in_features // 64) // 8))
 

@@ -73,7 +73,8 @@ class Attention(Mixer):
         nq, nkv, D = s.num_heads, s.num_kv_heads, s.head_dim
         own_kv = s.kv_source is None
         qkv = rt.buffer("attention.qkv", (n, (nq + 2 * nkv) * D if own_kv else nq * D))
-        qkv = self.qkv.forward(h, qkv, allow_partials=True)      # [n, features], or partial sums [s, n, features]
+        # [n, features], or partial sums [s, n, features] in steps of few tokens (the inputs kernel adds them one head a warp)
+        qkv = self.qkv.forward(h, qkv, allow_partials=n <= 256)
         q = rt.buffer("attention.q", (n, nq, D))
         meta = step.group(cache.group_index)
         ops.attention_inputs(qkv, q, cache.k, cache.v, self.q_norm, self.k_norm, s.qk_norm_eps,
