@@ -361,7 +361,9 @@ def test_one_layer_at_apertus_8b_sizes(dtype):
         assert float((got - refs[0][:142]).abs().max()) <= tol
         used = {k: v - before.get(k, 0) for k, v in library.call_counts.items() if v > before.get(k, 0)}
         if dtype == "bfloat16":                                        # the kernels written for these sizes did the work
-            assert used.get("ti_attention_prefill_tc") == 1 and used.get("ti_gemm_tcgen05") == 5         # four of the layer, and the head
+            # 142 tokens: q|k|v, o and down on the 128-row product; the up projection and the head, whose k cannot be cut,
+            # on the product with the tokens in the tensor-memory lanes (two halves of 128)
+            assert used.get("ti_attention_prefill_tc") == 1 and used.get("ti_gemm_tcgen05") == 3 and used.get("ti_gemm_tcgen05_decode") == 2
             assert "ti_attention_prefill" not in used and "ti_gemm_plain" not in used and "ti_attention_plain" not in used
         else:
             assert "ti_gemm_tcgen05" not in used and "ti_attention_prefill_tc" not in used

@@ -670,6 +670,8 @@ def test_gemm_tcgen05(ops, n, out, k, splits):
 
 @pytest.mark.parametrize("n,out,k,tile,splits", [(9, 100, 72, 16, 1), (37, 301, 120, 48, 1), (64, 512, 1024, 112, 4), (128, 384, 512, 256, 1),
                                                  (100, 4099, 264, 160, 3), (17, 2000, 4160, 240, 2), (64, 1000, 584, 0, 1),
+                                                 (130, 301, 120, 48, 1), (200, 1000, 584, 0, 1), (256, 700, 2048, 112, 2),     # two halves of 128 tokens
+                                                 (255, 512, 1024, 256, 1),
                                                  (33, 3000, 200, 32, 1)])     # the last one: a block walks several tiles
 def test_gemm_tcgen05_decode(ops, n, out, k, tile, splits):
     """The decode-batch product (tokens in the tensor-memory lanes, weight rows in tiles of any multiple of 16)

@@ -1,4 +1,4 @@
-// Tensor-core product for decode batches (up to 128 tokens): y[n, out] = x[n, in] · W[out, in]ᵀ in
+// Tensor-core product for decode batches and short prompts (up to 256 tokens): y[n, out] = x[n, in] · W[out, in]ᵀ in
 // bfloat16 with 32-bit accumulation, built to stream W once from HBM with every SM equally loaded.
 //
 // Here the TOKENS are the 128-row operand of tcgen05.mma (rows beyond n are zero-filled by TMA and
@@ -7,7 +7,8 @@
 // (21,504 rows: 135 tiles of 160; 131,072 rows: 586 tiles of 224 = 3.96 rounds of 148), where tiles of
 // a fixed 128 rows leave either a ragged second round or SMs with a short pipeline. One block per SM
 // owns all of the SM's shared memory: a stage holds 64 of k (16 KB of tokens, 128 bytes per weight
-// row), five to eight stages deep, which keeps 100 to 160 KB of weight loads in flight per SM.
+// row), five to eight stages deep, which keeps 100 to 160 KB of weight loads in flight per SM. A step of
+// 129 to 256 tokens is two such token tiles per stage and two accumulators: the weights are still read once.
 // Products with few rows are also cut over k (32-bit partial sums [split, n, out], added in split
 // order by the consumer), with fewer and longer slices than tiles of 128 rows need.
 //
@@ -41,6 +42,7 @@ struct Params {
     int nt;                        // weight rows per tile (multiple of 16, at most 256)
     int m_tiles, splits, k_blocks;
     int stages, stage_bytes, tmem_cols;
+    int halves, acc_stride;        // 128-token halves of the step (1 or 2) and the tensor-memory columns between their accumulators
     long long ldy;
     int epilogue;
     XieluParams act;
@@ -116,7 +118,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
     tc_fence_after();
     TileIter it;
     it.id = blockIdx.x; it.step = gridDim.x; it.total = p.m_tiles * p.splits;
-    const int b_bytes = p.nt * BK * 2;
+    const int b_bytes = p.nt * BK * 2, a_bytes = p.halves * A_BYTES;
 
     // The weights do not depend on the previous kernel: the loads of the first tile's first weight blocks
     // (as many as there are stages) are on their way before the wait for it. Its results (the tokens,
@@ -129,8 +131,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
             if (lane == 0)
                 for (int s = 0; s < ahead; ++s) {
                     const unsigned bar = full0 + 8 * s;
-                    mbar_expect_tx(bar, (unsigned)(A_BYTES + b_bytes));
-                    tma_load_2d(smem_addr(tiles + (size_t)s * p.stage_bytes) + A_BYTES, &map_w, (first.kb_lo + s) * BK, first.m * p.nt, bar);
+                    mbar_expect_tx(bar, (unsigned)(a_bytes + b_bytes));
+                    tma_load_2d(smem_addr(tiles + (size_t)s * p.stage_bytes) + a_bytes, &map_w, (first.kb_lo + s) * BK, first.m * p.nt, bar);
                 }
             __syncwarp();
         }
@@ -151,10 +153,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
                 const unsigned bar = full0 + 8 * stage;
                 const unsigned dst = smem_addr(tiles + (size_t)stage * p.stage_bytes);
                 if (issued >= ahead) {                      // else this stage's weights are already on their way
-                    mbar_expect_tx(bar, (unsigned)(A_BYTES + b_bytes));
-                    tma_load_2d(dst + A_BYTES, &map_w, kb * BK, it.m * p.nt, bar);
+                    mbar_expect_tx(bar, (unsigned)(a_bytes + b_bytes));
+                    tma_load_2d(dst + a_bytes, &map_w, kb * BK, it.m * p.nt, bar);
                 }
-                tma_load_2d(dst, &map_x, kb * BK, 0, bar);
+                for (int h = 0; h < p.halves; ++h) tma_load_2d(dst + h * A_BYTES, &map_x, kb * BK, h * BMT, bar);
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
         }
@@ -173,11 +175,14 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
                 if (!ok) break;
                 tc_fence_after();
                 const unsigned a_addr = smem_addr(tiles + (size_t)stage * p.stage_bytes);
-                const unsigned long long da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + A_BYTES);
+                const unsigned long long db = smem_desc_sw128(a_addr + a_bytes);
+                for (int h = 0; h < p.halves; ++h) {       // the second 128 tokens of a step of up to 256 have an accumulator of their own
+                    const unsigned long long da = smem_desc_sw128(a_addr + h * A_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)          // 16 of k = 32 bytes further along the swizzled row
-                    umma_bf16(tmem_base, da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), idesc,
-                              (kb > it.kb_lo || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / 16; ++k)      // 16 of k = 32 bytes further along the swizzled row
+                        umma_bf16(tmem_base + (unsigned)(h * p.acc_stride), da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), idesc,
+                                  (kb > it.kb_lo || k > 0) ? 1u : 0u);
+                }
                 umma_commit(empty0 + 8 * stage);           // the stage is free once these MMAs have read it
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
             }
@@ -189,7 +194,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
         // ---------------------------------------------------------------- epilogue (16 warps)
         const int quarter = warp & 3;                      // the tensor-memory lanes this warp may read
         const int col_group = (warp - 2) >> 2;             // four warps share a quarter: chunks of 32 columns go round among them
-        const int token = quarter * 32 + lane;
         const bool vec_bf16 = (p.ldy % 8 == 0) && (((uintptr_t)y & 15) == 0);
         const bool vec_f32 = (p.ldy % 4 == 0) && (((uintptr_t)y & 15) == 0);
         const XieluPacked act = xielu_pack(p.act);
@@ -201,8 +205,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
             tc_fence_after();
             const int m0 = it.m * p.nt;
             const int cols = min(p.nt, p.M - m0);          // features of this tile that exist
-            if (quarter * 32 < p.N) {                      // uniform across the warp: some of its tokens exist
-                const unsigned t_row = tmem_base + ((unsigned)(quarter * 32) << 16);
+            for (int h = 0; h < p.halves; ++h) {
+            const int token = h * BMT + quarter * 32 + lane;
+            if (h * BMT + quarter * 32 < p.N) {            // uniform across the warp: some of its tokens exist
+                const unsigned t_row = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(h * p.acc_stride);
 #pragma unroll 1
                 for (int c = col_group * 32; c < cols; c += (EPI_WARPS / 4) * 32) {
                     const int count = min(32, p.nt - c);   // 32, or 16 at the end of a tile whose width is an odd multiple of 16
@@ -238,6 +244,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
                     }
                 }
             }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce);
@@ -261,8 +268,8 @@ int tensor_map_2d(CUtensorMap* out, const void* ptr, unsigned long long rows, un
     return ti_tensor_map_bf16(out, ptr, 2, dims, strides, box, true);
 }
 
-int stages_for(int nt) {
-    const int stage = A_BYTES + nt * BK * 2;
+int stages_for(int nt, int halves = 1) {
+    const int stage = halves * A_BYTES + nt * BK * 2;
     const int fit = (SMEM_LIMIT - 1024 /*alignment*/ - 256 /*barriers*/) / stage;
     return fit > MAX_STAGES ? MAX_STAGES : fit;
 }
@@ -281,7 +288,7 @@ void plan(int n, int out, int in, int max_splits, int sm_count, int* nt_out, int
     for (int s = 1; s <= max_splits && s <= 8; ++s) {
         if (s > 1 && k_blocks / s < 8) break;              // a slice has at least 512 of k
         for (int nt = 16; nt <= 256; nt += 16) {
-            if (stages_for(nt) < 3) continue;
+            if (stages_for(nt, n > BMT ? 2 : 1) < 3) continue;
             const long long tiles = (long long)((out + nt - 1) / nt) * s;
             const long long rounds = (tiles + sm_count - 1) / sm_count;
             const double kb = (double)((k_blocks + s - 1) / s);
@@ -317,15 +324,15 @@ extern "C" int ti_gemm_tcgen05_decode_plan(int n, int out, int in, int max_split
 }
 
 // y: [n, ldy] bfloat16 (float32 for the logits epilogue), or partial sums [splits, n, ldy] float32 for the
-// partial epilogue. n <= 128. `nt` and `splits` as given by the plan (nt 0: plan here, with no k slices).
+// partial epilogue. n <= 256 (from 129 tokens on as two halves of 128 with an accumulator each). `nt` and `splits` as given by the plan (nt 0: plan here, with no k slices).
 // `status` is a device word that must be zero; non-zero afterwards means a wait ran out.
 // Returns 2 when the sizes are outside what the kernel takes (the caller then uses another product).
 extern "C" int ti_gemm_tcgen05_decode(void* y, long long ldy, const void* x, long long ldx, const void* W, int n, int out, int in,
                                       int nt, int splits, int epilogue, float alpha_p, float alpha_n, float beta, float eps,
                                       int* status, cudaStream_t stream) {
     if (n == 0) return 0;
-    if (n > BMT || in % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)W & 15) || ((uintptr_t)x & 15) || in < 8) {
-        ti_fail("gemm_tcgen05_decode takes up to %d tokens and 16-byte aligned rows: n=%d, in=%d, ldx=%lld", BMT, n, in, ldx);
+    if (n > 2 * BMT || in % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)W & 15) || ((uintptr_t)x & 15) || in < 8) {
+        ti_fail("gemm_tcgen05_decode takes up to %d tokens and 16-byte aligned rows: n=%d, in=%d, ldx=%lld", 2 * BMT, n, in, ldx);
         return 2;
     }
     TI_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_tcgen05_decode: unknown epilogue %d", epilogue);
@@ -340,11 +347,13 @@ extern "C" int ti_gemm_tcgen05_decode(void* y, long long ldy, const void* x, lon
     p.splits = splits < 1 ? 1 : (splits > p.k_blocks ? p.k_blocks : splits);
     TI_REQUIRE(p.splits == splits || splits < 1, "gemm_tcgen05_decode: %d slices of %d blocks of k", splits, p.k_blocks);
     TI_REQUIRE(p.splits == 1 || epilogue == EPI_PARTIAL, "gemm_tcgen05_decode: a split product leaves partial sums");
-    p.stages = stages_for(nt);
+    p.halves = n > BMT ? 2 : 1;
+    p.stages = stages_for(nt, p.halves);
     TI_REQUIRE(p.stages >= 2, "gemm_tcgen05_decode: tile width %d leaves no room for a pipeline", nt);
-    p.stage_bytes = A_BYTES + nt * BK * 2;
+    p.stage_bytes = p.halves * A_BYTES + nt * BK * 2;
     p.tmem_cols = 32;
-    while (p.tmem_cols < nt) p.tmem_cols *= 2;
+    while (p.tmem_cols < p.halves * nt) p.tmem_cols *= 2;
+    p.acc_stride = p.halves == 2 ? p.tmem_cols / 2 : 0;          // a power of two of at least nt columns
     p.ldy = ldy; p.epilogue = epilogue; p.act = XieluParams{alpha_p, alpha_n, beta, eps}; p.status = status;
     CUtensorMap mw, mx;
     if (int rc = tensor_map_2d(&mw, W, out, in, in, nt)) return rc;

@@ -106,7 +106,8 @@ def tc_splits(out_features: int, in_features: int, n: int) -> int:
     return max(1, min(8, slots // tiles, (in_features // 64) // 8))
 
 
-# The product with the tokens in the tensor-memory lanes (gemm_tcgen05_decode.cu) takes up to 128 tokens.
+# The product with the tokens in the tensor-memory lanes (gemm_tcgen05_decode.cu) takes up to 256 tokens (two halves of
+# 128 from 129 on: a prompt of 256 tokens runs its up projection in 55 us there instead of 67 us in two rounds of SM pairs).
 # The engine uses it from 65 tokens on for the products whose k cannot be cut (activation or logits
 # epilogue). Measured inside a decode step of Apertus-8B layers against the 128-row kernel: at 128 tokens
 # the up projection takes 41.6 us instead of 58.0 (its 168 tiles of 128 rows need a second round of blocks;
@@ -115,7 +116,7 @@ def tc_splits(out_features: int, in_features: int, n: int) -> int:
 # for 8 layers at 48 tokens), and products that may be cut over k are no faster here, while more slices cost
 # their consumer more (residual add + norm of 128 tokens: 8 us with 4 slices, 15 us with 7).
 DECODE_PRODUCT_MIN_TOKENS = 65
-DECODE_PRODUCT_MAX_TOKENS = 128
+DECODE_PRODUCT_MAX_TOKENS = 256
 _plans = {}
 
 
