@@ -350,7 +350,7 @@ def test_one_layer_at_apertus_8b_sizes(dtype):
         folder = write_model_folder(ApertusConfig.from_dict(cfg_dict), 5, os.path.join(d, "m"))
         pc, pw = plain.load_folder(folder)
         pdt = torch.float32 if dtype == "float32" else torch.bfloat16
-        prompts = helpers.random_prompts(16384, [150, 37, 330], 6)
+        prompts = helpers.random_prompts(16384, [150, 37, 400], 6)
         refs = [plain.forward(pc, pw, p, pdt) for p in prompts]
         eng = ti.load_model(folder, dtype=dtype, max_context=512, max_seqs=2)
         tol = tolerance(dtype, refs[0])
@@ -363,8 +363,10 @@ def test_one_layer_at_apertus_8b_sizes(dtype):
         if dtype == "bfloat16":                                        # the kernels written for these sizes did the work
             # 142 tokens: q|k|v, o and down on the 128-row product; the up projection and the head, whose k cannot be cut,
             # on the product with the tokens in the tensor-memory lanes (two halves of 128)
-            assert used.get("ti_attention_prefill_tc") == 1 and used.get("ti_gemm_tcgen05") == 3 and used.get("ti_gemm_tcgen05_decode") == 2
-            assert "ti_attention_prefill" not in used and "ti_gemm_plain" not in used and "ti_attention_plain" not in used
+            assert used.get("ti_gemm_tcgen05") == 3 and used.get("ti_gemm_tcgen05_decode") == 2
+            # a short prompt: the mma.sync attention (the tensor-memory kernel takes sequences beyond 384 positions, below)
+            assert used.get("ti_attention_prefill") == 1 and "ti_attention_prefill_tc" not in used
+            assert "ti_gemm_plain" not in used and "ti_attention_plain" not in used
         else:
             assert "ti_gemm_tcgen05" not in used and "ti_attention_prefill_tc" not in used
         for t in range(142, 150):                                      # the last tokens one by one
@@ -384,16 +386,18 @@ def test_one_layer_at_apertus_8b_sizes(dtype):
             assert library.call_counts.get("ti_gemm_tcgen05_decode", 0) - before.get("ti_gemm_tcgen05_decode", 0) == 2   # up projection and head
         eng.free_sequence(a)
         eng.free_sequence(b)
-        # 330 + 37 tokens in one step: the o and down products have fewer tiles of 256 x 256 than there are SM pairs and
-        # come in k slices that the norms add up.
+        # 400 + 37 tokens in one step: the o and down products have fewer tiles of 256 x 256 than there are SM pairs and
+        # come in k slices that the norms add up; a sequence of 400 positions takes the tensor-memory attention.
         a, b = eng.new_sequence(), eng.new_sequence()
-        wanted = [0, 100, 255, 256, 329]
+        wanted = [0, 100, 255, 256, 399]
+        before = dict(library.call_counts)
         got = eng.step([(a, prompts[2]), (b, prompts[1])], [wanted, [0, 36]]).cpu()
         want = torch.stack([refs[2][i] for i in wanted] + [refs[1][0], refs[1][36]])
         assert float((got - want).abs().max()) <= tolerance(dtype, refs[2])
         if dtype == "bfloat16":
             from tileinfer_b200.kernels import fast
-            assert fast.tc_splits(4096, 21504, 367) > 1 and fast.tc_splits(4096, 4096, 367) > 1
+            assert fast.tc_splits(4096, 21504, 437) > 1 and fast.tc_splits(4096, 4096, 437) > 1
+            assert library.call_counts.get("ti_attention_prefill_tc", 0) - before.get("ti_attention_prefill_tc", 0) == 1
         eng.check_health()
 
 

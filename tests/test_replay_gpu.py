@@ -29,7 +29,7 @@ CASES = {
     "8B layers": (LAYERS_8B, 4, [3, 70, 130, 33]),
     "A": (helpers.TINY_A, 0, [5, 9, 13, 40, 70, 33, 100]),
     "B": (helpers.TINY_B, 1, [1, 4, 17, 33, 70, 129, 64]),
-    "D": (helpers.TINY_D, 3, [3, 70, 130, 200, 64, 257, 31]),       # head size 64: the tensor-core prefill attention
+    "D": (helpers.TINY_D, 3, [3, 70, 130, 200, 64, 450, 31]),       # head size 64: the tensor-core prefill attention (beyond 384 positions)
 }
 
 

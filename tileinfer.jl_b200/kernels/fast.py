@@ -237,6 +237,10 @@ def decode_splits(batch: int, kv_heads: int, max_context: int) -> int:
     return max(1, min(want, 32, -(-max_context // 64)))
 
 
+SHORT_PROMPT = 384
+SHORT_STEP = 512
+
+
 def attention(out, q, cache, meta, step, spec) -> bool:
     if q.dtype != torch.bfloat16:
         return False
@@ -269,7 +273,12 @@ def attention(out, q, cache, meta, step, spec) -> bool:
     tokens_per_tile = 128 // group
     # The tensor-core kernel for the sizes it takes (head size 64 or 128, a power-of-two group).
     blocks = sum(-(-n // (2 * tokens_per_tile)) for n in step.host_q_lens)
-    rc = lib().ti_attention_prefill_tc(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0],
+    # A short step of short sequences (every one ends within SHORT_PROMPT positions, SHORT_STEP tokens in all) takes the
+    # mma.sync kernel: with three key steps or fewer per block, and fewer blocks than SMs, the tensor-memory kernel's
+    # set-up outweighs its products (a layer of one 256-token prompt: 12 us less; level at 448 tokens; the tensor-memory
+    # kernel 2 us ahead at 512, and ahead for four or more prompts of 256 tokens in one step).
+    short = step.max_kv_len <= SHORT_PROMPT and step.n_tokens <= SHORT_STEP
+    rc = 2 if short else lib().ti_attention_prefill_tc(out.data_ptr(), q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), cache.k.shape[0],
                                        meta.block_table.data_ptr(), meta.block_table.stride(0), step.seq_slots.data_ptr(),
                                        step.cu_seqlens.data_ptr(), step.kv_lens.data_ptr(), step.n_seqs, step.n_tokens, blocks,
                                        spec.scale, spec.num_heads, spec.num_kv_heads, spec.head_dim, cache.page_size,
