@@ -354,7 +354,7 @@ def run_sweep(args, pk, pk_source):
         pt = decode_point(engine, b, steps, warmup, cfg.vocab_size, pk, cached=c)
         decode.append({"batch": b, "cached": c, "ms": round(pt["ms"], 4), "tok_s": round(pt["value"], 1), "frac": round(pt["frac"], 4)})
     prefill = []
-    for tokens in (128, 512, 2048, 8192):
+    for tokens in (128, 256, 512, 1024, 2048, 8192):
         ms = time_prefill(engine, tokens, cfg.vocab_size, reps=2)
         flops = flops_prefill(cfg_dict, cfg.num_hidden_layers, tokens)
         prefill.append({"tokens": tokens, "ms": round(ms, 3), "tok_s": round(tokens * 1000.0 / ms, 1),
