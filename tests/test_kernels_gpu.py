@@ -509,7 +509,8 @@ def test_attention_prefill(ops, nq, nkv, D):
     assert float((head - vs[3][5, 1 // (nq // nkv)]).abs().max()) < 0.2
 
 
-@pytest.mark.parametrize("nq,nkv,D,window", [(32, 8, 128, 0), (8, 8, 64, 0), (16, 1, 64, 0), (4, 2, 128, 0), (6, 3, 64, 150), (8, 1, 128, 333)])
+@pytest.mark.parametrize("nq,nkv,D,window", [(32, 8, 128, 0), (8, 8, 64, 0), (16, 1, 64, 0), (4, 2, 128, 0), (6, 3, 64, 150), (8, 1, 128, 333),
+                                             (24, 8, 128, 0), (6, 2, 64, 0), (5, 1, 64, 0), (14, 2, 128, 150), (12, 1, 64, 0)])   # groups of 3, 5, 7, 12
 def test_attention_prefill_tensor_core(ops, nq, nkv, D, window):
     """The tcgen05 prefill kernel on unequal sequences in one launch (some continuing from cached
     positions, one a single token, one of several key steps), shuffled pages, with and without a

@@ -128,6 +128,18 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 9) tmem_alloc(smem_addr(tmem_slot), C::TMEM_COLS);
+    // A group that does not divide 128 leaves the last rows of a query tile without a (token, head): the TMA box does not
+    // write them, so they are zeroed here once (whole 128-byte rows: the swizzle moves bytes within a row only), and
+    // nothing is written out for them below.
+    const int rows_used = tokens_per_tile * p.group;
+    if (rows_used < ROWS) {
+        const int spare = ROWS - rows_used, words = spare * 32;         // 32 words of 4 bytes a row
+        for (int i = threadIdx.x; i < 2 * C::HALVES * words; i += THREADS) {
+            const int blk = i / words, w = i % words;                    // blk: (tile, 64-column block)
+            reinterpret_cast<unsigned*>(q_tiles + (size_t)blk * C::HALF_BYTES + (size_t)rows_used * 128)[w] = 0u;
+        }
+        fence_async_smem();
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -136,7 +148,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
     if (warp == 8) {
         // ---------------------------------------------------------------- loads (one thread)
         if (lane == 0) {
-            mbar_expect_tx(q_full, 2 * C::Q_TILE_BYTES);
+            mbar_expect_tx(q_full, (unsigned)(2 * rows_used * D * 2));
             for (int x = 0; x < 2; ++x)
                 for (int h = 0; h < C::HALVES; ++h)
                     tma_load_3d(smem_addr(q_tiles + x * C::Q_TILE_BYTES + h * C::HALF_BYTES), &map_q, h * 64, kvh * p.group,
@@ -326,7 +338,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc_kernel(const 
                 unsigned r[32];
                 tmem_ld32(o_addr + c * 32, r);
                 tmem_ld_wait();
-                if (tok < q_len) {
+                if (tok < q_len && row < rows_used) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 w;
@@ -367,9 +379,9 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 }  // namespace
 
 // out, q: [tokens, nq, D] bfloat16; k_cache, v_cache: [pages, nkv, 64, D] bfloat16. `total_blocks` = sum over
-// the sequences of ceil(new tokens / (256 / (nq / nkv))). `status` is a device word that must be zero; a
+// the sequences of ceil(new tokens / (2 * (128 / (nq / nkv)))), the division inside rounding down. `status` is a device word that must be zero; a
 // non-zero value afterwards means a wait ran out. Returns 2 when the sizes are outside what this kernel
-// takes (head size 64 or 128, nq / nkv a power of two up to 16, pages of 64): the caller then runs the
+// takes (head size 64 or 128, 1 to 16 query heads per KV head, pages of 64): the caller then runs the
 // kernel for all sizes.
 extern "C" int ti_attention_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache, int n_pages,
                                        const int* block_table, int table_stride, const int* seq_slots,
@@ -378,9 +390,9 @@ extern "C" int ti_attention_prefill_tc(void* out, const void* q, const void* k_c
                                        cudaStream_t stream) {
     if (n_seqs == 0 || total_blocks == 0) return 0;
     const int group = nkv > 0 ? nq / nkv : 0;
-    if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || (group & (group - 1)) || group > 16 || (D != 64 && D != 128) || nkv > 65535 ||
+    if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || group < 1 || group > 16 || (D != 64 && D != 128) || nkv > 65535 ||
         ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15)) {
-        ti_fail("attention_prefill_tc takes head size 64 or 128, pages of 64 and 1, 2, 4, 8 or 16 query heads per KV head; "
+        ti_fail("attention_prefill_tc takes head size 64 or 128, pages of 64 and 1 to 16 query heads per KV head; "
                 "got head size %d, page %d, %d/%d heads", D, page_size, nq, nkv);
         return 2;
     }

@@ -233,12 +233,12 @@ def bench_sampling(batch, vocab, once):
         print("launched 3 kernels of each kind")
 
 
-def timeline(batch, layers, cached=1023, prefill_tokens=0):
+def timeline(batch, layers, cached=1023, prefill_tokens=0, shape=None):
     from torch.profiler import ProfilerActivity, profile
 
     from ..config import ApertusConfig
     from ..engine import Engine
-    s = APERTUS_8B_LAYER
+    s = dict(APERTUS_8B_LAYER, **(shape or {}))
     cfg = ApertusConfig.from_dict({
         "architectures": ["ApertusForCausalLM"], "num_hidden_layers": layers, "hidden_size": s["hidden"],
         "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["head_dim"],
@@ -307,6 +307,7 @@ def main(argv=None):
     ap.add_argument("--products", default="new", choices=["new", "rows128"],
                     help="timeline: the engine's choice of product kernels, or the 128-row kernel everywhere")
     ap.add_argument("--once", action="store_true", help="a few eager launches and no timing (for ncu)")
+    ap.add_argument("--shape", default="", help="timeline: layer sizes other than Apertus-8B's, as hidden,heads,kv_heads,head_dim,intermediate")
     a = ap.parse_args(argv)
     if a.products == "rows128":
         fast.DECODE_PRODUCT_MAX_TOKENS = 0
@@ -323,7 +324,8 @@ def main(argv=None):
     elif a.what == "sampling":
         bench_sampling(a.batch, a.out if a.out != 21504 else 131072, a.once)
     else:
-        timeline(a.batch, a.layers, prefill_tokens=a.tokens if a.tokens > 1 else 0)
+        shape = dict(zip(("hidden", "heads", "kv_heads", "head_dim", "intermediate"), (int(v) for v in a.shape.split(",")))) if a.shape else None
+        timeline(a.batch, a.layers, prefill_tokens=a.tokens if a.tokens > 1 else 0, shape=shape)
     return 0
 
 
