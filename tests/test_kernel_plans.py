@@ -67,6 +67,7 @@ def test_slices_of_the_other_decode_products():
     assert fast.tc_splits(4096, 21504, 512) == 2 and fast.tc_splits(4096, 4096, 367) == 2     # 32 tiles -> 64
     assert fast.tc_splits(4096, 21504, 768) == 3                                         # 48 tiles -> 144 in two rounds of a third
     assert fast.tc_splits(4096, 1024, 512) == 1                                          # a slice keeps at least 1,024 of k
+    assert fast.tc_splits(8192, 43008, 1024) == 1                                        # 128 tiles, two rounds: four slices would gain 2 %
     assert fast.decode_splits(1, 8, 4096) == 32 and fast.decode_splits(64, 8, 4096) == 1
 
 
