@@ -330,7 +330,8 @@ def test_gemv_bf16(ops, n, out, k):
     close(got, ref, torch.bfloat16, ulps=4.0)
 
 
-@pytest.mark.parametrize("nq,nkv,D", [(32, 8, 128), (6, 3, 32), (5, 1, 48), (4, 2, 16), (16, 1, 64), (12, 3, 96)])
+@pytest.mark.parametrize("nq,nkv,D", [(32, 8, 128), (6, 3, 32), (5, 1, 48), (4, 2, 16), (16, 1, 64), (12, 3, 96),
+                                      (32, 1, 64), (40, 2, 128), (17, 1, 32)])       # more than 16 query heads per KV head: blocks of 16
 def test_attention_decode(ops, nq, nkv, D):
     """Batch of sequences of very different lengths (one key, a page border, hundreds of keys), shuffled
     pages, against exact 32-bit attention. One sequence has a far key made to stand out."""
@@ -510,7 +511,8 @@ def test_attention_prefill(ops, nq, nkv, D):
 
 
 @pytest.mark.parametrize("nq,nkv,D,window", [(32, 8, 128, 0), (8, 8, 64, 0), (16, 1, 64, 0), (4, 2, 128, 0), (6, 3, 64, 150), (8, 1, 128, 333),
-                                             (24, 8, 128, 0), (6, 2, 64, 0), (5, 1, 64, 0), (14, 2, 128, 150), (12, 1, 64, 0)])   # groups of 3, 5, 7, 12
+                                             (24, 8, 128, 0), (6, 2, 64, 0), (5, 1, 64, 0), (14, 2, 128, 150), (12, 1, 64, 0),    # groups of 3, 5, 7, 12
+                                             (32, 1, 64, 0), (40, 2, 128, 0), (128, 1, 64, 200)])                                  # 32, 20 and 128 heads per KV head
 def test_attention_prefill_tensor_core(ops, nq, nkv, D, window):
     """The tcgen05 prefill kernel on unequal sequences in one launch (some continuing from cached
     positions, one a single token, one of several key steps), shuffled pages, with and without a
@@ -599,6 +601,7 @@ def test_attention_window_edge(ops):
 
 
 @pytest.mark.parametrize("nq,nkv,D,splits,lengths", [(8, 2, 64, 6, [3, 1500, 64, 129, 700]),
+                                                     (40, 2, 64, 5, [7, 1000, 300]),               # 20 query heads per KV head
                                                      (32, 8, 128, 9, [5, 32768, 700, 20000])])    # Apertus-8B heads, long contexts
 def test_attention_decode_with_shared_out_slots(ops, nq, nkv, D, splits, lengths):
     """Decode attention over sequences of very unequal lengths with the work slots shared out by length

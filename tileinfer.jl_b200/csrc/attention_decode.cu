@@ -50,7 +50,9 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
     // slot without work; then the sequence's length) the slots are shared out by the host in proportion to
     // the sequences' lengths.
     int b, split, parts, kv_len, slot;
-    const int kvh = blockIdx.y;
+    // More than 16 query heads per KV head: blocks of 16 of them each (`slabs` per KV head), which read the keys again.
+    const int full_group = nq / nkv, slabs = (full_group + 15) / 16;
+    const int kvh = blockIdx.y / slabs, slab = blockIdx.y % slabs;
     if (TABLE) {                                             // one load: the slot's work and its sequence's length
         slot = blockIdx.x;
         const int2 w = __ldcg(reinterpret_cast<const int2*>(work) + slot);
@@ -62,7 +64,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
         kv_len = __ldcg(kv_lens + b);
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int group = nq / nkv;
+    const int group = min(16, full_group - slab * 16);            // this block's query heads
     // The step's lengths and block tables were uploaded before its first kernel, and every page but
     // the sequence's last one holds only older positions: their copies start BEFORE waiting for the
     // kernel that writes this step's key, value and query.
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
     // Query rows = the heads of this KV head's group, padded to 16.
     unsigned qf[KS][4];
     {
-        const bf16* q0 = q + ((size_t)b * nq + (size_t)kvh * group) * D;
+        const bf16* q0 = q + ((size_t)b * nq + (size_t)kvh * full_group + slab * 16) * D;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int d = ks * 16 + 2 * t;
@@ -161,7 +163,7 @@ __global__ void __launch_bounds__(AD_THREADS) attention_decode_kernel(
             L += src[D + 1] * f;
             O += src[d] * f;
         }
-        const int head = kvh * group + row;
+        const int head = kvh * full_group + slab * 16 + row;
         if (splits == 1) {
             out[((size_t)b * nq + head) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);   // a sequence without keys: zeros
         } else {
@@ -243,11 +245,12 @@ static int launch_decode(bf16* out, const bf16* q, const bf16* k, const bf16* v,
         if (e != cudaSuccess) return ti_fail("attention_decode: %s", cudaGetErrorString(e));
         configured = true;
     }
+    const int slabs = (nq / nkv + 15) / 16;
     if (work != nullptr && splits > 1)
-        ti_launch(attention_decode_kernel<D, true>, dim3(B * splits, nkv), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
+        ti_launch(attention_decode_kernel<D, true>, dim3(B * splits, nkv * slabs), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
                   seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window);
     else
-        ti_launch(attention_decode_kernel<D, false>, dim3(splits, nkv, B), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
+        ti_launch(attention_decode_kernel<D, false>, dim3(splits, nkv * slabs, B), dim3(AD_THREADS), smem, stream, out, q, k, v, table, table_stride,
                   seq_slots, kv_lens, work, ws_o, ws_ml, scale * 1.4426950408889634f, nq, nkv, splits, window);
     if (int rc = ti_check_launch("attention_decode")) return rc;
     if (splits > 1) {
@@ -268,8 +271,8 @@ extern "C" int ti_attention_decode_shared(void* out, const void* q, const void* 
                                           const int* work, const int* seq_work, float* ws_o, float* ws_ml, float scale, int B,
                                           int nq, int nkv, int D, int page_size, int splits, int window, cudaStream_t stream) {
     if (B == 0) return 0;
-    if (page_size != AD_PAGE || nq % nkv != 0 || nq / nkv > 16 || D % 16 != 0 || B > 32767 || nkv > 65535) {
-        ti_fail("attention_decode takes page size %d, at most 16 query heads per KV head and head sizes in steps of 16; "
+    if (page_size != AD_PAGE || nq % nkv != 0 || nq / nkv > 128 || D % 16 != 0 || B > 32767 || (long long)nkv * ((nq / nkv + 15) / 16) > 65535) {
+        ti_fail("attention_decode takes page size %d, at most 128 query heads per KV head and head sizes in steps of 16; "
                 "got page %d, %d/%d heads, head size %d", AD_PAGE, page_size, nq, nkv, D);
         return 2;
     }

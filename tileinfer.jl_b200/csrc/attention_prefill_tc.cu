@@ -381,7 +381,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 // out, q: [tokens, nq, D] bfloat16; k_cache, v_cache: [pages, nkv, 64, D] bfloat16. `total_blocks` = sum over
 // the sequences of ceil(new tokens / (2 * (128 / (nq / nkv)))), the division inside rounding down. `status` is a device word that must be zero; a
 // non-zero value afterwards means a wait ran out. Returns 2 when the sizes are outside what this kernel
-// takes (head size 64 or 128, 1 to 16 query heads per KV head, pages of 64): the caller then runs the
+// takes (head size 64 or 128, 1 to 128 query heads per KV head, pages of 64): the caller then runs the
 // kernel for all sizes.
 extern "C" int ti_attention_prefill_tc(void* out, const void* q, const void* k_cache, const void* v_cache, int n_pages,
                                        const int* block_table, int table_stride, const int* seq_slots,
@@ -390,9 +390,9 @@ extern "C" int ti_attention_prefill_tc(void* out, const void* q, const void* k_c
                                        cudaStream_t stream) {
     if (n_seqs == 0 || total_blocks == 0) return 0;
     const int group = nkv > 0 ? nq / nkv : 0;
-    if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || group < 1 || group > 16 || (D != 64 && D != 128) || nkv > 65535 ||
+    if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || group < 1 || group > ROWS || (D != 64 && D != 128) || nkv > 65535 ||
         ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15)) {
-        ti_fail("attention_prefill_tc takes head size 64 or 128, pages of 64 and 1 to 16 query heads per KV head; "
+        ti_fail("attention_prefill_tc takes head size 64 or 128, pages of 64 and 1 to 128 query heads per KV head; "
                 "got head size %d, page %d, %d/%d heads", D, page_size, nq, nkv);
         return 2;
     }

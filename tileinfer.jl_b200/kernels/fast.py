@@ -272,7 +272,7 @@ def attention(out, q, cache, meta, step, spec) -> bool:
     if group < 1 or group > 128 or spec.num_heads % spec.num_kv_heads:
         return False
     tokens_per_tile = 128 // group
-    # The tensor-core kernel for the sizes it takes (head size 64 or 128, up to 16 query heads per KV head).
+    # The tensor-core kernel for the sizes it takes (head size 64 or 128, up to 128 query heads per KV head).
     blocks = sum(-(-n // (2 * tokens_per_tile)) for n in step.host_q_lens)
     # A short step of short sequences (every one ends within SHORT_PROMPT positions, SHORT_STEP tokens in all) takes the
     # mma.sync kernel: with three key steps or fewer per block, and fewer blocks than SMs, the tensor-memory kernel's
