@@ -278,6 +278,37 @@ def test_a_long_prompt_in_chunks_through_the_tensor_core_attention(dtype):
         eng.check_health()
 
 
+@pytest.mark.parametrize("heads,kv_heads", [(20, 1), (36, 2)])
+def test_many_query_heads_per_kv_head_run_the_fast_attention(heads, kv_heads):
+    """20 and 18 query heads per KV head (more than the 16 a decode block takes at once): a prompt of 500
+    tokens through the tensor-core prefill attention and two shorter ones beside it, then 12 decode steps
+    of the three together, against the plain implementation; the fast kernels are the ones that ran."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.kernels import library
+    from tileinfer_b200.weights import write_model_folder
+    cfg = dict(helpers.TINY_D, num_attention_heads=heads, num_key_value_heads=kv_heads, hidden_size=144, max_position_embeddings=2048)
+    with tempfile.TemporaryDirectory() as d:
+        folder = write_model_folder(ApertusConfig.from_dict(cfg), 12, os.path.join(d, "m"))
+        pc, pw = plain.load_folder(folder)
+        prompts = helpers.random_prompts(pc.vocab, [512, 45, 141], 16)
+        refs = [plain.forward(pc, pw, p, torch.bfloat16) for p in prompts]
+        eng = ti.Engine.load(folder, dtype="bfloat16", max_context=512, max_seqs=3)
+        ids = [eng.new_sequence() for _ in prompts]
+        before = dict(library.call_counts)
+        got = eng.step([(i, p[:-12]) for i, p in zip(ids, prompts)], [[0, len(p) - 13] for p in prompts]).cpu()
+        for n, (p, ref) in enumerate(zip(prompts, refs)):
+            assert float((got[2 * n:2 * n + 2] - ref[[0, len(p) - 13]]).abs().max()) <= tolerance("bfloat16", ref), n
+        for t in range(12, 0, -1):
+            rows = eng.step([(i, [p[-t]]) for i, p in zip(ids, prompts)]).cpu()
+            for n, (p, ref) in enumerate(zip(prompts, refs)):
+                assert float((rows[n] - ref[len(p) - t]).abs().max()) <= tolerance("bfloat16", ref), (n, t)
+        used = {k: v - before.get(k, 0) for k, v in library.call_counts.items() if v > before.get(k, 0)}
+        assert used.get("ti_attention_prefill_tc") == pc.layers and used.get("ti_attention_decode_shared", 0) >= pc.layers
+        assert "ti_attention_plain" not in used and "ti_attention_prefill" not in used
+        eng.check_health()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_long_context_beyond_8192_positions_next_to_a_short_one(dtype):
     """9,000 positions (past the 8,192 of Apertus-8B's rope scaling record, 141 pages) next to a sequence of 300:
