@@ -278,6 +278,32 @@ def test_a_long_prompt_in_chunks_through_the_tensor_core_attention(dtype):
         eng.check_health()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_more_sequences_in_a_decode_step_than_tokens_in_a_prompt_chunk(dtype):
+    """40 sequences with prompt steps cut at 16 tokens: the prompts go through in several chunks, the one-token
+    steps of all 40 together are never cut and have more tokens than any chunk. Logits of the prompts' last
+    tokens and of four decode steps against the plain implementation."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.weights import write_model_folder
+    with tempfile.TemporaryDirectory() as d:
+        folder = write_model_folder(ApertusConfig.from_dict(helpers.TINY_B), 21, os.path.join(d, "m"))
+        pc, pw = plain.load_folder(folder)
+        prompts = helpers.random_prompts(pc.vocab, [5 + (7 * i) % 11 for i in range(40)], 22)
+        pdt = torch.float32 if dtype == "float32" else torch.bfloat16
+        refs = [plain.forward(pc, pw, p, pdt) for p in prompts]
+        eng = ti.Engine.load(folder, dtype=dtype, max_context=64, max_seqs=40, max_step_tokens=16)
+        ids = [eng.new_sequence() for _ in prompts]
+        got = eng.step([(i, p[:-4]) for i, p in zip(ids, prompts)], [[len(p) - 5] for p in prompts]).cpu()
+        for n, (p, ref) in enumerate(zip(prompts, refs)):
+            assert float((got[n] - ref[len(p) - 5]).abs().max()) <= tolerance(dtype, ref), n
+        for t in range(4, 0, -1):
+            rows = eng.step([(i, [p[-t]]) for i, p in zip(ids, prompts)]).cpu()
+            for n, (p, ref) in enumerate(zip(prompts, refs)):
+                assert float((rows[n] - ref[len(p) - t]).abs().max()) <= tolerance(dtype, ref), (n, t)
+        eng.check_health()
+
+
 @pytest.mark.parametrize("heads,kv_heads", [(20, 1), (36, 2)])
 def test_many_query_heads_per_kv_head_run_the_fast_attention(heads, kv_heads):
     """20 and 18 query heads per KV head (more than the 16 a decode block takes at once): a prompt of 500

@@ -49,6 +49,30 @@ def test_a_batch_of_unequal_sequences():
         planner.plan([(a, [1])], [[1]])
 
 
+def test_a_one_token_step_of_more_sequences_than_a_cut_step_has_tokens():
+    """Steps of several tokens per sequence are cut at max_step_tokens, one-token steps never are: 40 sequences
+    with a planner of 8 tokens a step go through both paths, and the general path refuses what it cannot hold
+    instead of writing past its buffers."""
+    cache = Cache([CacheRequest("paged_kv", kv_heads=2, head_dim=16)], torch.float32, "cpu", max_tokens=400, max_seqs=40, page_size=4)
+    planner = StepPlanner(cache, 8, "cpu")
+    slots = [cache.alloc_slot() for _ in range(40)]
+    for i, s in enumerate(slots):
+        cache.reserve([(s, 1 + i % 5)])
+        cache.advance(s, 1 + i % 5)
+    cache.reserve([(s, 1) for s in slots])
+    short = planner.plan_decode(slots, list(range(40)))
+    assert short.token_ids.tolist() == list(range(40)) and short.positions.tolist() == [1 + i % 5 for i in range(40)]
+    assert short.kv_lens.tolist() == [2 + i % 5 for i in range(40)] and short.want_idx.tolist() == list(range(40))
+    places = short.group(0).slot_mapping.tolist()
+    assert places == [place(cache, s, 1 + i % 5) for i, s in enumerate(slots)] and len(set(places)) == 40
+    o, _ = planner._layout(40, 40, 40)
+    assert o["end"] <= planner.capacity
+    first = planner.meta[:o["end"]].clone()
+    with pytest.raises(ValueError, match="max_step_tokens"):
+        planner.plan([(slots[0], list(range(9)))], [[0]])
+    assert torch.equal(planner.meta[:o["end"]], first)
+
+
 def test_the_short_path_for_one_token_steps_writes_what_the_general_one_writes():
     rng = random.Random(3)
     cache, planner = make(max_seqs=6, max_tokens=400)

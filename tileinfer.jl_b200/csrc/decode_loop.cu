@@ -91,7 +91,8 @@ public:
         nvtxRangePop();
         if (rc) return rc;
         turn_ ^= 1;
-        cudaMemcpyAsync(host_[turn_], tokens_, (size_t)rows * sizeof(int), cudaMemcpyDeviceToHost, stream);
+        const cudaError_t copied = cudaMemcpyAsync(host_[turn_], tokens_, (size_t)rows * sizeof(int), cudaMemcpyDeviceToHost, stream);
+        if (copied != cudaSuccess) return ti_fail("the copy of a step's tokens to the host: %s", cudaGetErrorString(copied));
         cudaEventRecord(events_[turn_], stream);
         pending_rows_ = rows;
         if (n_next == 0) return 0;

@@ -31,7 +31,9 @@ void StepPlanner::attach_plan(int group, GroupPlan* plan) {
 
 int StepPlanner::capacity() const {
     const int groups = std::max<int>(1, (int)cache_->groups.size());
-    int cap = align32(max_step_tokens_) * (3 + groups + 1) + 4 * align32(cache_->max_seqs + 1) + 64;
+    // A step of one token per sequence is never cut: it may have more tokens (up to max_seqs) than max_step_tokens.
+    const int most_tokens = std::max(max_step_tokens_, cache_->max_seqs);
+    int cap = align32(most_tokens) * (3 + groups + 1) + 4 * align32(cache_->max_seqs + 1) + 64;
     for (GroupPlan* p : plans_) {
         if (!p) continue;
         int most = 0;
@@ -88,15 +90,17 @@ int32_t* StepPlanner::staging(int* turn) {
     return staging_[t];
 }
 
-void StepPlanner::upload(int turn, int count, int skip, cudaStream_t stream) {
+int StepPlanner::upload(int turn, int count, int skip, cudaStream_t stream) {
     last_upload_bytes = (long long)(count - skip) * 4;
     if (on_device_) {
-        cudaMemcpyAsync(meta_ + skip, staging_[turn] + skip, (size_t)(count - skip) * 4, cudaMemcpyHostToDevice, stream);
+        const cudaError_t e = cudaMemcpyAsync(meta_ + skip, staging_[turn] + skip, (size_t)(count - skip) * 4, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return ti_fail("the copy of a step's metadata to the device: %s", cudaGetErrorString(e)), 2;
         cudaEventRecord(events_[turn], stream);
         in_flight_[turn] = true;
     } else {
         std::memcpy(meta_ + skip, staging_[turn] + skip, (size_t)(count - skip) * 4);
     }
+    return 0;
 }
 
 void StepPlanner::fill_plans(const StepLayout& lay, int32_t* st, const int64_t* lengths_after) {
@@ -123,6 +127,7 @@ int StepPlanner::plan(int n_entries, const int* slots, const int* q_lens, const 
     int turn;
     int32_t* st = staging(&turn);
     if (!st) return ti_fail("no pinned memory for the step's staging buffers"), 2;
+    if (lay.end > capacity_) return ti_fail("a step of %d tokens, %d sequences and %d wanted rows needs %d words of metadata; the buffers hold %d", n, n_entries, nw, lay.end, capacity_), 2;
     std::vector<int64_t> after(n_entries);
     int row = 0, wrow = lay.want, w = 0;
     for (int i = 0; i < n_entries; ++i) {
@@ -151,8 +156,7 @@ int StepPlanner::plan(int n_entries, const int* slots, const int* q_lens, const 
     }
     st[lay.cu + n_entries] = row;
     if (n == n_entries) fill_plans(lay, st, after.data());
-    upload(turn, lay.end, 0, stream);
-    return 0;
+    return upload(turn, lay.end, 0, stream);
 }
 
 int StepPlanner::plan_decode(int batch, const int* slots, const int* tokens, cudaStream_t stream, int64_t* starts) {
@@ -161,6 +165,7 @@ int StepPlanner::plan_decode(int batch, const int* slots, const int* tokens, cud
     int turn;
     int32_t* st = staging(&turn);
     if (!st) return ti_fail("no pinned memory for the step's staging buffers"), 2;
+    if (lay.end > capacity_) return ti_fail("a step of %d sequences needs %d words of metadata; the buffers hold %d", batch, lay.end, capacity_), 2;
     std::vector<int64_t> after(batch);
     for (int i = 0; i < batch; ++i) {
         const int slot = slots[i];
@@ -183,8 +188,7 @@ int StepPlanner::plan_decode(int batch, const int* slots, const int* tokens, cud
     }
     st[lay.cu + batch] = batch;
     fill_plans(lay, st, after.data());
-    upload(turn, lay.end, tokens ? 0 : align32(batch), stream);
-    return 0;
+    return upload(turn, lay.end, tokens ? 0 : align32(batch), stream);
 }
 
 }  // namespace ti

@@ -38,7 +38,7 @@ public:
 
 private:
     int32_t* staging(int* turn);
-    void upload(int turn, int count, int skip, cudaStream_t stream);
+    int upload(int turn, int count, int skip, cudaStream_t stream);
     void fill_plans(const StepLayout& lay, int32_t* st, const int64_t* lengths_after);
 
     CacheBook* cache_;
