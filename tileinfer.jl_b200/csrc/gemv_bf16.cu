@@ -30,6 +30,14 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
     return v;
 }
 
+// The tokens: every block reads all of them, so they are worth a place in L1 (the weights pass it by).
+__device__ __forceinline__ uint4 ld_tokens(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
                                          unsigned b1) {
     asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -85,7 +93,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(const bf16* __
             const bool ok = bb < blk_hi && bb * 32 + 8 * t < K;
             const int idx = bb * 4 + t;
 #pragma unroll
-            for (int j = 0; j < NT; ++j) xb[j][u] = (ok && xv[j]) ? __ldcg(xr[j] + idx) : zero;
+            for (int j = 0; j < NT; ++j) xb[j][u] = (ok && xv[j]) ? ld_tokens(xr[j] + idx) : zero;
         }
 #pragma unroll
         for (int u = 0; u < U; ++u)
