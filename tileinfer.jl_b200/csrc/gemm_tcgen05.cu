@@ -50,6 +50,7 @@ struct Params {
     XieluParams act;
     int* status;
     int tma_out;                   // bfloat16 results leave through shared memory and TMA stores
+    int rotate;                    // every weight tile starts at another place of its k range
 };
 
 // MT: 128-row weight sub-tiles per block. With MT = 2 a block owns 256 weight rows: the token
@@ -81,7 +82,7 @@ template <int BN> __device__ __forceinline__ constexpr unsigned instr_desc() {
 
 struct TileIter {
     int id, step, total;
-    int m, n, kb_lo, kb_hi, split;
+    int m, n, kb_lo, kb_hi, split, rot;
     __device__ bool next(const Params& p) {
         if (id >= total) return false;
         int t = id;
@@ -89,9 +90,11 @@ struct TileIter {
         split = t % p.splits; m = t / p.splits;
         kb_lo = (int)((long long)p.k_blocks * split / p.splits);
         kb_hi = (int)((long long)p.k_blocks * (split + 1) / p.splits);
+        rot = p.rotate ? (m * 7) % (kb_hi - kb_lo) : 0;
         id += step;
         return true;
     }
+    __device__ int kb_at(int i) const { const int n_kb = kb_hi - kb_lo; int k = i + rot; if (k >= n_kb) k -= n_kb; return kb_lo + k; }
 };
 
 // The epilogue of 32 accumulator rows (one warp's tensor-memory lanes, features m_first .. m_first + 31)
@@ -202,7 +205,7 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
                     const unsigned a_dst = smem_addr(tiles + (size_t)s * C::STAGE_BYTES);
 #pragma unroll
                     for (int h = 0; h < MT; ++h)
-                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, (first.kb_lo + s) * BK, (first.m * MT + h) * BM, bar);
+                        tma_load_2d(a_dst + h * (BM * BK * 2), &map_w, first.kb_at(s) * BK, (first.m * MT + h) * BM, bar);
                 }
             __syncwarp();
         }
@@ -220,7 +223,8 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
         bool ok = true;
         int issued = 0;                                     // k blocks of this block so far
         while (lane == 0 && ok && it.next(p)) {
-            for (int kb = it.kb_lo; kb < it.kb_hi; ++kb, ++issued) {
+            for (int i = 0; i < it.kb_hi - it.kb_lo; ++i, ++issued) {
+                const int kb = it.kb_at(i);
                 ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 1);
                 if (!ok) break;
                 const unsigned bar = full0 + 8 * stage;
@@ -248,7 +252,7 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
             if (!ok) break;
             tc_fence_after();
             const unsigned d_tmem = tmem_base + (unsigned)(acc * MT * BN);
-            for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
+            for (int i = 0; i < it.kb_hi - it.kb_lo; ++i) {
                 ok = mbar_wait(full0 + 8 * stage, phase, p.status, 3);
                 if (!ok) break;
                 tc_fence_after();
@@ -259,7 +263,7 @@ __global__ void __launch_bounds__(Cfg<BN, MT>::THREADS, Cfg<BN, MT>::BLOCKS_PER_
 #pragma unroll
                     for (int h = 0; h < MT; ++h)           // the sub-tiles share the token operand
                         umma_bf16(d_tmem + (unsigned)(h * BN), smem_desc_sw128(a_addr + h * (BM * BK * 2)) + (unsigned long long)(2 * k),
-                                  db + (unsigned long long)(2 * k), instr_desc<BN>(), (kb > it.kb_lo || k > 0) ? 1u : 0u);
+                                  db + (unsigned long long)(2 * k), instr_desc<BN>(), (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(empty0 + 8 * stage);           // the stage is free once these MMAs have read it
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
             }
@@ -582,6 +586,10 @@ int gemm_dispatch(void* y, long long ldy, const void* x, long long ldx, const vo
     CUtensorMap mw, mx, my;
     if (int rc = tensor_map(&mw, W, out, in, in, BM)) return rc;
     if (int rc = tensor_map(&mx, x, n, in, ldx, pair ? bn / 2 : bn)) return rc;   // a pair's blocks load half a token tile each
+    // A step of a few tokens: all blocks would ask L2 for the same token lines at the same time, so each weight
+    // tile walks its k range from a start of its own (a function of the tile alone: a token's result does not
+    // depend on the step it is in). With many tokens the tiles of a row of blocks share lines on purpose.
+    p.rotate = n <= 64;
     p.tma_out = bn >= 128 && (epilogue == EPI_NONE || epilogue == EPI_XIELU) && ldy % 8 == 0 && !((uintptr_t)y & 15);
     if (p.tma_out) {
         if (int rc = tensor_map(&my, y, n, out, ldy, 32, 32)) return rc;

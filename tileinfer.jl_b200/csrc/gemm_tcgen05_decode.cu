@@ -42,6 +42,7 @@ struct Params {
     int nt;                        // weight rows per tile (multiple of 16, at most 256)
     int m_tiles, splits, k_blocks;
     int stages, stage_bytes, tmem_cols;
+    int rotate;                    // every weight tile starts at another place of its k range
     int halves, acc_stride;        // 128-token halves of the step (1 or 2) and the tensor-memory columns between their accumulators
     long long ldy;
     int epilogue;
@@ -51,16 +52,18 @@ struct Params {
 
 struct TileIter {
     int id, step, total;
-    int m, split, kb_lo, kb_hi;
+    int m, split, kb_lo, kb_hi, rot;
     __device__ bool next(const Params& p) {
         if (id >= total) return false;
         split = id % p.splits;
         m = id / p.splits;
         kb_lo = (int)((long long)p.k_blocks * split / p.splits);
         kb_hi = (int)((long long)p.k_blocks * (split + 1) / p.splits);
+        rot = p.rotate ? (m * 7) % (kb_hi - kb_lo) : 0;
         id += step;
         return true;
     }
+    __device__ int kb_at(int i) const { const int n_kb = kb_hi - kb_lo; int k = i + rot; if (k >= n_kb) k -= n_kb; return kb_lo + k; }
 };
 
 // The stores of one thread's chunk: `count` consecutive features of one token, starting at a multiple of 16.
@@ -132,7 +135,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
                 for (int s = 0; s < ahead; ++s) {
                     const unsigned bar = full0 + 8 * s;
                     mbar_expect_tx(bar, (unsigned)(a_bytes + b_bytes));
-                    tma_load_2d(smem_addr(tiles + (size_t)s * p.stage_bytes) + a_bytes, &map_w, (first.kb_lo + s) * BK, first.m * p.nt, bar);
+                    tma_load_2d(smem_addr(tiles + (size_t)s * p.stage_bytes) + a_bytes, &map_w, first.kb_at(s) * BK, first.m * p.nt, bar);
                 }
             __syncwarp();
         }
@@ -147,7 +150,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
         unsigned phase = 0;
         bool ok = true;
         while (lane == 0 && ok && it.next(p)) {
-            for (int kb = it.kb_lo; kb < it.kb_hi; ++kb, ++issued) {
+            for (int i = 0; i < it.kb_hi - it.kb_lo; ++i, ++issued) {
+                const int kb = it.kb_at(i);
                 ok = mbar_wait(empty0 + 8 * stage, phase ^ 1, p.status, 11);
                 if (!ok) break;
                 const unsigned bar = full0 + 8 * stage;
@@ -170,7 +174,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
             ok = mbar_wait(acce, (unsigned)((local & 1) ^ 1), p.status, 12);   // the epilogue has read the last tile
             if (!ok) break;
             tc_fence_after();
-            for (int kb = it.kb_lo; kb < it.kb_hi; ++kb) {
+            for (int i = 0; i < it.kb_hi - it.kb_lo; ++i) {
                 ok = mbar_wait(full0 + 8 * stage, phase, p.status, 13);
                 if (!ok) break;
                 tc_fence_after();
@@ -181,7 +185,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_decode_kernel(const _
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)      // 16 of k = 32 bytes further along the swizzled row
                         umma_bf16(tmem_base + (unsigned)(h * p.acc_stride), da + (unsigned long long)(2 * k), db + (unsigned long long)(2 * k), idesc,
-                                  (kb > it.kb_lo || k > 0) ? 1u : 0u);
+                                  (i > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(empty0 + 8 * stage);           // the stage is free once these MMAs have read it
                 if (++stage == p.stages) { stage = 0; phase ^= 1; }
@@ -353,6 +357,7 @@ extern "C" int ti_gemm_tcgen05_decode(void* y, long long ldy, const void* x, lon
     p.stage_bytes = p.halves * A_BYTES + nt * BK * 2;
     p.tmem_cols = 32;
     while (p.tmem_cols < p.halves * nt) p.tmem_cols *= 2;
+    p.rotate = 1;                                                // the blocks do not all ask L2 for the same token lines at once
     p.acc_stride = p.halves == 2 ? p.tmem_cols / 2 : 0;          // a power of two of at least nt columns
     p.ldy = ldy; p.epilogue = epilogue; p.act = XieluParams{alpha_p, alpha_n, beta, eps}; p.status = status;
     CUtensorMap mw, mx;
