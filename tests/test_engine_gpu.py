@@ -278,6 +278,34 @@ def test_a_long_prompt_in_chunks_through_the_tensor_core_attention(dtype):
         eng.check_health()
 
 
+def test_a_group_wider_than_the_fast_attention_takes_falls_back_to_the_plain_kernel():
+    """130 query heads on one KV head: more than the fast attention kernels take (128), so prompt and decode steps
+    run the plain attention kernel, with the same logits as the plain implementation."""
+    import tileinfer_b200 as ti
+    from tileinfer_b200.config import ApertusConfig
+    from tileinfer_b200.kernels import library
+    from tileinfer_b200.weights import write_model_folder
+    cfg = dict(helpers.TINY_A, num_attention_heads=130, num_key_value_heads=1, head_dim=16, hidden_size=72)
+    with tempfile.TemporaryDirectory() as d:
+        folder = write_model_folder(ApertusConfig.from_dict(cfg), 4, os.path.join(d, "m"))
+        pc, pw = plain.load_folder(folder)
+        prompts = helpers.random_prompts(pc.vocab, [70, 9], 5)
+        refs = [plain.forward(pc, pw, p, torch.bfloat16) for p in prompts]
+        eng = ti.Engine.load(folder, dtype="bfloat16", max_context=128, max_seqs=2)
+        ids = [eng.new_sequence() for _ in prompts]
+        before = dict(library.call_counts)
+        got = eng.step([(i, p[:-3]) for i, p in zip(ids, prompts)], [[len(p) - 4] for p in prompts]).cpu()
+        for n, (p, ref) in enumerate(zip(prompts, refs)):
+            assert float((got[n] - ref[len(p) - 4]).abs().max()) <= tolerance("bfloat16", ref), n
+        for t in range(3, 0, -1):
+            rows = eng.step([(i, [p[-t]]) for i, p in zip(ids, prompts)]).cpu()
+            for n, (p, ref) in enumerate(zip(prompts, refs)):
+                assert float((rows[n] - ref[len(p) - t]).abs().max()) <= tolerance("bfloat16", ref), (n, t)
+        used = {k for k, v in library.call_counts.items() if v > before.get(k, 0)}
+        assert "ti_attention_plain" in used
+        eng.check_health()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_more_sequences_in_a_decode_step_than_tokens_in_a_prompt_chunk(dtype):
     """40 sequences with prompt steps cut at 16 tokens: the prompts go through in several chunks, the one-token
