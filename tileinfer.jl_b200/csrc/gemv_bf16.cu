@@ -10,7 +10,8 @@
 // of its token, so every global load is 16 bytes; the k positions inside the two mma
 // operands are permuted the same way on both sides, which leaves the dot product unchanged.
 // The weights are read once and pass L1 by; the tokens, which every block reads, go through it,
-// so the blocks that an SM runs one after the other ask L2 for them once.
+// where a block finds part of what the blocks before it on the same SM read (about half of the
+// token reads hit at 8 tokens).
 //
 // Epilogues: none, xIELU (up_proj), 32-bit logits (LM head), or raw 32-bit partial sums
 // [split, n, out] that the following residual-add + RMSNorm kernel adds in a fixed order.
