@@ -43,7 +43,7 @@ def read_config(c: dict) -> SimpleNamespace:
         head_dim=c.get("head_dim") or c["hidden_size"] // heads,
         eps=c["rms_norm_eps"], theta=theta, scaling=scaling,
         max_pos=c["max_position_embeddings"], tied=c.get("tie_word_embeddings", False),
-        qk_norm=c.get("qk_norm", True), init_std=c.get("initializer_range", 0.02),
+        qk_norm=c.get("qk_norm", False), init_std=c.get("initializer_range", 0.02),
         eos=[] if eos is None else [eos] if isinstance(eos, int) else list(eos),
     )
 

@@ -31,6 +31,14 @@ def test_defaults_and_derived_sizes():
                             "high_freq_factor": 4.0, "original_max_position_embeddings": 128}
     c = ApertusConfig.from_dict(d)
     assert c.rope_theta == 5e5 and c.rope_scaling.factor == 2.0
+    # Keys a config may leave out take the reference's defaults (src/config.jl:84-91): no q/k norm unless it says
+    # so, untied head, no stop tokens.
+    for key in ("qk_norm", "tie_word_embeddings", "eos_token_id"):
+        d.pop(key, None)
+    c = ApertusConfig.from_dict(d)
+    assert not c.qk_norm and not c.tie_word_embeddings and c.eos_token_ids == ()
+    from tileinfer_b200.engine.model import tensor_declarations
+    assert not any("q_norm" in t.name for t in tensor_declarations(c.model_spec()))
 
 
 def test_round_trip_through_config_json():

@@ -122,8 +122,9 @@ class ApertusConfig:
             rope_scaling=parse_rope_scaling(scaling),
             max_position_embeddings=int(_require(c, "max_position_embeddings")),
             tie_word_embeddings=bool(c.get("tie_word_embeddings", False)),
-            # Every Apertus checkpoint norms q and k; a config may still switch it off.
-            qk_norm=bool(c.get("qk_norm", True)),
+            # Apertus checkpoints say qk_norm: true; a config without the key has none, as in the reference
+            # (src/config.jl:91: the default is false for every model type but qwen3).
+            qk_norm=bool(c.get("qk_norm", False)),
             hidden_act=hidden_act,
             dtype=dtype,
             bos_token_id=c.get("bos_token_id"),

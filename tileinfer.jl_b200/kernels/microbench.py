@@ -243,7 +243,7 @@ def timeline(batch, layers, cached=1023, prefill_tokens=0, shape=None):
         "architectures": ["ApertusForCausalLM"], "num_hidden_layers": layers, "hidden_size": s["hidden"],
         "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["head_dim"],
         "intermediate_size": s["intermediate"], "vocab_size": s["vocab"], "rope_theta": 12e6, "rms_norm_eps": 1e-5,
-        "max_position_embeddings": 4096})
+        "max_position_embeddings": 4096, "qk_norm": True, "hidden_act": "xielu"})
     eng = Engine.random(cfg, seed=0, dtype="bfloat16", max_context=4096, max_seqs=max(batch, 1),
                         max_tokens=max(batch * 1280, prefill_tokens + 64), max_step_tokens=max(prefill_tokens, 2048))
     if prefill_tokens:
