@@ -123,3 +123,25 @@ def test_decode_work_tables_cover_every_page_once():
             order = np.argsort(lengths)
             parts_of = (seq & 255)[order]
             assert all(parts_of[i] <= parts_of[i + 1] for i in range(B - 1))           # more keys, no fewer parts
+
+
+def test_every_legal_step_fits_the_metadata_buffers():
+    """For random engine sizes (with and without the decode attention's tables, one or two cache groups): the layout of
+    every step the engine may ask for (up to max_step_tokens tokens over up to max_seqs sequences, every token wanted;
+    one token for each of up to max_seqs sequences) ends inside the planner's buffers."""
+    rng = random.Random(11)
+    for _ in range(40):
+        max_seqs = rng.choice([1, 2, 7, 33, 64, 200])
+        max_step = rng.choice([1, 5, 31, 32, 33, 500, 4096])
+        requests = [CacheRequest("paged_kv", kv_heads=2, head_dim=16)]
+        if rng.random() < 0.4:
+            requests.append(CacheRequest("paged_kv", kv_heads=1, head_dim=32, window=24))
+        cache = Cache(requests, torch.float32, "cpu", max_tokens=64 * max_seqs, max_seqs=max_seqs, page_size=rng.choice([4, 16, 64]))
+        planner = StepPlanner(cache, max_step, "cpu")
+        if rng.random() < 0.7:
+            planner.attach_plan(cache.paged_groups[0], SplitKvPlan(2, cache.page_size, cache.max_tokens))
+        cases = [(b, b, b) for b in {1, max_seqs, max(1, max_seqs // 2)}]
+        cases += [(max_step, min(max_step, max_seqs), max_step), (max_step, 1, max_step), (max_step, min(max_step, max_seqs), 0)]
+        for n, B, nw in cases:
+            o, _ = planner._layout(n, B, nw)
+            assert o["end"] <= planner.capacity, (max_seqs, max_step, n, B, nw, o["end"], planner.capacity)
